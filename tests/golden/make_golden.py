@@ -1,0 +1,91 @@
+"""Generate the golden fixtures in this folder.
+
+Runs the reference's own, unmodified Python modules (imported from its
+checkout through ``oracle/ref_shim.py``) on seeded synthetic inputs and
+stores what they return.  Needs the reference checkout; run from the repo
+root:  ``python tests/golden/make_golden.py``.
+
+Fixtures
+  layer_tiny_fp32.npz   one DeiT-Ti DGE block, fp32, B=2, 16x16 grid + cls,
+                        dim 192, 3 heads; weights seed 0, tokens seed 1,
+                        gate logits seed 2 injected in place of the router.
+  model_tiny_fp32.npz   full DeiT-Ti+DGE (12 blocks), fp32, B=2, images seed 1,
+                        free-running router: logits, per-layer grain indices
+                        and per-image query counts.
+Inputs are regenerated from the seeds by the tests; each fixture carries a
+float64 sum of its inputs so RNG drift is detected rather than misread as a
+parity failure.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from oracle import dge_oracle as O  # noqa: E402
+from oracle import ref_shim  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def layer_fixture():
+    _, _, deit_dge, _ = ref_shim.reference_modules()
+    sd = O.make_state_dict(192, 1, 3, seed=0)
+    x = O.make_tokens(2, 257, 192, seed=1)
+    gate = O.make_gate_logits(2, 4, 4, 3, seed=2)
+    blk = deit_dge.Block(192, 3, mlp_ratio=4, qkv_bias=True,
+                         norm_layer=lambda d: torch.nn.LayerNorm(d, eps=1e-6),
+                         split_sizes=[4, 2, 1])
+    blk.load_state_dict(O.block_weights(sd, 0), strict=True)
+    blk.eval()
+    blk.dge.router.forward = lambda t: gate          # teacher-forced gate logits
+    with torch.no_grad():
+        out = blk(x)
+    st = blk.dge.states
+    np.savez_compressed(
+        os.path.join(HERE, "layer_tiny_fp32.npz"),
+        input_sum=np.float64(x.double().sum().item()),
+        weight_sum=np.float64(sum(v.double().sum().item() for v in sd.values())),
+        gate_sum=np.float64(gate.double().sum().item()),
+        patches=st["patches"].numpy().astype(np.int16),
+        batch_lengths=st["batches"].numpy(),
+        comp_rows=st["comp"][::7].numpy(),
+        out=out.numpy(),
+    )
+    print("layer:", out.shape, st["batches"].tolist())
+
+
+def model_fixture():
+    _, _, deit_dge, _ = ref_shim.reference_modules()
+    sd = O.make_state_dict(192, 12, 3, seed=0)
+    m = deit_dge.deit_dge_s124_tiny_patch16_256()
+    m.load_state_dict(sd, strict=True)
+    m.eval()
+    x = O.make_images(2, 256, seed=1)
+    with torch.no_grad():
+        logits = m(x)
+        idx, cnt, margin = [], [], []
+        for blk in m.blocks:
+            g = blk.dge.states["gate"]
+            idx.append(g.argmax(-1).numpy())
+            cnt.append(blk.dge.states["batches"].numpy())
+            top2 = g.topk(2, dim=-1).values
+            margin.append((top2[..., 0] - top2[..., 1]).numpy())
+    np.savez_compressed(
+        os.path.join(HERE, "model_tiny_fp32.npz"),
+        input_sum=np.float64(x.double().sum().item()),
+        weight_sum=np.float64(sum(v.double().sum().item() for v in sd.values())),
+        logits=logits.numpy(),
+        grain_indices=np.stack(idx).astype(np.int8),
+        batch_lengths=np.stack(cnt),
+        gate_margin=np.stack(margin),
+    )
+    print("model:", logits.shape, np.stack(cnt).tolist(), "min margin", float(np.stack(margin).min()))
+
+
+if __name__ == "__main__":
+    layer_fixture()
+    model_fixture()

@@ -1,0 +1,173 @@
+"""CPU tests that pin the oracle: golden fixtures produced by the reference's
+own Python modules, and (when the reference checkout is present) cross-checks
+against the reference's independent dense implementations."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import dge_oracle as O
+from oracle import ref_shim
+
+needs_ref = pytest.mark.skipif(not ref_shim.reference_available(),
+                               reason="reference checkout not present")
+
+
+def _load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+def test_layer_golden(golden_dir):
+    g = _load(golden_dir, "layer_tiny_fp32.npz")
+    sd = O.make_state_dict(192, 1, 3, seed=0)
+    x = O.make_tokens(2, 257, 192, seed=1)
+    gate = O.make_gate_logits(2, 4, 4, 3, seed=2)
+    assert math.isclose(x.double().sum().item(), float(g["input_sum"]), rel_tol=0, abs_tol=1e-9)
+    assert math.isclose(sum(v.double().sum().item() for v in sd.values()), float(g["weight_sum"]),
+                        rel_tol=0, abs_tol=1e-9)
+    assert math.isclose(gate.double().sum().item(), float(g["gate_sum"]), rel_tol=0, abs_tol=1e-9)
+    tr = {}
+    out = O.dge_block_forward(x, O.block_weights(sd, 0), 3, (4, 2, 1), forced_gate=gate, trace=tr)
+    pg = torch.from_numpy(g["patches"].astype(np.int64))
+    keep = pg[:, 1] >= 0
+    assert torch.equal(tr["patches"][:, [0, 1, 3]], pg[:, [0, 1, 3]])
+    assert torch.equal(tr["patches"][keep, 2], pg[keep, 2])
+    assert tr["batches"].tolist() == g["batch_lengths"].tolist()
+    assert torch.equal(tr["comp"][::7], torch.from_numpy(g["comp_rows"]))
+    assert torch.equal(out, torch.from_numpy(g["out"]))
+
+
+def test_model_golden(golden_dir):
+    g = _load(golden_dir, "model_tiny_fp32.npz")
+    sd = O.make_state_dict(192, 12, 3, seed=0)
+    x = O.make_images(2, 256, seed=1)
+    assert math.isclose(x.double().sum().item(), float(g["input_sum"]), rel_tol=0, abs_tol=1e-9)
+    tr = []
+    logits = O.deit_dge_forward(x, sd, 12, 3, (4, 2, 1), trace=tr)
+    assert np.array_equal(np.stack([t["indices"].numpy() for t in tr]), g["grain_indices"])
+    assert np.array_equal(np.stack([t["batches"].numpy() for t in tr]), g["batch_lengths"])
+    assert torch.equal(logits, torch.from_numpy(g["logits"]))
+
+
+def test_patch_order_and_counts():
+    """Rows are ordered by (image, extra first, region row-major, dy, dx) and the
+    per-image count is extra + sum(split^2)  (grained_sample.cu:146-196,302-345)."""
+    g = torch.Generator().manual_seed(5)
+    idx = torch.randint(0, 3, (3, 4, 4), generator=g)
+    splits = torch.tensor([4, 2, 1])
+    patches, lens = O.grained_sample_index_to_patch(idx, splits, 4, 1)
+    assert lens.tolist() == (1 + (splits[idx] ** 2).reshape(3, -1).sum(1)).tolist()
+    assert patches.shape[0] == int(lens.sum())
+    row = 0
+    for b in range(3):
+        assert patches[row].tolist()[0:2] == [b, -1] and patches[row, 3] == 1
+        row += 1
+        for ry in range(4):
+            for rx in range(4):
+                s = int(splits[idx[b, ry, rx]])
+                step = 4 // s
+                for dy in range(s):
+                    for dx in range(s):
+                        assert patches[row].tolist() == [b, ry * 4 + dy * step, rx * 4 + dx * step, step]
+                        row += 1
+    assert row == patches.shape[0]
+
+
+def test_empty_and_extreme_gates():
+    splits = torch.tensor([4, 2, 1])
+    # all coarse / all fine / no extra tokens
+    for k, per_region in ((2, 1), (0, 16)):
+        idx = torch.full((2, 4, 4), k)
+        p, l = O.grained_sample_index_to_patch(idx, splits, 4, 1)
+        assert l.tolist() == [1 + 16 * per_region] * 2
+        p0, l0 = O.grained_sample_index_to_patch(idx, splits, 4, 0)
+        assert l0.tolist() == [16 * per_region] * 2 and (p0[:, 1] >= 0).all()
+    x = torch.randn(2, 257, 8)
+    idx = torch.zeros(2, 4, 4, dtype=torch.int64)
+    p, l = O.grained_sample_index_to_patch(idx, splits, 4, 1)
+    comp = O.grained_sample_compress(x, p, 16, 16, 1)
+    # all-fine: compress is a permutation of the tokens (region-major order)
+    back = O.grained_sample_decompress(comp, p, torch.zeros_like(x), 16, 16, 1, True)
+    assert torch.equal(back, x)
+
+
+@needs_ref
+def test_sparse_matches_reference_dense():
+    """One-hot gate: the sparse ops equal the rows the reference's dense PyTorch
+    functions select (vtpack/layers/grained_sample.py:126-177)."""
+    _, gs, _, _ = ref_shim.reference_modules()
+    g = torch.Generator().manual_seed(11)
+    B, H, W, C = 3, 16, 16, 24
+    x = torch.randn(B, H * W + 1, C, generator=g)
+    splits = torch.tensor([4, 2, 1])
+    idx = torch.randint(0, 3, (B, 4, 4), generator=g)
+    patches, lens = O.grained_sample_index_to_patch(idx, splits, 4, 1)
+    comp = O.grained_sample_compress(x, patches, H, W, 1)
+    dense, dlen = gs.grained_sample_compress_dense(x, splits, 4, H, W, 1)
+    dense = dense.reshape(B, -1, C)                      # [B, 1+256+64+16, C]
+    starts = {1: 1, 2: 1 + 256, 4: 1 + 256 + 64}
+    for r in range(patches.shape[0]):
+        b, y, xx, step = patches[r].tolist()
+        if y < 0:
+            ref = dense[b, -y - 1]
+        else:
+            wi = W // step
+            ref = dense[b, starts[step] + (y // step) * wi + xx // step]
+        assert torch.allclose(comp[r], ref, rtol=1e-6, atol=1e-6)
+
+    # decompress: scatter sparse rows into the dense layout, one-hot gate
+    q = torch.randn(patches.shape[0], C, generator=g)
+    gate = torch.zeros(B, 4, 4, 3).scatter_(-1, idx[..., None], 1.0)
+    qd = torch.zeros(B, dense.shape[1], C)
+    for r in range(patches.shape[0]):
+        b, y, xx, step = patches[r].tolist()
+        if y < 0:
+            qd[b, -y - 1] = q[r]
+        else:
+            qd[b, starts[step] + (y // step) * (W // step) + xx // step] = q[r]
+    ref_out = gs.grained_sample_decompress_dense(qd.reshape(-1, C), gate, x, splits, 4, H, W, 1, True)
+    out = O.grained_sample_decompress(q, patches, x, H, W, 1, True)
+    assert torch.allclose(out, ref_out, rtol=1e-6, atol=1e-6)
+
+
+@needs_ref
+def test_all_fine_equals_reference_dense_block():
+    """Every region at split 4: the DGE block is the dense DeiT block
+    (vtpack/models/standard/deit.py:50-83) with q|kv concatenated to qkv."""
+    _, _, _, deit = ref_shim.reference_modules()
+    C, h = 96, 3
+    sd = O.make_state_dict(C, 1, h, seed=3)
+    w = O.block_weights(sd, 0)
+    x = O.make_tokens(2, 257, C, seed=4)
+    gate = torch.zeros(2, 4, 4, 3)
+    gate[..., 0] = 1.0
+    out = O.dge_block_forward(x, w, h, (4, 2, 1), forced_gate=gate)
+    blk = deit.Block(C, h, mlp_ratio=4, qkv_bias=True,
+                     norm_layer=lambda d: torch.nn.LayerNorm(d, eps=1e-6))
+    dsd = {k: v for k, v in w.items() if not k.startswith(("dge.", "attn.q.", "attn.kv."))}
+    dsd["attn.qkv.weight"] = torch.cat([w["attn.q.weight"], w["attn.kv.weight"]], 0)
+    dsd["attn.qkv.bias"] = torch.cat([w["attn.q.bias"], w["attn.kv.bias"]], 0)
+    blk.load_state_dict(dsd, strict=True)
+    blk.eval()
+    with torch.no_grad():
+        ref = blk(x)
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(O.dense_block_forward(x, w, h), ref, rtol=1e-5, atol=1e-5)
+
+
+@needs_ref
+def test_reference_modules_match_restatement():
+    """The reference's Block/VisionTransformer over the _C stand-in equal the
+    module-level restatement bit for bit."""
+    _, _, deit_dge, _ = ref_shim.reference_modules()
+    sd = O.make_state_dict(192, 2, 3, seed=7)
+    m = deit_dge.VisionTransformer(img_size=256, patch_size=16, embed_dim=192, depth=2, num_heads=3,
+                                   mlp_ratio=4, qkv_bias=True, split_sizes=[4, 2, 1])
+    m.load_state_dict(sd, strict=True)
+    m.eval()
+    x = O.make_images(2, 256, seed=8)
+    with torch.no_grad():
+        ref = m(x)
+    assert torch.equal(O.deit_dge_forward(x, sd, 2, 3, (4, 2, 1)), ref)
