@@ -1,0 +1,303 @@
+#!/usr/bin/env python
+"""Throughput benchmark of the DeiT+DGE eval forward (BASELINE metric: images/sec).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One step = one forward of `--batch` synthetic 256x256 images per GPU through the whole
+model (patch embed, 12 DGE blocks, head) with the logits all-gathered when N > 1.
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the
+reference's eval path on the host cores instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+STAGES = ["router_gate", "patch_list", "pool_ln1", "q_proj", "kv_proj", "attention", "out_proj", "ln2", "fc1_gelu",
+          "fc2", "unpool_add"]
+# DRAM bytes per launch of the dominant kernel from the ncu capture summarised under profiles/ (null until captured)
+NCU_TRAFFIC_BYTES = None
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {k: float(d.get(k, FALLBACK_PEAKS[k])) for k in FALLBACK_PEAKS}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while running."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_reference_rate(model_kind, batch, steps, warmup):
+    """images/sec of the CPU restatement of the reference's eval forward (fp32, all host cores)."""
+    from oracle import dge_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = O.MODEL_CONFIGS[model_kind]
+    sd = O.make_state_dict(cfg["embed_dim"], cfg["depth"], cfg["num_heads"], seed=0)
+    img = O.make_images(batch, 256, seed=1)
+    with torch.no_grad():
+        for _ in range(warmup):
+            O.deit_dge_forward(img, sd, cfg["depth"], cfg["num_heads"], (4, 2, 1))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            O.deit_dge_forward(img, sd, cfg["depth"], cfg["num_heads"], (4, 2, 1))
+        dt = time.perf_counter() - t0
+    return batch * steps / dt, dt / steps * 1e3, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    b = args.cpu_batch
+    rate, ms, cores = cpu_reference_rate(args.model, b, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": "images/sec", "value": rate, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"DeiT-{args.model}+DGE s124 256px eval forward, CPU, fp32", "batch_per_step": b},
+        "cpu_baseline": {"value": rate, "unit": "images/s", "cores": cores, "kind": "port",
+                         "sample": f"{args.steps} forwards of {b} images (same model/config), torch CPU fp32"},
+        "e2e": {"value": rate, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def stage_profile(model, batch, device, iters, pk):
+    """Per-kernel times of one DGE block (block 0 weights) on N(0,1) tokens, from events the
+    library records between its launches; returns (rows, roofline of the dominant kernel)."""
+    import ctypes
+    from vtpack_b200 import _lib
+    from vtpack_b200.models.dge.deit_dge import _pack_block
+    from vtpack_b200.runtime import scratch
+    blk = model.blocks[len(model.blocks) // 2]
+    C, N = model.embed_dim, (model.img_size // model.patch_size) ** 2 + 1
+    dtype = model.compute_dtype()
+    e = 2 if dtype == torch.bfloat16 else 4
+    x = torch.randn(batch, N, C, device=device, generator=torch.Generator(device).manual_seed(3)).to(dtype)
+    out = torch.empty_like(x)
+    s = blk.shape_struct(x)
+    w = _pack_block(blk, dtype)
+    lib = _lib.lib()
+    nbytes = lib.vtp_block_workspace_bytes(ctypes.byref(s))
+    ws = scratch(device, nbytes)
+    counts = torch.empty(batch, dtype=torch.int32, device=device)
+    n_ev = len(STAGES) + 1
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(n_ev)] for _ in range(iters)]
+    stream = torch.cuda.current_stream(device)
+    for it in range(iters + 2):
+        row = evs[max(it - 2, 0)]
+        for ev in row:
+            ev.record(stream)            # creates the underlying cudaEvent_t
+        arr = (ctypes.c_void_p * n_ev)(*[ev.cuda_event for ev in row])
+        _lib.check(lib.vtp_dge_block_forward_timed(ctypes.byref(s), ctypes.byref(w), x.data_ptr(), out.data_ptr(),
+                                                   None, counts.data_ptr(), ws.data_ptr(), nbytes, arr, n_ev,
+                                                   stream.cuda_stream))
+    torch.cuda.synchronize(device)
+    L = int(counts.sum().item())
+    ms = [sum(evs[i][j].elapsed_time(evs[i][j + 1]) for i in range(iters)) / iters for j in range(len(STAGES))]
+    BN, H = batch * N, 4 * C
+    work = {   # (kind, algorithmic bytes or flops)
+        "router_gate": ("hbm", batch * (N - 1) * C * e), "patch_list": ("hbm", L * 16),
+        "pool_ln1": ("hbm", 2 * (BN + L) * C * e), "q_proj": ("tensor", 2 * L * C * C),
+        "kv_proj": ("tensor", 4 * BN * C * C), "attention": ("tensor", 4 * L * N * C),
+        "out_proj": ("tensor", 2 * L * C * C), "ln2": ("hbm", 2 * L * C * e),
+        "fc1_gelu": ("tensor", 2 * L * C * H), "fc2": ("tensor", 2 * L * C * H),
+        "unpool_add": ("hbm", (2 * BN + 2 * L) * C * e),
+    }
+    rows = []
+    for name, t in zip(STAGES, ms):
+        kind, amount = work[name]
+        if kind == "hbm":
+            ach, peak, unit = amount / (t * 1e-3) / 1e9, pk["hbm_gbs"], "GB/s"
+        else:
+            ach, peak, unit = amount / (t * 1e-3) / 1e12, pk["bf16_tflops_sustained"], "TFLOP/s"
+        rows.append({"kernel": name, "ms": round(t, 4), "bound": kind, "achieved": round(ach, 1), "unit": unit,
+                     "frac": round(ach / peak, 3)})
+    gemm = [r for r in rows if r["kernel"] in ("q_proj", "kv_proj", "out_proj", "fc1_gelu", "fc2")]
+    gemm_ms = sum(r["ms"] for r in gemm)
+    gemm_flops = sum(work[r["kernel"]][1] for r in gemm)
+    ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    roof = {"kernel": "linear_tc_kernel (q, kv, out, fc1, fc2 projections of one DGE block)", "bound": "tensor",
+            "achieved": round(ach, 1), "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+            "frac": round(ach / pk["bf16_tflops_sustained"], 3), "traffic": NCU_TRAFFIC_BYTES,
+            "share_of_block": round(gemm_ms / sum(ms), 3)}
+    t_roof = sum(work[r["kernel"]][1] / ((pk["hbm_gbs"] * 1e9) if r["bound"] == "hbm"
+                                         else (pk["bf16_tflops_sustained"] * 1e12)) for r in rows)
+    return rows, roof, {"queries_per_image": L / batch, "block_ms": round(sum(ms), 4),
+                        "kernel_weighted_roofline_frac": round(t_roof / (sum(ms) * 1e-3), 3)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--model", default="small", choices=["tiny", "small", "base"])
+    ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
+    ap.add_argument("--cpu-batch", type=int, default=8, help="images per step of the CPU arm")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--cuda-cores", action="store_true", help="bf16: CUDA-core GEMM/attention instead of tcgen05")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-stage-profile", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch.distributed as dist
+    from vtpack_b200 import _lib, parallel, synthetic
+    from vtpack_b200.serve import HostPipeline
+
+    rank, world, local = parallel.init_from_env("nccl")
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    _lib.lib()                                       # fails loudly if the CUDA library is missing
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    model = synthetic.build_model(args.model, device, dtype)
+    if args.cuda_cores:
+        model.flags = _lib.FLAG_CUDA_CORES
+    B = args.batch
+    img_dev = synthetic.images(B, 256, seed=1 + rank).to(device)          # 201 MB at B=256: larger than L2
+    logits = torch.empty(B, 1000, device=device)
+    gathered = torch.empty(world * B, 1000, device=device) if world > 1 else None
+
+    def step():
+        model(img_dev, logits_out=logits)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, logits)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms_total = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
+    ms_total = float(ms_total.item())
+    value = world * B * args.steps / (ms_total * 1e-3)
+
+    # end to end: pinned host images -> device -> forward -> (gather) -> host logits, copies overlapped
+    pipe = HostPipeline(model, B, 256, device, world=world)
+    host = [synthetic.images(B, 256, seed=100 + rank + 7 * i, pin=True) for i in range(2)]
+    batches = [host[i & 1] for i in range(args.steps)]
+    pipe.run(batches[:max(args.warmup, 3)])
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    pipe.run(batches)
+    e1.record()
+    barrier()
+    e2e_ms = torch.tensor([max(e0.elapsed_time(e1), 0.0)], device=device)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = world * B * args.steps / (float(e2e_ms.item()) * 1e-3)
+    _ = t0
+    clocks = sampler.stop() if sampler else None
+    status = _lib.device_status()
+
+    if rank == 0:
+        pk, pk_src = peaks()
+        line = {
+            "metric": "images/sec", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+            "config": {"workload": f"DeiT-{args.model}+DGE s124 (budget 0.5 stand-in: free-running random-init gate) "
+                                   f"256px eval forward, batch {B}/GPU, logits all-gathered",
+                       "batch_per_gpu": B, "global_batch": B * world, "parallelism": f"dp{world}",
+                       "l2": "inputs larger than L2 (fp32 images 201 MB/step at B=256)"},
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": pipe.h2d_bytes,
+                    "d2h_bytes_per_step": pipe.d2h_bytes},
+            "gpu_launches": args.steps * (5 + 12 * len(model.blocks)),
+            "clocks": clocks, "device_status": status, "peaks": pk_src,
+        }
+        if not args.no_stage_profile and dtype == torch.bfloat16:
+            rows, roof, extra = stage_profile(model, B, device, 10, pk)
+            line["roofline"] = roof
+            line["kernels"] = rows
+            line["block"] = extra
+        if world == 1 and not args.no_cpu_baseline:
+            rate, ms, cores = cpu_reference_rate(args.model, args.cpu_batch, 3, 1)
+            line["cpu_baseline"] = {"value": rate, "unit": "images/s", "cores": cores, "kind": "port",
+                                    "sample": f"3 forwards of {args.cpu_batch} images after 1 warm-up, fp32 torch CPU"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,250 @@
+/*
+ * vtpack_b200 — C ABI of the B200 (sm_100a) Dynamic Grained Encoder eval path.
+ *
+ * Conventions for every entry point
+ *   - plain device pointers, explicit sizes, `void* stream` = the caller's cudaStream_t;
+ *   - returns int: 0 ok; <0 an invalid argument found on the host before any launch
+ *     (VTP_ERR_*); >0 a cudaError_t / CUresult reported by the launch;
+ *   - never allocates device memory, never synchronises, never creates streams: the
+ *     caller owns every buffer, including worst-case sized scratch (L_max = B*N rows);
+ *   - element type is VTP_F32 or VTP_BF16; small per-channel vectors (biases, LayerNorm
+ *     weight/bias, gate weights) are always fp32;
+ *   - counts that are only known on the device (number of queries L) are read by the
+ *     kernels from `offsets[B]`; no entry point copies them to the host unless it says so.
+ *
+ * Each declaration cites the reference interface it replaces (paths inside the
+ * StevenGrove/vtpack tree).  The reference binds these through pybind11
+ * (vtpack/layers/csrc/vision.cpp:9-29) with at::Tensor arguments.
+ */
+#ifndef VTPACK_B200_H
+#define VTPACK_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VTP_F32 0
+#define VTP_BF16 1
+
+#define VTP_OK 0
+#define VTP_ERR_NULL -1        /* required pointer is null */
+#define VTP_ERR_SHAPE -2       /* size out of the supported range */
+#define VTP_ERR_DTYPE -3       /* unknown element type */
+#define VTP_ERR_ALIGN -4       /* pointer or stride not 16-byte aligned */
+#define VTP_ERR_UNSUPPORTED -5 /* combination not implemented */
+#define VTP_ERR_DRIVER -6      /* driver entry point unavailable */
+
+/* flags for vtp_linear / vtp_sparse_attention / block + model forward */
+#define VTP_FLAG_GELU 1u        /* erf GELU on (acc + bias) */
+#define VTP_FLAG_OUT_F32 2u     /* write fp32 even when inputs are bf16 */
+#define VTP_FLAG_CUDA_CORES 4u  /* bf16 inputs: use the CUDA-core kernel instead of tcgen05 */
+
+/* Library version, 1000*major + minor. */
+int vtp_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* vtp_last_error_string(void);
+
+/*
+ * Device status word: kernels that wait on mbarriers give up after a bounded time and
+ * OR a code into a per-device word instead of hanging.  Reads it back (synchronises the
+ * device); `reset` != 0 clears it.  0 = no kernel gave up.
+ */
+int vtp_device_status(int* value, int reset);
+
+/*
+ * Router gate: mean of each region's raw tokens, Linear(C -> n_splits) in fp32, argmax
+ * with the lowest index winning ties.
+ * Replaces DynamicRouter.forward + gate.argmax (vtpack/layers/dge.py:145-150, :75).
+ *   x           [B, num_extra + H*W, C]
+ *   gate_w/b    fp32 [n_splits, C] / [n_splits]
+ *   logits_out  fp32 [B, H/region, W/region, n_splits] or null
+ *   grain_idx   int32 [B, H/region, W/region]
+ */
+int vtp_router_gate(const void* x, int dtype, int B, int H, int W, int C, int num_extra,
+                    int region, const float* gate_w, const float* gate_b, int n_splits,
+                    float* logits_out, int32_t* grain_idx, void* stream);
+
+/* argmax over the last axis of fp32 logits [rows, n_splits] (first maximum wins), for
+ * teacher-forced gates.  Replaces gate.argmax(dim=-1) (vtpack/layers/dge.py:75). */
+int vtp_gate_argmax(const float* logits, int rows, int n_splits, int32_t* grain_idx,
+                    void* stream);
+
+/*
+ * Patch list from grain indices.
+ * Replaces grained_sample_index_to_patch (grained_sample.cu:302-345, kernel :146-196),
+ * without its device-to-host copy.
+ *   indices     [B, Hr, Wr] int32 (idx_is_i64 = 0) or int64 (1): index into splits
+ *   splits      HOST array, n_splits entries (e.g. 4,2,1): sub-patches per region side
+ *   counts      int32 [B]     queries per image = num_extra + sum(split^2)
+ *   offsets     int32 [B+1]   exclusive prefix of counts; offsets[B] = L
+ *   patches     int32 [L_max,4] rows [b, y, x, step]; extra tokens [b, -idx-1, 0, 1]
+ *   patches64   int64 [L_max,4] mirror in the reference's dtype, or null
+ */
+int vtp_index_to_patch(const void* indices, int idx_is_i64, const int* splits, int n_splits,
+                       int B, int Hr, int Wr, int region, int num_extra, int32_t* counts,
+                       int32_t* offsets, int32_t* patches, int64_t* patches64, void* stream);
+
+/*
+ * Multi-grain average pooling, optionally fused with the two LayerNorms that follow it.
+ * Replaces grained_sample_compress (grained_sample.cu:198-239, kernel :31-69) and, when
+ * ln_w != null, norm1(x) and norm1(q) (vtpack/models/dge/deit_dge.py:127).
+ *   x [B,N,C]; patches int32 [L,4]; n_patches_dev -> device int32 holding L (e.g.
+ *   offsets + B), or null to use n_patches_max as L.
+ *   comp [L_max,C];  xn [B,N,C] = LN(x) or null;  qn [L_max,C] = LN(comp) or null.
+ */
+int vtp_pool(const void* x, int dtype, int B, int N, int C, int W, int num_extra,
+             const int32_t* patches, const int32_t* n_patches_dev, int n_patches_max,
+             void* comp, const float* ln_w, const float* ln_b, float eps, void* xn, void* qn,
+             void* stream);
+
+/*
+ * Replicate-unpool with residual: out[b,tok,:] = q[p,:] - comp[p,:] + ref[b,tok,:] for
+ * every token of patch p.  comp may be null (q is already a delta); ref may be null
+ * (no residual).  out may alias ref.
+ * Replaces DynamicGrainedEncoder.decompress (vtpack/layers/dge.py:87-112) and
+ * grained_sample_decompress (grained_sample.cu:241-300, kernels :71-144).
+ */
+int vtp_unpool_add(const void* q, const void* comp, int dtype, int B, int N, int C, int W,
+                   int num_extra, const int32_t* patches, const int32_t* n_patches_dev,
+                   int n_patches_max, const void* ref, void* out, void* stream);
+
+/*
+ * LayerNorm over the last axis.  Row r of the input starts at x + r*in_row_stride
+ * elements; output rows are dense.  rows_dev (device int32) overrides rows_max when set.
+ * Replaces nn.LayerNorm norm2 / norm (vtpack/models/dge/deit_dge.py:128, :277).
+ */
+int vtp_layernorm(const void* x, int dtype, int rows_max, const int32_t* rows_dev, int C,
+                  long long in_row_stride, const float* w, const float* b, float eps, void* y,
+                  void* stream);
+
+/*
+ * y[m, n] = act(sum_k a[m,k] * w[n,k] + bias[n]) + residual[m,n]
+ * a [M,K] (row stride lda elements), w [N,K] dense, bias fp32 [N] or null,
+ * residual [M,N] (row stride ldr) or null, y [M,N] (row stride ldy).
+ * m_dev (device int32) overrides m_max when set.  bf16 inputs run on tcgen05 tensor
+ * cores (K % 64 == 0, 16-byte aligned rows); fp32 inputs on CUDA cores.
+ * Replaces nn.Linear q/kv/proj/fc1/fc2/head (vtpack/models/dge/deit_dge.py:27-29,55-58,216)
+ * with the GELU (:40) and the residual adds (:127-128) as epilogues.
+ */
+int vtp_linear(const void* a, long long lda, const void* w, const float* bias,
+               const void* residual, long long ldr, void* y, long long ldy, int dtype,
+               int m_max, const int32_t* m_dev, int N, int K, unsigned flags, void* stream);
+
+/*
+ * Variable-length-query attention: for image i, head h,
+ *   out[rows of i] = softmax(scale * Q_i K_i^T) V_i   over all n_keys keys.
+ * q/out rows are the packed queries (offsets[i] .. offsets[i+1]); strides are in
+ * elements; the head dim is contiguous.  Accepts the Linear outputs in place:
+ * q [L, h*d] -> q_row_stride = h*d, q_head_stride = d;  kv [B, N, 2, h, d] ->
+ * k = kv, v = kv + h*d, kv_batch_stride = N*2*h*d, kv_row_stride = 2*h*d.
+ * offsets int32 [B+1] (device): first packed row of each image; l_max rows are allocated
+ * in q/out; max_q_per_image bounds the queries of any one image (it sizes the grid).
+ * Replaces batched_sparse_attention_forward (batched_sparse_gemm.cu:219-305) and the
+ * .contiguous() copies in front of it (vtpack/layers/sparse_ops.py:60-78).
+ */
+int vtp_sparse_attention(const void* q, long long q_row_stride, long long q_head_stride,
+                         const void* k, const void* v, long long kv_batch_stride,
+                         long long kv_row_stride, long long kv_head_stride, void* out,
+                         long long o_row_stride, long long o_head_stride, int dtype, int B,
+                         int n_keys, int heads, int head_dim, const int32_t* offsets,
+                         int l_max, int max_q_per_image, float scale, unsigned flags,
+                         void* stream);
+
+/*
+ * Patch embedding front end: images fp32 [B,3,S,S] -> im2col rows [B*(S/P)^2, 3*P*P] in
+ * `dtype` (column = c*P*P + py*P + px, the flattening of the conv weight), and writes the
+ * cls row x[b,0,:] = cls_token + pos_embed[0].  The GEMM itself is vtp_linear.
+ * Replaces PatchEmbed + cls/pos add (vtpack/models/dge/deit_dge.py:268-275).
+ */
+int vtp_patch_im2col(const float* images, int B, int S, int P, int dtype, void* cols,
+                     const void* cls_token, const void* pos_embed, int C, void* x,
+                     void* stream);
+
+/* Pointers to one block's parameters (device memory).  Matrices are in the model dtype,
+ * vectors fp32.  Keys are the reference's state_dict names below blocks.{i}. */
+typedef struct {
+    const float* norm1_w; const float* norm1_b;
+    const void* q_w; const float* q_b;          /* attn.q    [C, C]  */
+    const void* kv_w; const float* kv_b;        /* attn.kv   [2C, C] */
+    const void* proj_w; const float* proj_b;    /* attn.proj [C, C]  */
+    const float* norm2_w; const float* norm2_b;
+    const void* fc1_w; const float* fc1_b;      /* mlp.fc1   [hidden, C] */
+    const void* fc2_w; const float* fc2_b;      /* mlp.fc2   [C, hidden] */
+    const float* gate_w; const float* gate_b;   /* dge.router.gate [n_splits, C] fp32 */
+} vtp_block_weights;
+
+/* Shapes shared by the block and model entry points. */
+typedef struct {
+    int dtype;       /* VTP_F32 / VTP_BF16 */
+    int B, H, W;     /* images, token grid */
+    int num_extra;   /* cls tokens in front of the grid (1) */
+    int C, heads, hidden;
+    int region;      /* tokens per region side (4) */
+    int n_splits;    /* entries of splits */
+    int splits[8];   /* sub-patches per region side, e.g. 4,2,1 */
+    float eps;       /* LayerNorm epsilon */
+    unsigned flags;  /* VTP_FLAG_CUDA_CORES */
+} vtp_dge_shape;
+
+/* Scratch bytes vtp_dge_block_forward needs for this shape (16-byte aligned slices). */
+long long vtp_block_workspace_bytes(const vtp_dge_shape* s);
+
+/*
+ * Eval forward of one DeiT+DGE block, x_in [B,N,C] -> x_out [B,N,C] (may alias).
+ * forced_logits (fp32 [B,Hr,Wr,n_splits]) replaces the router output when non-null.
+ * counts_out (int32 [B], optional) receives the per-image query counts.
+ * Replaces Block.forward (vtpack/models/dge/deit_dge.py:123-130).
+ */
+int vtp_dge_block_forward(const vtp_dge_shape* s, const vtp_block_weights* w, const void* x_in,
+                          void* x_out, const float* forced_logits, int32_t* counts_out,
+                          void* workspace, long long workspace_bytes, void* stream);
+
+/*
+ * Same as vtp_dge_block_forward, and records events[i] (cudaEvent_t created by the caller,
+ * null entries skipped) on the stream after stage i:
+ *   0 start, 1 router gate, 2 patch list, 3 pool+LN1, 4 q proj, 5 kv proj, 6 attention,
+ *   7 out proj+residual, 8 LN2, 9 fc1+GELU, 10 fc2+residual, 11 unpool+residual.
+ * For per-kernel timing; the reference has no counterpart (it logs wall-clock time per
+ * iteration only, vtpack/engine/utils.py:128-172).
+ */
+#define VTP_BLOCK_STAGES 12
+int vtp_dge_block_forward_timed(const vtp_dge_shape* s, const vtp_block_weights* w,
+                                const void* x_in, void* x_out, const float* forced_logits,
+                                int32_t* counts_out, void* workspace, long long workspace_bytes,
+                                void* const* events, int n_events, void* stream);
+
+/* Dense DeiT block from the same weights (q and kv applied to every token), the
+ * comparison baseline.  Replaces Block.forward of vtpack/models/standard/deit.py:79-83. */
+int vtp_dense_block_forward(const vtp_dge_shape* s, const vtp_block_weights* w, const void* x_in,
+                            void* x_out, void* workspace, long long workspace_bytes,
+                            void* stream);
+
+/* Model-level parameters outside the blocks. */
+typedef struct {
+    const void* patch_w; const float* patch_b;  /* patch_embed.proj [C, 3*P*P] */
+    const void* cls_token;                      /* [C]    model dtype */
+    const void* pos_embed;                      /* [N, C] model dtype */
+    const float* norm_w; const float* norm_b;
+    const void* head_w; const float* head_b;    /* head [classes, C] */
+    int depth, patch, img_size, num_classes;
+} vtp_model_weights;
+
+long long vtp_model_workspace_bytes(const vtp_dge_shape* s, const vtp_model_weights* m);
+
+/*
+ * Eval forward of DeiT+DGE: images fp32 [B,3,S,S] (device) -> logits fp32 [B,classes].
+ * counts_out int32 [depth,B] optional.
+ * Replaces VisionTransformer.forward (vtpack/models/dge/deit_dge.py:267-299).
+ */
+int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weights* m,
+                         const vtp_block_weights* blocks, const float* images, float* logits,
+                         int32_t* counts_out, void* workspace, long long workspace_bytes,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VTPACK_B200_H */

@@ -1,0 +1,87 @@
+"""CPU checks of the C-ABI boundary: the library builds and loads, exports every symbol
+the header declares, and rejects bad arguments on the host with the documented codes
+(no kernel is launched)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from vtpack_b200 import build
+    build.build()
+    from vtpack_b200 import _lib
+    return _lib.lib()
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "vtpack_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(vtp_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(lib):
+    names = _declared()
+    assert len(names) >= 15
+    for n in names:
+        assert getattr(lib, n) is not None
+
+
+def test_bindings_cover_header(lib):
+    from vtpack_b200 import _lib
+    assert sorted(_lib.PROTOTYPES) == _declared()
+
+
+def test_version_and_error_string(lib):
+    assert lib.vtp_version() >= 1000
+    assert isinstance(lib.vtp_last_error_string(), bytes)
+
+
+def test_null_and_shape_errors(lib):
+    from vtpack_b200 import _lib
+    # null pointers
+    assert lib.vtp_router_gate(None, 0, 1, 16, 16, 64, 1, 4, None, None, 3, None, None, None) == -1
+    assert b"null" in lib.vtp_last_error_string()
+    assert lib.vtp_pool(None, 0, 1, 257, 64, 16, 1, None, None, 10, None, None, None, 0.0, None, None, None) == -1
+    assert lib.vtp_linear(None, 8, None, None, None, 0, None, 8, 0, 4, None, 8, 8, 0, None) == -1
+    # bad dtype / shape, with fake but aligned non-null pointers (never dereferenced on the host)
+    p = ctypes.c_void_p(4096)
+    assert lib.vtp_router_gate(p, 7, 1, 16, 16, 64, 1, 4, p, p, 3, None, p, None) == -3
+    assert lib.vtp_router_gate(p, 0, 1, 15, 16, 64, 1, 4, p, p, 3, None, p, None) == -2
+    assert lib.vtp_layernorm(p, 1, 4, None, 60, 60, p, p, 1e-6, p, None) == -2      # C not 16-byte multiple
+    q = ctypes.c_void_p(4100)
+    assert lib.vtp_layernorm(q, 1, 4, None, 64, 64, p, p, 1e-6, p, None) == -4      # unaligned
+    splits = (ctypes.c_int * 3)(4, 3, 1)
+    assert lib.vtp_index_to_patch(p, 0, splits, 3, 1, 4, 4, 4, 1, p, p, p, None, None) == -2  # 3 does not divide 4
+    s = _lib.DgeShape()
+    assert lib.vtp_block_workspace_bytes(ctypes.byref(s)) == -1
+
+
+def test_workspace_size_formula(lib):
+    from vtpack_b200 import _lib
+    s = _lib.DgeShape()
+    s.dtype, s.B, s.H, s.W, s.num_extra, s.C, s.heads, s.hidden, s.region, s.n_splits = 1, 4, 16, 16, 1, 192, 3, 768, 4, 3
+    s.splits[0], s.splits[1], s.splits[2] = 4, 2, 1
+    n = lib.vtp_block_workspace_bytes(ctypes.byref(s))
+    rows = 4 * 257
+    lower = rows * 2 * (192 * 6 + 2 * 192 + 768)
+    assert lower <= n <= lower + rows * 16 + 64 * 1024
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from vtpack_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libvtpack_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.lib()
+
+
+def test_cpu_tensors_rejected():
+    import torch
+    from vtpack_b200.layers import grained_sample_compress
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        grained_sample_compress(torch.zeros(1, 17, 8), torch.zeros(2, 4, dtype=torch.int64), 4, 4, 1)

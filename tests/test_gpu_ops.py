@@ -1,0 +1,223 @@
+"""GPU parity of the individual ops, called through the C ABI, against the CPU oracle."""
+import ctypes
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from tests.gpu_util import O, random_indices, rel_err, strip_col2_of_extra
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def vl():
+    from vtpack_b200 import _lib
+    from vtpack_b200 import layers
+    _lib.lib()
+    return _lib, layers
+
+
+@pytest.mark.parametrize("B,Hr,Wr,splits,extra", [
+    (1, 4, 4, [4, 2, 1], 1), (2, 4, 4, [4, 2, 1], 1), (64, 4, 4, [4, 2, 1], 1), (3, 8, 8, [4, 2, 1], 1),
+    (5, 4, 4, [2, 1], 1), (4, 4, 4, [4, 2, 1], 0), (2, 4, 4, [4, 2, 1], 2), (300, 4, 4, [4, 2, 1], 1),
+])
+def test_index_to_patch_bit_exact(vl, B, Hr, Wr, splits, extra):
+    _, layers = vl
+    idx = random_indices(B, Hr, Wr, len(splits), seed=B * 7 + Hr)
+    sp = torch.tensor(splits)
+    ref_p, ref_l = O.grained_sample_index_to_patch(idx, sp, max(splits), extra)
+    for dt in (torch.int64, torch.int32):
+        p, l = layers.grained_sample_index_to_patch(idx.to(DEV, dt), sp, max(splits), extra)
+        assert l.device.type == "cpu" and l.dtype == torch.int64
+        assert torch.equal(l, ref_l)
+        assert p.dtype == torch.int64 and torch.equal(strip_col2_of_extra(p.cpu()), ref_p)
+        assert torch.equal(p._vtp_i32.cpu().long(), p.cpu())
+        off = p._vtp_offsets.cpu().long()
+        assert torch.equal(off[1:] - off[:-1], ref_l) and off[0] == 0
+
+
+@pytest.mark.parametrize("k", [0, 2])
+def test_index_to_patch_extremes(vl, k):
+    _, layers = vl
+    sp = torch.tensor([4, 2, 1])
+    idx = torch.full((3, 4, 4), k)
+    ref_p, ref_l = O.grained_sample_index_to_patch(idx, sp, 4, 1)
+    p, l = layers.grained_sample_index_to_patch(idx.to(DEV), sp, 4, 1)
+    assert torch.equal(l, ref_l) and torch.equal(strip_col2_of_extra(p.cpu()), ref_p)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,G,C", [(2, 16, 192), (3, 16, 384), (2, 32, 64), (1, 16, 768), (2, 8, 8)])
+def test_pool_unpool_bit_exact(vl, dtype, B, G, C):
+    _, layers = vl
+    if dtype == torch.bfloat16 and C % 8:
+        pytest.skip("C must be a multiple of 16 bytes")
+    sp = torch.tensor([4, 2, 1])
+    idx = random_indices(B, G // 4, G // 4, 3, seed=G + C)
+    x = O.make_tokens(B, G * G + 1, C, seed=3).to(dtype)
+    patches, lens = O.grained_sample_index_to_patch(idx, sp, 4, 1)
+    ref = O.grained_sample_compress(x, patches, G, G, 1)
+    p_dev, _ = layers.grained_sample_index_to_patch(idx.to(DEV), sp, 4, 1)
+    got = layers.grained_sample_compress(x.to(DEV), p_dev, G, G, 1)
+    assert got.dtype == dtype and torch.equal(got.cpu(), ref)
+    # plain int64 patch list without the cached int32 mirror (the reference's calling convention)
+    got2 = layers.grained_sample_compress(x.to(DEV), patches.to(DEV), G, G, 1)
+    assert torch.equal(got2.cpu(), ref)
+
+    q = torch.randn(patches.shape[0], C, generator=torch.Generator().manual_seed(9)).to(dtype)
+    for add in (True, False):
+        ref_o = O.grained_sample_decompress(q, patches, x, G, G, 1, add)
+        got_o = layers.grained_sample_decompress(q.to(DEV), p_dev, x.to(DEV), G, G, 1, add)
+        assert torch.equal(got_o.cpu(), ref_o)
+
+
+def test_pool_all_fine_round_trip(vl):
+    _, layers = vl
+    sp = torch.tensor([4, 2, 1])
+    B, G, C = 4, 16, 384
+    idx = torch.zeros(B, 4, 4, dtype=torch.int64)
+    x = O.make_tokens(B, 257, C, seed=4).to(torch.bfloat16).to(DEV)
+    p, l = layers.grained_sample_index_to_patch(idx.to(DEV), sp, 4, 1)
+    assert l.tolist() == [257] * B
+    comp = layers.grained_sample_compress(x, p, G, G, 1)
+    back = layers.grained_sample_decompress(comp, p, torch.zeros_like(x), G, G, 1, True)
+    assert torch.equal(back, x)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("C", [192, 384, 768])
+def test_router_gate(vl, dtype, C):
+    from vtpack_b200.layers import DynamicRouter
+    B, G = 8, 16
+    x = O.make_tokens(B, G * G, C, seed=5).to(dtype)
+    r = DynamicRouter(C, [4, 2, 1])
+    torch.nn.init.trunc_normal_(r.gate.weight, std=0.02, generator=torch.Generator().manual_seed(6))
+    ref = O.router_forward(x.float().reshape(B, G, G, C), r.gate.weight.detach(), r.gate.bias.detach(), 4)
+    got = r.to(DEV)(x.to(DEV).reshape(B, G, G, C))
+    assert got.dtype == torch.float32
+    assert torch.allclose(got.cpu(), ref, rtol=1e-4, atol=1e-5)
+    top2 = ref.topk(2, -1).values
+    sure = (top2[..., 0] - top2[..., 1]) > 1e-5
+    assert torch.equal(r.last_indices.cpu().long()[sure], ref.argmax(-1)[sure])
+
+
+def test_gate_argmax_ties(vl):
+    _lib, _ = vl
+    logits = torch.tensor([[1., 1., 1.], [0., 2., 2.], [3., 1., 3.], [-1., -2., -0.5]], device=DEV)
+    idx = torch.empty(4, dtype=torch.int32, device=DEV)
+    _lib.check(_lib.lib().vtp_gate_argmax(logits.data_ptr(), 4, 3, idx.data_ptr(), None))
+    assert idx.tolist() == logits.cpu().argmax(-1).tolist() == [0, 1, 0, 2]
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("rows,C", [(5, 192), (1000, 384), (33, 768)])
+def test_layernorm(vl, dtype, tol, rows, C):
+    from vtpack_b200.models.dge.deit_dge import _layernorm
+    g = torch.Generator().manual_seed(7)
+    x = (torch.randn(rows, C, generator=g) * 3 + 1).to(dtype)
+    ln = torch.nn.LayerNorm(C, eps=1e-6)
+    ln.weight.data = torch.randn(C, generator=g)
+    ln.bias.data = torch.randn(C, generator=g)
+    ref = F.layer_norm(x.float(), (C,), ln.weight, ln.bias, 1e-6)
+    got = _layernorm(x.to(DEV), ln.to(DEV))
+    assert rel_err(got.float(), ref) < tol
+
+
+def _linear_case(M, N, K, dtype, gelu, res, flags, seed=0):
+    from vtpack_b200.models.dge.deit_dge import _linear
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    lin = torch.nn.Linear(K, N)
+    lin.weight.data = (torch.randn(N, K, generator=g) * 0.05).to(dtype).float()
+    lin.bias.data = torch.randn(N, generator=g)
+    r = torch.randn(M, N, generator=g).to(dtype) if res else None
+    ref = F.linear(x.float(), lin.weight, lin.bias)
+    if gelu:
+        ref = F.gelu(ref)
+    if res:
+        ref = ref + r.float()
+    got = _linear(x.to(DEV), lin.to(DEV), residual=None if r is None else r.to(DEV), gelu=gelu, flags=flags)
+    return got, ref
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (130, 192, 192), (257, 768, 192), (64, 1000, 384), (300, 384, 1536)])
+@pytest.mark.parametrize("gelu,res", [(False, False), (True, False), (False, True)])
+def test_linear_fp32(vl, M, N, K, gelu, res):
+    got, ref = _linear_case(M, N, K, torch.float32, gelu, res, 0)
+    assert rel_err(got, ref) < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (130, 192, 192), (257, 768, 192), (64, 1000, 384), (300, 384, 1536),
+                                   (1024, 1536, 384)])
+@pytest.mark.parametrize("gelu,res", [(False, False), (True, False), (False, True)])
+def test_linear_bf16_tensor_cores(vl, M, N, K, gelu, res):
+    _lib, _ = vl
+    got, ref = _linear_case(M, N, K, torch.bfloat16, gelu, res, 0)
+    assert _lib.device_status() == 0
+    assert rel_err(got.float(), ref) < 8e-3          # one bf16 rounding of the output
+    got_cc, _ = _linear_case(M, N, K, torch.bfloat16, gelu, res, _lib.FLAG_CUDA_CORES)
+    assert rel_err(got.float(), got_cc.float()) < 8e-3
+
+
+def test_linear_device_side_row_count(vl):
+    _lib, _ = vl
+    M, N, K = 500, 384, 384
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    m_dev = torch.tensor([137], dtype=torch.int32, device=DEV)
+    y = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    _lib.check(_lib.lib().vtp_linear(x.data_ptr(), K, w.data_ptr(), None, None, 0, y.data_ptr(), N, 1, M,
+                                     m_dev.data_ptr(), N, K, 0, None))
+    ref = x[:137].float() @ w.float().t()
+    assert rel_err(y[:137].float(), ref) < 8e-3
+    assert bool((y[137:] == 7.0).all())
+
+
+def _attn_case(dtype, B, N, h, lens, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    d = 64
+    L = sum(lens)
+    q = torch.randn(h, L, d, generator=g).to(dtype)
+    k = torch.randn(h, B, N, d, generator=g).to(dtype)
+    v = torch.randn(h, B, N, d, generator=g).to(dtype)
+    ref = O.batched_sparse_attention_forward(q.float(), k.float(), v.float(), torch.tensor(lens), d ** -0.5)
+    return q, k, v, ref
+
+
+@pytest.mark.parametrize("B,N,h,lens", [(2, 257, 3, [131, 116]), (3, 257, 6, [17, 257, 64]), (2, 1025, 2, [65, 1025]),
+                                        (1, 17, 1, [1])])
+def test_attention_fp32(vl, B, N, h, lens):
+    _, layers = vl
+    q, k, v, ref = _attn_case(torch.float32, B, N, h, lens)
+    got = layers.batched_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), torch.tensor(lens), 64 ** -0.5)
+    assert got.shape == ref.shape and rel_err(got, ref) < 1e-5
+
+
+@pytest.mark.parametrize("B,N,h,lens", [(2, 257, 3, [131, 116]), (3, 257, 6, [17, 257, 64]), (2, 1025, 2, [65, 1025])])
+def test_attention_bf16_cuda_cores(vl, B, N, h, lens):
+    _lib, layers = vl
+    q, k, v, ref = _attn_case(torch.bfloat16, B, N, h, lens)
+    got = layers.batched_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), torch.tensor(lens), 64 ** -0.5,
+                                          flags=_lib.FLAG_CUDA_CORES)
+    assert rel_err(got.float(), ref) < 8e-3
+
+
+def test_attention_strided_views(vl):
+    """q / k / v as permuted views of Linear outputs, as the model passes them."""
+    _, layers = vl
+    g = torch.Generator().manual_seed(3)
+    B, N, h, d = 2, 257, 3, 64
+    lens = [100, 57]
+    qflat = torch.randn(sum(lens), h * d, generator=g).to(DEV)
+    kv = torch.randn(B, N, 2, h, d, generator=g).to(DEV)
+    qv = qflat.reshape(-1, h, d).permute(1, 0, 2)
+    kvp = kv.permute(2, 3, 0, 1, 4)
+    ref = O.batched_sparse_attention_forward(qv.cpu().contiguous(), kvp[0].cpu().contiguous(),
+                                             kvp[1].cpu().contiguous(), torch.tensor(lens), d ** -0.5)
+    got = layers.batched_sparse_attention(qv, kvp[0], kvp[1], torch.tensor(lens), d ** -0.5)
+    assert rel_err(got, ref) < 1e-5
+    assert got.transpose(0, 1).reshape(-1, h * d).is_contiguous()

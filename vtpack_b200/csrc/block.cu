@@ -1,0 +1,313 @@
+// Whole-block and whole-model eval forwards: the host-side sequencing of the kernels on
+// one stream, with every intermediate in a caller-provided workspace and every
+// data-dependent size (the number of packed queries L) left on the device.
+//
+// Replaces Block.forward and VisionTransformer.forward
+// (vtpack/models/dge/deit_dge.py:123-130, 267-299) and, for the comparison baseline,
+// Block.forward of vtpack/models/standard/deit.py:79-83.
+#include "attention.h"
+#include "linear.h"
+
+namespace vtp {
+
+struct Carver {
+    char* base;
+    long long off = 0;
+    explicit Carver(void* p) : base(static_cast<char*>(p)) {}
+    void* take(long long bytes) {
+        void* r = base ? base + off : nullptr;
+        off += round_up(bytes, 256);
+        return r;
+    }
+};
+
+struct BlockScratch {
+    int32_t *idx, *counts, *offsets, *patches;
+    float* logits;
+    void *comp, *xn, *qn, *qp, *kv, *ao, *q1, *hid;
+    long long bytes;
+};
+
+static BlockScratch carve_block(const vtp_dge_shape& s, void* ws) {
+    const long long e = (long long)elem_size(s.dtype);
+    const int N = s.num_extra + s.H * s.W;
+    const long long rows = (long long)s.B * N;            // worst case: every region at the finest grain
+    const int R = (s.H / s.region) * (s.W / s.region);
+    Carver c(ws);
+    BlockScratch b;
+    b.idx = (int32_t*)c.take((long long)s.B * R * 4);
+    b.counts = (int32_t*)c.take((long long)s.B * 4);
+    b.offsets = (int32_t*)c.take((long long)(s.B + 1) * 4);
+    b.patches = (int32_t*)c.take(rows * 16);
+    b.logits = (float*)c.take((long long)s.B * R * s.n_splits * 4);
+    b.comp = c.take(rows * s.C * e);
+    b.xn = c.take(rows * s.C * e);
+    b.qn = c.take(rows * s.C * e);
+    b.qp = c.take(rows * s.C * e);
+    b.kv = c.take(rows * 2 * s.C * e);
+    b.ao = c.take(rows * s.C * e);
+    b.q1 = c.take(rows * s.C * e);
+    b.hid = c.take(rows * s.hidden * e);
+    b.bytes = c.off;
+    return b;
+}
+
+static int check_shape(const vtp_dge_shape* s) {
+    VTP_REQUIRE(s, VTP_ERR_NULL, "block: null shape");
+    VTP_REQUIRE(s->dtype == VTP_F32 || s->dtype == VTP_BF16, VTP_ERR_DTYPE, "block: dtype %d", s->dtype);
+    VTP_REQUIRE(s->B > 0 && s->H > 0 && s->W > 0 && s->C > 0 && s->heads > 0 && s->hidden > 0 && s->num_extra >= 0,
+                VTP_ERR_SHAPE, "block: bad shape");
+    VTP_REQUIRE(s->C % s->heads == 0, VTP_ERR_SHAPE, "block: C=%d not divisible by %d heads", s->C, s->heads);
+    VTP_REQUIRE(s->region > 0 && s->H % s->region == 0 && s->W % s->region == 0, VTP_ERR_SHAPE,
+                "block: grid %dx%d not divisible by region %d", s->H, s->W, s->region);
+    VTP_REQUIRE(s->n_splits >= 1 && s->n_splits <= 8, VTP_ERR_SHAPE, "block: n_splits %d", s->n_splits);
+    VTP_REQUIRE((long long)s->B * (s->num_extra + s->H * s->W) < (1ll << 30), VTP_ERR_SHAPE, "block: too many tokens");
+    return VTP_OK;
+}
+
+// Records events[i] on the stream after stage i when the caller asked for stage timing.
+struct StageMarks {
+    void* const* events = nullptr;
+    int n = 0;
+    cudaStream_t st = nullptr;
+    int mark(int i) const {
+        if (!events || i >= n || !events[i]) return VTP_OK;
+        const cudaError_t e = cudaEventRecord(static_cast<cudaEvent_t>(events[i]), st);
+        return e == cudaSuccess ? VTP_OK : fail((int)e, "stage event %d: %s", i, cudaGetErrorString(e));
+    }
+};
+
+static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, const void* x_in, void* x_out,
+                         const float* forced_logits, int32_t* counts_out, void* ws, cudaStream_t st,
+                         const StageMarks& marks = StageMarks()) {
+    const int N = s.num_extra + s.H * s.W;
+    const int rows = s.B * N;
+    const int Hr = s.H / s.region, Wr = s.W / s.region;
+    const int C = s.C, d = C / s.heads;
+    const unsigned kflag = s.flags & VTP_FLAG_CUDA_CORES;
+    BlockScratch b = carve_block(s, ws);
+    const int32_t* L_dev = b.offsets + s.B;
+    int rc;
+    if ((rc = marks.mark(0))) return rc;
+
+    if (forced_logits)
+        rc = vtp_gate_argmax(forced_logits, s.B * Hr * Wr, s.n_splits, b.idx, st);
+    else
+        rc = vtp_router_gate(x_in, s.dtype, s.B, s.H, s.W, C, s.num_extra, s.region, w.gate_w, w.gate_b,
+                             s.n_splits, b.logits, b.idx, st);
+    if (rc || (rc = marks.mark(1))) return rc;
+    rc = vtp_index_to_patch(b.idx, 0, s.splits, s.n_splits, s.B, Hr, Wr, s.region, s.num_extra, b.counts,
+                            b.offsets, b.patches, nullptr, st);
+    if (rc || (rc = marks.mark(2))) return rc;
+    if (counts_out) {
+        const cudaError_t e = cudaMemcpyAsync(counts_out, b.counts, (size_t)s.B * 4, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) return fail((int)e, "block: counts copy: %s", cudaGetErrorString(e));
+    }
+    rc = vtp_pool(x_in, s.dtype, s.B, N, C, s.W, s.num_extra, b.patches, L_dev, rows, b.comp, w.norm1_w,
+                  w.norm1_b, s.eps, b.xn, b.qn, st);
+    if (rc || (rc = marks.mark(3))) return rc;
+
+    LinearArgs lq;   // q = LN(comp) Wq^T + b
+    lq.a = b.qn; lq.lda = C; lq.w = w.q_w; lq.bias = w.q_b; lq.y = b.qp; lq.ldy = C; lq.dtype = s.dtype;
+    lq.m_max = rows; lq.m_dev = L_dev; lq.N = C; lq.K = C; lq.flags = kflag;
+    if ((rc = linear(lq, st)) || (rc = marks.mark(4))) return rc;
+
+    LinearArgs lkv;  // kv = LN(x) Wkv^T + b, rows stay [b, token, {k,v}, head, d]
+    lkv.a = b.xn; lkv.lda = C; lkv.w = w.kv_w; lkv.bias = w.kv_b; lkv.y = b.kv; lkv.ldy = 2 * C;
+    lkv.dtype = s.dtype; lkv.m_max = rows; lkv.N = 2 * C; lkv.K = C; lkv.flags = kflag;
+    if ((rc = linear(lkv, st)) || (rc = marks.mark(5))) return rc;
+
+    AttnArgs at;
+    const long long e = (long long)elem_size(s.dtype);
+    at.q = b.qp; at.q_rs = C; at.q_hs = d;
+    at.k = b.kv; at.v = static_cast<const char*>(b.kv) + (long long)C * e;
+    at.kv_bs = (long long)N * 2 * C; at.kv_rs = 2 * C; at.kv_hs = d;
+    at.out = b.ao; at.o_rs = C; at.o_hs = d;
+    at.dtype = s.dtype; at.B = s.B; at.n_keys = N; at.heads = s.heads; at.head_dim = d;
+    at.offsets = b.offsets; at.l_max = rows; at.max_q = N; at.scale = 1.0f / sqrtf((float)d); at.flags = kflag;
+    if ((rc = attention(at, st)) || (rc = marks.mark(6))) return rc;
+
+    LinearArgs lp;   // q1 = comp + attn_out Wp^T + b
+    lp.a = b.ao; lp.lda = C; lp.w = w.proj_w; lp.bias = w.proj_b; lp.res = b.comp; lp.ldr = C; lp.y = b.q1;
+    lp.ldy = C; lp.dtype = s.dtype; lp.m_max = rows; lp.m_dev = L_dev; lp.N = C; lp.K = C; lp.flags = kflag;
+    if ((rc = linear(lp, st)) || (rc = marks.mark(7))) return rc;
+
+    rc = vtp_layernorm(b.q1, s.dtype, rows, L_dev, C, C, w.norm2_w, w.norm2_b, s.eps, b.qn, st);
+    if (rc || (rc = marks.mark(8))) return rc;
+
+    LinearArgs l1;   // hid = GELU(LN2(q1) W1^T + b)
+    l1.a = b.qn; l1.lda = C; l1.w = w.fc1_w; l1.bias = w.fc1_b; l1.y = b.hid; l1.ldy = s.hidden;
+    l1.dtype = s.dtype; l1.m_max = rows; l1.m_dev = L_dev; l1.N = s.hidden; l1.K = C;
+    l1.flags = kflag | VTP_FLAG_GELU;
+    if ((rc = linear(l1, st)) || (rc = marks.mark(9))) return rc;
+
+    LinearArgs l2;   // q2 = q1 + hid W2^T + b   (into the q-projection buffer, dead by now)
+    l2.a = b.hid; l2.lda = s.hidden; l2.w = w.fc2_w; l2.bias = w.fc2_b; l2.res = b.q1; l2.ldr = C; l2.y = b.qp;
+    l2.ldy = C; l2.dtype = s.dtype; l2.m_max = rows; l2.m_dev = L_dev; l2.N = C; l2.K = s.hidden; l2.flags = kflag;
+    if ((rc = linear(l2, st)) || (rc = marks.mark(10))) return rc;
+
+    rc = vtp_unpool_add(b.qp, b.comp, s.dtype, s.B, N, C, s.W, s.num_extra, b.patches, L_dev, rows, x_in,
+                        x_out, st);
+    if (rc) return rc;
+    return marks.mark(11);
+}
+
+__global__ void dense_offsets_kernel(int32_t* offsets, int B, int N) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= B) offsets[i] = i * N;
+}
+
+static int dense_block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, const void* x_in, void* x_out,
+                               void* ws, cudaStream_t st) {
+    const int N = s.num_extra + s.H * s.W;
+    const int rows = s.B * N;
+    const int C = s.C, d = C / s.heads;
+    const unsigned kflag = s.flags & VTP_FLAG_CUDA_CORES;
+    BlockScratch b = carve_block(s, ws);
+    int rc;
+    dense_offsets_kernel<<<ceil_div(s.B + 1, 128), 128, 0, st>>>(b.offsets, s.B, N);
+    if ((rc = check_launch("dense offsets"))) return rc;
+    rc = vtp_layernorm(x_in, s.dtype, rows, nullptr, C, C, w.norm1_w, w.norm1_b, s.eps, b.xn, st);
+    if (rc) return rc;
+    LinearArgs lq;
+    lq.a = b.xn; lq.lda = C; lq.w = w.q_w; lq.bias = w.q_b; lq.y = b.qp; lq.ldy = C; lq.dtype = s.dtype;
+    lq.m_max = rows; lq.N = C; lq.K = C; lq.flags = kflag;
+    if ((rc = linear(lq, st))) return rc;
+    LinearArgs lkv;
+    lkv.a = b.xn; lkv.lda = C; lkv.w = w.kv_w; lkv.bias = w.kv_b; lkv.y = b.kv; lkv.ldy = 2 * C;
+    lkv.dtype = s.dtype; lkv.m_max = rows; lkv.N = 2 * C; lkv.K = C; lkv.flags = kflag;
+    if ((rc = linear(lkv, st))) return rc;
+    AttnArgs at;
+    const long long e = (long long)elem_size(s.dtype);
+    at.q = b.qp; at.q_rs = C; at.q_hs = d;
+    at.k = b.kv; at.v = static_cast<const char*>(b.kv) + (long long)C * e;
+    at.kv_bs = (long long)N * 2 * C; at.kv_rs = 2 * C; at.kv_hs = d;
+    at.out = b.ao; at.o_rs = C; at.o_hs = d;
+    at.dtype = s.dtype; at.B = s.B; at.n_keys = N; at.heads = s.heads; at.head_dim = d;
+    at.offsets = b.offsets; at.l_max = rows; at.max_q = N; at.scale = 1.0f / sqrtf((float)d); at.flags = kflag;
+    if ((rc = attention(at, st))) return rc;
+    LinearArgs lp;
+    lp.a = b.ao; lp.lda = C; lp.w = w.proj_w; lp.bias = w.proj_b; lp.res = x_in; lp.ldr = C; lp.y = b.q1;
+    lp.ldy = C; lp.dtype = s.dtype; lp.m_max = rows; lp.N = C; lp.K = C; lp.flags = kflag;
+    if ((rc = linear(lp, st))) return rc;
+    rc = vtp_layernorm(b.q1, s.dtype, rows, nullptr, C, C, w.norm2_w, w.norm2_b, s.eps, b.qn, st);
+    if (rc) return rc;
+    LinearArgs l1;
+    l1.a = b.qn; l1.lda = C; l1.w = w.fc1_w; l1.bias = w.fc1_b; l1.y = b.hid; l1.ldy = s.hidden;
+    l1.dtype = s.dtype; l1.m_max = rows; l1.N = s.hidden; l1.K = C; l1.flags = kflag | VTP_FLAG_GELU;
+    if ((rc = linear(l1, st))) return rc;
+    LinearArgs l2;
+    l2.a = b.hid; l2.lda = s.hidden; l2.w = w.fc2_w; l2.bias = w.fc2_b; l2.res = b.q1; l2.ldr = C; l2.y = x_out;
+    l2.ldy = C; l2.dtype = s.dtype; l2.m_max = rows; l2.N = C; l2.K = s.hidden; l2.flags = kflag;
+    return linear(l2, st);
+}
+
+struct ModelScratch {
+    void *cols, *x, *cls_n;
+    void* block_ws;
+    long long bytes;
+};
+
+static ModelScratch carve_model(const vtp_dge_shape& s, const vtp_model_weights& m, void* ws) {
+    const long long e = (long long)elem_size(s.dtype);
+    const int N = s.num_extra + s.H * s.W;
+    Carver c(ws);
+    ModelScratch r;
+    r.cols = c.take((long long)s.B * s.H * s.W * 3 * m.patch * m.patch * e);
+    r.x = c.take((long long)s.B * N * s.C * e);
+    r.cls_n = c.take((long long)s.B * s.C * e);
+    r.block_ws = c.take(carve_block(s, nullptr).bytes);
+    r.bytes = c.off;
+    return r;
+}
+
+}  // namespace vtp
+
+using namespace vtp;
+
+extern "C" long long vtp_block_workspace_bytes(const vtp_dge_shape* s) {
+    if (check_shape(s)) return -1;
+    return carve_block(*s, nullptr).bytes;
+}
+
+extern "C" int vtp_dge_block_forward(const vtp_dge_shape* s, const vtp_block_weights* w, const void* x_in,
+                                     void* x_out, const float* forced_logits, int32_t* counts_out,
+                                     void* workspace, long long workspace_bytes, void* stream) {
+    if (int rc = check_shape(s)) return rc;
+    VTP_REQUIRE(w && x_in && x_out && workspace, VTP_ERR_NULL, "block: null pointer");
+    VTP_REQUIRE(aligned16(workspace), VTP_ERR_ALIGN, "block: workspace must be 16-byte aligned");
+    VTP_REQUIRE(workspace_bytes >= carve_block(*s, nullptr).bytes, VTP_ERR_SHAPE,
+                "block: workspace of %lld bytes is smaller than the %lld needed", workspace_bytes,
+                carve_block(*s, nullptr).bytes);
+    return block_forward(*s, *w, x_in, x_out, forced_logits, counts_out, workspace,
+                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vtp_dge_block_forward_timed(const vtp_dge_shape* s, const vtp_block_weights* w, const void* x_in,
+                                           void* x_out, const float* forced_logits, int32_t* counts_out,
+                                           void* workspace, long long workspace_bytes, void* const* events,
+                                           int n_events, void* stream) {
+    if (int rc = check_shape(s)) return rc;
+    VTP_REQUIRE(w && x_in && x_out && workspace && events, VTP_ERR_NULL, "block: null pointer");
+    VTP_REQUIRE(aligned16(workspace), VTP_ERR_ALIGN, "block: workspace must be 16-byte aligned");
+    VTP_REQUIRE(workspace_bytes >= carve_block(*s, nullptr).bytes, VTP_ERR_SHAPE, "block: workspace too small");
+    StageMarks marks;
+    marks.events = events; marks.n = n_events; marks.st = static_cast<cudaStream_t>(stream);
+    return block_forward(*s, *w, x_in, x_out, forced_logits, counts_out, workspace, marks.st, marks);
+}
+
+extern "C" int vtp_dense_block_forward(const vtp_dge_shape* s, const vtp_block_weights* w, const void* x_in,
+                                       void* x_out, void* workspace, long long workspace_bytes, void* stream) {
+    if (int rc = check_shape(s)) return rc;
+    VTP_REQUIRE(w && x_in && x_out && workspace, VTP_ERR_NULL, "dense block: null pointer");
+    VTP_REQUIRE(x_in != x_out, VTP_ERR_UNSUPPORTED, "dense block: x_out must not alias x_in");
+    VTP_REQUIRE(workspace_bytes >= carve_block(*s, nullptr).bytes, VTP_ERR_SHAPE, "dense block: workspace too small");
+    return dense_block_forward(*s, *w, x_in, x_out, workspace, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" long long vtp_model_workspace_bytes(const vtp_dge_shape* s, const vtp_model_weights* m) {
+    if (check_shape(s) || !m) return -1;
+    return carve_model(*s, *m, nullptr).bytes;
+}
+
+extern "C" int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weights* m,
+                                    const vtp_block_weights* blocks, const float* images, float* logits,
+                                    int32_t* counts_out, void* workspace, long long workspace_bytes,
+                                    void* stream) {
+    if (int rc = check_shape(s)) return rc;
+    VTP_REQUIRE(m && blocks && images && logits && workspace, VTP_ERR_NULL, "model: null pointer");
+    VTP_REQUIRE(m->depth > 0 && m->patch > 0 && m->num_classes > 0, VTP_ERR_SHAPE, "model: bad shape");
+    VTP_REQUIRE(m->img_size == s->H * m->patch && s->H == s->W && s->num_extra == 1, VTP_ERR_SHAPE,
+                "model: image %d does not match a %dx%d grid of %d-pixel patches with one cls token",
+                m->img_size, s->H, s->W, m->patch);
+    VTP_REQUIRE(aligned16(workspace), VTP_ERR_ALIGN, "model: workspace must be 16-byte aligned");
+    const ModelScratch ms = carve_model(*s, *m, workspace);
+    VTP_REQUIRE(workspace_bytes >= ms.bytes, VTP_ERR_SHAPE, "model: workspace of %lld bytes, %lld needed",
+                workspace_bytes, ms.bytes);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int HW = s->H * s->W, N = HW + 1, C = s->C;
+    const int KP = 3 * m->patch * m->patch;
+    const long long e = (long long)elem_size(s->dtype);
+    int rc = vtp_patch_im2col(images, s->B, m->img_size, m->patch, s->dtype, ms.cols, m->cls_token, m->pos_embed,
+                              C, ms.x, st);
+    if (rc) return rc;
+    LinearArgs pe;   // token (b, 1+t) = cols(b,t) Wp^T + bias + pos_embed[1+t]
+    pe.a = ms.cols; pe.lda = KP; pe.w = m->patch_w; pe.bias = m->patch_b; pe.res = m->pos_embed; pe.ldr = C;
+    pe.y = ms.x; pe.ldy = C; pe.dtype = s->dtype; pe.m_max = s->B * HW; pe.N = C; pe.K = KP;
+    pe.flags = s->flags & VTP_FLAG_CUDA_CORES;
+    pe.out_grp = HW; pe.out_skip = 1; pe.res_mod = HW; pe.res_off = 1;
+    if ((rc = linear(pe, st))) return rc;
+    for (int i = 0; i < m->depth; ++i) {
+        rc = block_forward(*s, blocks[i], ms.x, ms.x, nullptr, counts_out ? counts_out + (size_t)i * s->B : nullptr,
+                           ms.block_ws, st);
+        if (rc) return rc;
+    }
+    rc = vtp_layernorm(ms.x, s->dtype, s->B, nullptr, C, (long long)N * C, m->norm_w, m->norm_b, s->eps, ms.cls_n, st);
+    if (rc) return rc;
+    LinearArgs hd;
+    hd.a = ms.cls_n; hd.lda = C; hd.w = m->head_w; hd.bias = m->head_b; hd.y = logits; hd.ldy = m->num_classes;
+    hd.dtype = s->dtype; hd.m_max = s->B; hd.N = m->num_classes; hd.K = C;
+    hd.flags = (s->flags & VTP_FLAG_CUDA_CORES) | VTP_FLAG_OUT_F32;
+    (void)e;
+    return linear(hd, st);
+}

@@ -1,0 +1,82 @@
+// Patch-embedding front end: im2col of the fp32 images into GEMM rows, and the cls rows.
+// The 16x16/16 convolution is then one Linear (column = c*P*P + py*P + px matches the
+// flattened conv weight [C, 3, P, P]).
+//
+// Replaces PatchEmbed, the cls-token concat and the position-embedding add of
+// VisionTransformer.forward_features (vtpack/models/dge/deit_dge.py:268-275).
+#include "common.cuh"
+
+namespace vtp {
+
+// One thread moves 8 horizontally adjacent pixels: two coalesced float4 loads, one
+// 16-byte (bf16) or two 16-byte (fp32) stores.
+template <typename T>
+__global__ void __launch_bounds__(256)
+im2col_kernel(const float* __restrict__ img, long long total8, int S, int P, T* __restrict__ cols) {
+    const int G = S / P;
+    const int KP = 3 * P * P;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total8;
+         e += (long long)gridDim.x * blockDim.x) {
+        const long long pix = e * 8;
+        const int ix = (int)(pix % S);
+        const int iy = (int)((pix / S) % S);
+        const int c = (int)((pix / ((long long)S * S)) % 3);
+        const long long b = pix / ((long long)3 * S * S);
+        const float4 v0 = __ldg(reinterpret_cast<const float4*>(img + pix));
+        const float4 v1 = __ldg(reinterpret_cast<const float4*>(img + pix) + 1);
+        const int gy = iy / P, py = iy % P, gx = ix / P, px = ix % P;
+        const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        T* dst = cols + ((b * G + gy) * G + gx) * KP + c * P * P + py * P + px;
+        if (sizeof(T) == 2) {
+            Vec<bf16> o;
+            o.from_float(f);
+            o.store(reinterpret_cast<bf16*>(dst));
+        } else {
+            reinterpret_cast<float4*>(dst)[0] = v0;
+            reinterpret_cast<float4*>(dst)[1] = v1;
+        }
+    }
+}
+
+template <typename T>
+__global__ void cls_row_kernel(const T* __restrict__ cls, const T* __restrict__ pos, int C, long long row_stride,
+                               T* __restrict__ x) {
+    const int b = blockIdx.x;
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+        x[(size_t)b * row_stride + c] = from_f32<T>(to_f32(cls[c]) + to_f32(pos[c]));
+}
+
+}  // namespace vtp
+
+using namespace vtp;
+
+extern "C" int vtp_patch_im2col(const float* images, int B, int S, int P, int dtype, void* cols,
+                                const void* cls_token, const void* pos_embed, int C, void* x, void* stream) {
+    VTP_REQUIRE(images && cols, VTP_ERR_NULL, "im2col: null pointer");
+    VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "im2col: dtype %d", dtype);
+    VTP_REQUIRE(B > 0 && S > 0 && P > 0 && S % P == 0 && P % 8 == 0, VTP_ERR_SHAPE,
+                "im2col: image %d / patch %d (patch must be a multiple of 8)", S, P);
+    VTP_REQUIRE(aligned16(images) && aligned16(cols), VTP_ERR_ALIGN, "im2col: unaligned pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long total8 = (long long)B * 3 * S * S / 8;
+    const int grid = (int)((total8 + 255) / 256 < (long long)sm_count() * 16 ? (total8 + 255) / 256
+                                                                             : (long long)sm_count() * 16);
+    if (dtype == VTP_F32)
+        im2col_kernel<float><<<grid, 256, 0, st>>>(images, total8, S, P, (float*)cols);
+    else
+        im2col_kernel<bf16><<<grid, 256, 0, st>>>(images, total8, S, P, (bf16*)cols);
+    if (int rc = check_launch("im2col")) return rc;
+    if (x) {
+        VTP_REQUIRE(cls_token && pos_embed && C > 0, VTP_ERR_NULL, "im2col: cls row needs cls_token and pos_embed");
+        const int G = S / P;
+        const long long row_stride = (long long)(G * G + 1) * C;
+        if (dtype == VTP_F32)
+            cls_row_kernel<float><<<B, 128, 0, st>>>((const float*)cls_token, (const float*)pos_embed, C,
+                                                     row_stride, (float*)x);
+        else
+            cls_row_kernel<bf16><<<B, 128, 0, st>>>((const bf16*)cls_token, (const bf16*)pos_embed, C, row_stride,
+                                                    (bf16*)x);
+        return check_launch("cls row");
+    }
+    return VTP_OK;
+}

@@ -1,0 +1,401 @@
+// HBM-bound token movers: multi-grain pooling (+ fused LayerNorms), replicate-unpool with
+// residual, and a stand-alone LayerNorm.  One warp owns one packed query row (pool/unpool)
+// or one token row (LayerNorm); lanes stride over 16-byte channel chunks so every global
+// access is a full, coalesced 16-byte vector.
+//
+// Replaces grained_sample_compress / grained_sample_decompress
+// (vtpack/layers/csrc/grained_sample/grained_sample.cu:31-69, 71-144) and the nn.LayerNorm
+// calls of Block.forward (vtpack/models/dge/deit_dge.py:127-128).
+#include "common.cuh"
+
+namespace vtp {
+
+template <typename T, int MAXCH>
+struct RowRegs {
+    static constexpr int VN = Vec<T>::N;
+    float f[MAXCH][VN];
+};
+
+// LayerNorm of one row held across the warp (two-pass: mean, then centred variance).
+template <typename T, int MAXCH>
+__device__ __forceinline__ void ln_row_store(const float (&f)[MAXCH][Vec<T>::N], int lane,
+                                             int nchunks, int C, const float (&w)[MAXCH][Vec<T>::N],
+                                             const float (&bb)[MAXCH][Vec<T>::N], float eps,
+                                             T* __restrict__ dst) {
+    constexpr int VN = Vec<T>::N;
+    float s = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch)
+        if (lane + 32 * ch < nchunks)
+#pragma unroll
+            for (int i = 0; i < VN; ++i) s += f[ch][i];
+    const float mean = warp_sum(s) / (float)C;
+    float v = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch)
+        if (lane + 32 * ch < nchunks)
+#pragma unroll
+            for (int i = 0; i < VN; ++i) { const float d = f[ch][i] - mean; v = fmaf(d, d, v); }
+    const float rstd = rsqrtf(warp_sum(v) / (float)C + eps);
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch) {
+        const int chunk = lane + 32 * ch;
+        if (chunk < nchunks) {
+            float o[VN];
+#pragma unroll
+            for (int i = 0; i < VN; ++i) o[i] = (f[ch][i] - mean) * rstd * w[ch][i] + bb[ch][i];
+            Vec<T> ov;
+            ov.from_float(o);
+            ov.store(dst + chunk * VN);
+        }
+    }
+}
+
+template <typename T, int MAXCH>
+__device__ __forceinline__ void load_vecs(float (&dst)[MAXCH][Vec<T>::N], const float* __restrict__ src,
+                                          int lane, int nchunks) {
+    constexpr int VN = Vec<T>::N;
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch) {
+        const int chunk = lane + 32 * ch;
+#pragma unroll
+        for (int i = 0; i < VN; ++i) dst[ch][i] = (chunk < nchunks) ? __ldg(src + chunk * VN + i) : 0.f;
+    }
+}
+
+// ------------------------------------------------------------------------------- pool
+// comp[p] = mean of the patch's tokens (sum in (dy,dx) order, then divide);  optionally
+// xn[b,tok] = LN(x[b,tok]) for every token read and qn[p] = LN(comp[p]).  Every token
+// belongs to exactly one patch, so x is read once.
+// Algorithmic bytes: (B*N + L)*C*e  (+ (B*N + L)*C*e when the LayerNorm outputs are on).
+template <typename T, int MAXCH, bool WITH_LN>
+__global__ void __launch_bounds__(256)
+pool_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
+            const int4* __restrict__ patches, const int32_t* __restrict__ n_dev, int n_max,
+            T* __restrict__ comp, const float* __restrict__ lnw, const float* __restrict__ lnb,
+            float eps, T* __restrict__ xn, T* __restrict__ qn) {
+    constexpr int VN = Vec<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int nchunks = C / VN;
+    int L = n_max;
+    if (n_dev) L = min(__ldg(n_dev), n_max);
+
+    float w[MAXCH][VN], bb[MAXCH][VN];
+    if (WITH_LN) {
+        load_vecs<T, MAXCH>(w, lnw, lane, nchunks);
+        load_vecs<T, MAXCH>(bb, lnb, lane, nchunks);
+    }
+
+    for (int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; p < L; p += warps) {
+        const int4 pt = __ldg(patches + p);
+        const bool extra = pt.y < 0;
+        const int step = extra ? 1 : pt.w;
+        const int tok0 = extra ? (-pt.y - 1) : (num_extra + pt.y * W + pt.z);
+        const size_t row0 = (size_t)pt.x * N + tok0;
+
+        float sum[MAXCH][VN];
+#pragma unroll
+        for (int ch = 0; ch < MAXCH; ++ch)
+#pragma unroll
+            for (int i = 0; i < VN; ++i) sum[ch][i] = 0.f;
+
+        for (int dy = 0; dy < step; ++dy) {
+            for (int dx0 = 0; dx0 < step; dx0 += 4) {
+                // up to four rows in flight before any arithmetic
+                Vec<T> raw[4][MAXCH];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (dx0 + j < step) {
+                        const T* src = x + (row0 + (size_t)dy * W + dx0 + j) * C;
+#pragma unroll
+                        for (int ch = 0; ch < MAXCH; ++ch)
+                            if (lane + 32 * ch < nchunks) raw[j][ch].load(src + (lane + 32 * ch) * VN);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (dx0 + j < step) {
+                        float f[MAXCH][VN];
+#pragma unroll
+                        for (int ch = 0; ch < MAXCH; ++ch) {
+                            if (lane + 32 * ch < nchunks) raw[j][ch].to_float(f[ch]);
+                            else
+#pragma unroll
+                                for (int i = 0; i < VN; ++i) f[ch][i] = 0.f;
+#pragma unroll
+                            for (int i = 0; i < VN; ++i) sum[ch][i] += f[ch][i];
+                        }
+                        if (WITH_LN && xn)
+                            ln_row_store<T, MAXCH>(f, lane, nchunks, C, w, bb, eps,
+                                                   xn + (row0 + (size_t)dy * W + dx0 + j) * C);
+                    }
+                }
+            }
+        }
+        const float denom = (float)(step * step);
+#pragma unroll
+        for (int ch = 0; ch < MAXCH; ++ch) {
+            const int chunk = lane + 32 * ch;
+#pragma unroll
+            for (int i = 0; i < VN; ++i) sum[ch][i] = sum[ch][i] / denom;
+            if (chunk < nchunks) {
+                Vec<T> ov;
+                ov.from_float(sum[ch]);
+                ov.store(comp + (size_t)p * C + chunk * VN);
+            }
+        }
+        if (WITH_LN && qn) ln_row_store<T, MAXCH>(sum, lane, nchunks, C, w, bb, eps, qn + (size_t)p * C);
+    }
+}
+
+// ----------------------------------------------------------------------------- unpool
+// out[b,tok] = (q[p] - comp[p]) + ref[b,tok] for every token of patch p.
+// Algorithmic bytes: (2*B*N + L)*C*e (+ L*C*e for comp).
+template <typename T, int MAXCH>
+__global__ void __launch_bounds__(256)
+unpool_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, int C, int W,
+              int num_extra, const int4* __restrict__ patches, const int32_t* __restrict__ n_dev,
+              int n_max, const T* ref, T* out) {
+    constexpr int VN = Vec<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int nchunks = C / VN;
+    int L = n_max;
+    if (n_dev) L = min(__ldg(n_dev), n_max);
+
+    for (int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; p < L; p += warps) {
+        const int4 pt = __ldg(patches + p);
+        const bool extra = pt.y < 0;
+        const int step = extra ? 1 : pt.w;
+        const int tok0 = extra ? (-pt.y - 1) : (num_extra + pt.y * W + pt.z);
+        const size_t row0 = (size_t)pt.x * N + tok0;
+
+        float d[MAXCH][VN];
+#pragma unroll
+        for (int ch = 0; ch < MAXCH; ++ch) {
+            const int chunk = lane + 32 * ch;
+            if (chunk < nchunks) {
+                Vec<T> qv;
+                qv.load(q + (size_t)p * C + chunk * VN);
+                qv.to_float(d[ch]);
+                if (comp) {
+                    Vec<T> cv;
+                    float c[VN];
+                    cv.load(comp + (size_t)p * C + chunk * VN);
+                    cv.to_float(c);
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) d[ch][i] -= c[i];
+                }
+            }
+        }
+        for (int dy = 0; dy < step; ++dy) {
+            for (int dx0 = 0; dx0 < step; dx0 += 4) {
+                Vec<T> raw[4][MAXCH];
+                if (ref) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (dx0 + j < step) {
+                            const T* src = ref + (row0 + (size_t)dy * W + dx0 + j) * C;
+#pragma unroll
+                            for (int ch = 0; ch < MAXCH; ++ch)
+                                if (lane + 32 * ch < nchunks) raw[j][ch].load(src + (lane + 32 * ch) * VN);
+                        }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (dx0 + j < step) {
+                        T* dst = out + (row0 + (size_t)dy * W + dx0 + j) * C;
+#pragma unroll
+                        for (int ch = 0; ch < MAXCH; ++ch) {
+                            const int chunk = lane + 32 * ch;
+                            if (chunk < nchunks) {
+                                float o[VN];
+                                if (ref) {
+                                    raw[j][ch].to_float(o);
+#pragma unroll
+                                    for (int i = 0; i < VN; ++i) o[i] = d[ch][i] + o[i];
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < VN; ++i) o[i] = d[ch][i];
+                                }
+                                Vec<T> ov;
+                                ov.from_float(o);
+                                ov.store(dst + chunk * VN);
+                            }
+                        }
+                    }
+            }
+        }
+    }
+}
+
+// -------------------------------------------------------------------------- layernorm
+template <typename T, int MAXCH>
+__global__ void __launch_bounds__(256)
+layernorm_kernel(const T* __restrict__ x, int rows_max, const int32_t* __restrict__ rows_dev, int C,
+                 long long in_stride, const float* __restrict__ lnw, const float* __restrict__ lnb,
+                 float eps, T* __restrict__ y) {
+    constexpr int VN = Vec<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int nchunks = C / VN;
+    int rows = rows_max;
+    if (rows_dev) rows = min(__ldg(rows_dev), rows_max);
+    float w[MAXCH][VN], bb[MAXCH][VN];
+    load_vecs<T, MAXCH>(w, lnw, lane, nchunks);
+    load_vecs<T, MAXCH>(bb, lnb, lane, nchunks);
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        float f[MAXCH][VN];
+#pragma unroll
+        for (int ch = 0; ch < MAXCH; ++ch) {
+            const int chunk = lane + 32 * ch;
+            if (chunk < nchunks) {
+                Vec<T> v;
+                v.load(x + (size_t)r * in_stride + chunk * VN);
+                v.to_float(f[ch]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VN; ++i) f[ch][i] = 0.f;
+            }
+        }
+        ln_row_store<T, MAXCH>(f, lane, nchunks, C, w, bb, eps, y + (size_t)r * C);
+    }
+}
+
+static int row_grid(int rows) {
+    const int per_block = 8;   // warps per 256-thread block
+    const int want = ceil_div(rows, per_block);
+    const int cap = sm_count() * 8;
+    return want < 1 ? 1 : (want < cap ? want : cap);
+}
+
+template <typename T>
+static int launch_pool(const void* x, int N, int C, int W, int num_extra, const int32_t* patches,
+                       const int32_t* n_dev, int n_max, void* comp, const float* lnw,
+                       const float* lnb, float eps, void* xn, void* qn, cudaStream_t st) {
+    const int maxch = ceil_div(C / Vec<T>::N, 32);
+    const int grid = row_grid(n_max);
+    const bool ln = lnw != nullptr;
+#define VTP_POOL(M)                                                                                  \
+    do {                                                                                             \
+        if (ln)                                                                                      \
+            pool_kernel<T, M, true><<<grid, 256, 0, st>>>(                                           \
+                (const T*)x, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp, lnw,  \
+                lnb, eps, (T*)xn, (T*)qn);                                                           \
+        else                                                                                         \
+            pool_kernel<T, M, false><<<grid, 256, 0, st>>>(                                          \
+                (const T*)x, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp,       \
+                nullptr, nullptr, eps, nullptr, nullptr);                                            \
+    } while (0)
+    if (maxch <= 1) VTP_POOL(1);
+    else if (maxch == 2) VTP_POOL(2);
+    else if (maxch == 3) VTP_POOL(3);
+    else if (maxch == 4) VTP_POOL(4);
+    else if (maxch <= 6) VTP_POOL(6);
+    else return fail(VTP_ERR_SHAPE, "pool: C=%d too large", C);
+#undef VTP_POOL
+    return check_launch("pool");
+}
+
+template <typename T>
+static int launch_unpool(const void* q, const void* comp, int N, int C, int W, int num_extra,
+                         const int32_t* patches, const int32_t* n_dev, int n_max, const void* ref,
+                         void* out, cudaStream_t st) {
+    const int maxch = ceil_div(C / Vec<T>::N, 32);
+    const int grid = row_grid(n_max);
+#define VTP_UNPOOL(M)                                                                           \
+    unpool_kernel<T, M><<<grid, 256, 0, st>>>((const T*)q, (const T*)comp, N, C, W, num_extra,  \
+                                              (const int4*)patches, n_dev, n_max, (const T*)ref, (T*)out)
+    if (maxch <= 1) VTP_UNPOOL(1);
+    else if (maxch == 2) VTP_UNPOOL(2);
+    else if (maxch == 3) VTP_UNPOOL(3);
+    else if (maxch == 4) VTP_UNPOOL(4);
+    else if (maxch <= 6) VTP_UNPOOL(6);
+    else return fail(VTP_ERR_SHAPE, "unpool: C=%d too large", C);
+#undef VTP_UNPOOL
+    return check_launch("unpool_add");
+}
+
+template <typename T>
+static int launch_ln(const void* x, int rows_max, const int32_t* rows_dev, int C, long long stride,
+                     const float* w, const float* b, float eps, void* y, cudaStream_t st) {
+    const int maxch = ceil_div(C / Vec<T>::N, 32);
+    const int grid = row_grid(rows_max);
+#define VTP_LN(M)                                                                                 \
+    layernorm_kernel<T, M><<<grid, 256, 0, st>>>((const T*)x, rows_max, rows_dev, C, stride, w, b, \
+                                                 eps, (T*)y)
+    if (maxch <= 1) VTP_LN(1);
+    else if (maxch == 2) VTP_LN(2);
+    else if (maxch == 3) VTP_LN(3);
+    else if (maxch == 4) VTP_LN(4);
+    else if (maxch <= 6) VTP_LN(6);
+    else return fail(VTP_ERR_SHAPE, "layernorm: C=%d too large", C);
+#undef VTP_LN
+    return check_launch("layernorm");
+}
+
+static int check_rows(const char* what, int dtype, int C, const void* a, const void* b) {
+    VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "%s: dtype %d", what, dtype);
+    VTP_REQUIRE(C > 0 && C % (16 / (int)elem_size(dtype)) == 0 && C % 4 == 0, VTP_ERR_SHAPE,
+                "%s: C=%d must be a multiple of 16 bytes", what, C);
+    VTP_REQUIRE(aligned16(a) && aligned16(b), VTP_ERR_ALIGN, "%s: unaligned pointer", what);
+    return VTP_OK;
+}
+
+}  // namespace vtp
+
+using namespace vtp;
+
+extern "C" int vtp_pool(const void* x, int dtype, int B, int N, int C, int W, int num_extra,
+                        const int32_t* patches, const int32_t* n_patches_dev, int n_patches_max,
+                        void* comp, const float* ln_w, const float* ln_b, float eps, void* xn,
+                        void* qn, void* stream) {
+    VTP_REQUIRE(x && patches && comp, VTP_ERR_NULL, "pool: null pointer");
+    VTP_REQUIRE((ln_w == nullptr) == (ln_b == nullptr), VTP_ERR_NULL, "pool: ln_w and ln_b go together");
+    VTP_REQUIRE(ln_w || (!xn && !qn), VTP_ERR_NULL, "pool: xn/qn need LayerNorm weights");
+    VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
+                "pool: bad shape");
+    if (int rc = check_rows("pool", dtype, C, x, comp)) return rc;
+    VTP_REQUIRE(aligned16(patches) && aligned16(xn) && aligned16(qn), VTP_ERR_ALIGN, "pool: unaligned pointer");
+    if (n_patches_max == 0) return VTP_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == VTP_F32)
+        return launch_pool<float>(x, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, comp,
+                                  ln_w, ln_b, eps, xn, qn, st);
+    return launch_pool<bf16>(x, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, comp, ln_w,
+                             ln_b, eps, xn, qn, st);
+}
+
+extern "C" int vtp_unpool_add(const void* q, const void* comp, int dtype, int B, int N, int C, int W,
+                              int num_extra, const int32_t* patches, const int32_t* n_patches_dev,
+                              int n_patches_max, const void* ref, void* out, void* stream) {
+    VTP_REQUIRE(q && patches && out, VTP_ERR_NULL, "unpool: null pointer");
+    VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
+                "unpool: bad shape");
+    if (int rc = check_rows("unpool", dtype, C, q, out)) return rc;
+    VTP_REQUIRE(aligned16(patches) && aligned16(comp) && aligned16(ref), VTP_ERR_ALIGN,
+                "unpool: unaligned pointer");
+    if (n_patches_max == 0) return VTP_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == VTP_F32)
+        return launch_unpool<float>(q, comp, N, C, W, num_extra, patches, n_patches_dev, n_patches_max,
+                                    ref, out, st);
+    return launch_unpool<bf16>(q, comp, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, ref,
+                               out, st);
+}
+
+extern "C" int vtp_layernorm(const void* x, int dtype, int rows_max, const int32_t* rows_dev, int C,
+                             long long in_row_stride, const float* w, const float* b, float eps,
+                             void* y, void* stream) {
+    VTP_REQUIRE(x && w && b && y, VTP_ERR_NULL, "layernorm: null pointer");
+    VTP_REQUIRE(rows_max >= 0 && in_row_stride >= C, VTP_ERR_SHAPE, "layernorm: bad shape");
+    if (int rc = check_rows("layernorm", dtype, C, x, y)) return rc;
+    VTP_REQUIRE((in_row_stride * (long long)elem_size(dtype)) % 16 == 0, VTP_ERR_ALIGN,
+                "layernorm: row stride not 16-byte aligned");
+    if (rows_max == 0) return VTP_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == VTP_F32)
+        return launch_ln<float>(x, rows_max, rows_dev, C, in_row_stride, w, b, eps, y, st);
+    return launch_ln<bf16>(x, rows_max, rows_dev, C, in_row_stride, w, b, eps, y, st);
+}

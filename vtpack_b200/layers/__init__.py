@@ -1,0 +1,13 @@
+"""Drop-in for ``vtpack.layers`` (forward / eval API), backed by libvtpack_b200.so."""
+from .dge import DynamicGrainedEncoder, DynamicRouter
+from .grained_sample import (
+    grained_sample_compress,
+    grained_sample_decompress,
+    grained_sample_index_to_patch,
+)
+from .sparse_ops import batched_sparse_attention
+
+__all__ = [
+    "DynamicGrainedEncoder", "DynamicRouter", "grained_sample_compress", "grained_sample_decompress",
+    "grained_sample_index_to_patch", "batched_sparse_attention",
+]

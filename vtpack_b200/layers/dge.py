@@ -1,0 +1,131 @@
+"""``DynamicGrainedEncoder`` / ``DynamicRouter`` with the reference's constructor,
+parameters (``splits``, ``router.gate.*``), ``states`` dict and methods
+(``vtpack/layers/dge.py:19-150``), for eval-mode inference on CUDA."""
+import ctypes
+import math
+from typing import List
+
+import torch
+from torch import nn
+
+from .. import _lib
+from ..runtime import dtype_code, ptr, require_cuda, stream_ptr
+from .grained_sample import grained_sample_compress, grained_sample_decompress, grained_sample_index_to_patch
+
+
+class DynamicRouter(nn.Module):
+    """Region average pool + Linear(C -> n_splits) (``dge.py:115-150``)."""
+
+    def __init__(self, num_channels, split_sizes, init_gate=0.95):
+        super().__init__()
+        self.num_channels = num_channels
+        self.region_size = max(split_sizes)
+        self.split_sizes = split_sizes
+        self.init_gate = init_gate
+        self.gate = nn.Linear(num_channels, len(split_sizes))
+        self.init_parameters()
+
+    def init_parameters(self):
+        nn.init.trunc_normal_(self.gate.weight, std=.01)
+        n = len(self.split_sizes)
+        if n == 1:
+            nn.init.constant_(self.gate.bias.data, 0)
+        else:
+            bias_value = math.log(math.sqrt(self.init_gate * (1 - n) / (self.init_gate - 1)))
+            self.gate.bias.data[0] = bias_value
+            self.gate.bias.data[1:] = -bias_value
+
+    def complexity(self, num_inputs, num_queries):
+        comp = num_inputs / (self.region_size ** 2) * self.num_channels
+        comp += num_inputs / (self.region_size ** 2) * self.num_channels * len(self.split_sizes)
+        return comp
+
+    def forward(self, x):
+        """x [B,H,W,C] -> gate logits fp32 [B,H/r,W/r,n_splits]."""
+        require_cuda(x)
+        x = x.contiguous()
+        B, H, W, C = x.shape
+        r = self.region_size
+        logits = torch.empty(B, H // r, W // r, len(self.split_sizes), dtype=torch.float32, device=x.device)
+        idx = torch.empty(B, H // r, W // r, dtype=torch.int32, device=x.device)
+        _lib.check(_lib.lib().vtp_router_gate(
+            ptr(x), dtype_code(x.dtype), B, H, W, C, 0, r, ptr(self.gate.weight.detach().float().contiguous()),
+            ptr(self.gate.bias.detach().float().contiguous()), len(self.split_sizes), ptr(logits), ptr(idx),
+            stream_ptr(x.device)))
+        self.last_indices = idx
+        return logits
+
+
+class DynamicGrainedEncoder(nn.Module):
+
+    def __init__(self, in_channels: int, split_sizes: List[int], complexity_handler=None,
+                 sparse_train: bool = False):
+        super().__init__()
+        self.region_size = max(split_sizes)
+        self.in_channels = in_channels
+        self.splits = nn.Parameter(torch.tensor(split_sizes), requires_grad=False)
+        self.router = DynamicRouter(in_channels, split_sizes)
+        self.complexity_handler = complexity_handler
+        self.sparse_train = sparse_train
+        self.states = {
+            "comp": None, "input": None, "patches": None, "batches": None,
+            "gate": None, "size": None, "num_extra_tokens": 0,
+        }
+
+    def get_complexity(self):
+        """MAC accounting of the last forward (``dge.py:40-59``)."""
+        if self.complexity_handler is None:
+            return {"static": None, "dynamic": None}
+        B, N, C = self.states["input"].shape
+        gate = self.states["gate"]
+        indices = gate.argmax(dim=-1, keepdim=True)
+        gate = torch.zeros_like(gate).scatter_(-1, indices, 1.0)
+        num_queries = gate * (self.splits[None, None, None, :] ** 2)
+        num_queries = num_queries.view(B, -1).double().sum(-1)
+        num_queries = num_queries + self.states["num_extra_tokens"]
+        num_inputs = num_queries.new_full([B], N, dtype=torch.double)
+        dge_cp = self.router.complexity(num_inputs, num_queries)
+        static_cp = self.complexity_handler(num_inputs, num_inputs) + dge_cp
+        dynamic_cp = self.complexity_handler(num_inputs, num_queries) + dge_cp
+        return {"static": static_cp, "dynamic": dynamic_cp}
+
+    def compress(self, x, H, W):
+        """x [B,N,C] -> packed queries [L,C] (``dge.py:61-85``, eval branch)."""
+        if self.training:
+            raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
+        require_cuda(x)
+        x = x.contiguous()
+        B, N, C = x.shape
+        num_extra_tokens = N - H * W
+        r = self.region_size
+        S = self.splits.numel()
+        gate = torch.empty(B, H // r, W // r, S, dtype=torch.float32, device=x.device)
+        indices = torch.empty(B, H // r, W // r, dtype=torch.int32, device=x.device)
+        _lib.check(_lib.lib().vtp_router_gate(
+            ptr(x), dtype_code(x.dtype), B, H, W, C, num_extra_tokens, r,
+            ptr(self.router.gate.weight.detach().float().contiguous()),
+            ptr(self.router.gate.bias.detach().float().contiguous()), S, ptr(gate), ptr(indices),
+            stream_ptr(x.device)))
+        patches, batches = grained_sample_index_to_patch(indices, self.splits, r, num_extra_tokens)
+        comp = grained_sample_compress(x, patches, H, W, num_extra_tokens)
+        self.states.update({
+            "comp": comp, "input": x, "patches": patches, "batches": batches,
+            "gate": gate, "size": (H, W), "num_extra_tokens": num_extra_tokens,
+        })
+        return comp
+
+    def decompress(self, x):
+        """packed queries [L,C] -> tokens [B,N,C]: input + replicate(x - comp) (``dge.py:87-112``)."""
+        if self.training:
+            raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
+        st = self.states
+        ref = st["input"]
+        B, N, C = ref.shape
+        H, W = st["size"]
+        x = x.contiguous()
+        p32 = st["patches"]._vtp_i32
+        out = torch.empty_like(ref)
+        _lib.check(_lib.lib().vtp_unpool_add(
+            ptr(x), ptr(st["comp"]), dtype_code(x.dtype), B, N, C, W, st["num_extra_tokens"], ptr(p32), None,
+            p32.shape[0], ptr(ref), ptr(out), stream_ptr(x.device)))
+        return out
