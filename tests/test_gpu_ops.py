@@ -206,6 +206,22 @@ def test_attention_bf16_cuda_cores(vl, B, N, h, lens):
     assert rel_err(got.float(), ref) < 8e-3
 
 
+@pytest.mark.parametrize("B,N,h,lens", [(2, 257, 3, [131, 116]), (3, 257, 6, [17, 257, 64]), (2, 1025, 2, [65, 1025]),
+                                        (1, 17, 1, [1]), (4, 257, 6, [257, 1, 128, 129]), (2, 65, 2, [65, 17])])
+def test_attention_bf16_tensor_cores(vl, B, N, h, lens):
+    _lib, layers = vl
+    q, k, v, ref = _attn_case(torch.bfloat16, B, N, h, lens, seed=B + N)
+    got = layers.batched_sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), torch.tensor(lens), 64 ** -0.5)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert rel_err(got.float(), ref) < 8e-3
+    # softmax rows far from uniform: scaled-up queries
+    q2 = (q.float() * 6).to(torch.bfloat16)
+    ref2 = O.batched_sparse_attention_forward(q2.float(), k.float(), v.float(), torch.tensor(lens), 64 ** -0.5)
+    got2 = layers.batched_sparse_attention(q2.to(DEV), k.to(DEV), v.to(DEV), torch.tensor(lens), 64 ** -0.5)
+    assert rel_err(got2.float(), ref2) < 1e-2
+
+
 def test_attention_strided_views(vl):
     """q / k / v as permuted views of Linear outputs, as the model passes them."""
     _, layers = vl
