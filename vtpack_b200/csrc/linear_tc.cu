@@ -3,13 +3,24 @@
 //
 //   y[m, n] = act(sum_k a[m,k] w[n,k] + bias[n]) + res[m, n]
 //
-// One CTA computes a 128 x BN tile.  Warp 0 (one lane) issues the TMA loads through a
-// STAGES-deep ring of shared-memory buffers, warp 1 (one lane) issues tcgen05.mma and
-// commits each stage back to the producer, then all four warps read the accumulator out of
-// TMEM (warp w owns lanes 32w..32w+31 = tile rows) and apply bias / GELU / residual.
-// Two CTAs fit on an SM (shared memory and TMEM), so one CTA's epilogue overlaps the
-// other's main loop.  The number of valid rows is read from device memory: CTAs whose row
-// tile starts beyond it exit at once, rows beyond it are never stored.
+// Persistent, warp-specialised: one CTA per SM walks 128 x BN output tiles (n fastest, so the
+// CTAs running at the same time share an A row tile in L2).
+//   warp 0   (one lane)  TMA producer: fills a STAGES-deep ring of {A 128x64, W BNx64} tiles;
+//                        the ring runs across tile boundaries, so the next tile's operands
+//                        stream in during the current tile's epilogue
+//   warp 1   (one lane)  issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
+//                        accumulators and commits each stage back to the producer
+//   warps 2-9            epilogue: read the finished accumulator with tcgen05.ld (warp w may
+//                        touch TMEM lanes 32*(w%4)..+31 = tile rows; two warps share a lane
+//                        quarter and split the columns), apply bias / GELU / residual, then
+//                        write the tile 64 columns at a time into a swizzled staging buffer
+//                        that one thread hands to a TMA store (full 128-byte lines, no partial
+//                        sectors).  The accumulator goes back to the MMA warp as soon as its
+//                        last columns are in registers.  Tiles that touch the last valid row,
+//                        row-remapped outputs and fp32 outputs store straight from registers.
+// The two accumulators let the MMA of tile i+1 overlap the epilogue of tile i.
+// The number of valid rows is read from device memory: tiles beyond it do not exist, rows
+// beyond it are never stored.
 //
 // Every mbarrier wait is bounded (see sm100.cuh); a wait that gives up ORs a code into the
 // device status word and the CTA unwinds.
@@ -26,13 +37,20 @@ using namespace sm100;
 
 constexpr int TBM = 128;   // tile rows = TMEM lanes
 constexpr int TBK = 64;    // 64 bf16 = one 128-byte swizzle row
+constexpr int TC_THREADS = 320;
 
 template <int BN, int STAGES>
 struct TcSmem {
     static constexpr int A_BYTES = TBM * TBK * 2;
     static constexpr int B_BYTES = BN * TBK * 2;
     static constexpr int RING = STAGES * (A_BYTES + B_BYTES);
-    static constexpr int TOTAL = RING + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int STAGE_OUT = 2 * TBM * 128;   // two 128-row x 64-column bf16 slabs
+    static constexpr int BIAS = 2 * BN * 4;           // the bias slice of two tiles in flight
+    static constexpr int USED = RING + STAGE_OUT + BIAS + 256 /* barriers */;
+    // Dynamic shared memory is only promised 16-byte alignment; the ring wants 1024.  In
+    // practice the base is already aligned; the kernel checks that what is left fits.
+    static constexpr int TOTAL = (USED + 1024 <= 232448) ? USED + 1024 : 232448;
+    static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
 };
 
 template <typename OutT> struct OutVec;
@@ -51,18 +69,31 @@ template <> struct OutVec<float> {
     }
 };
 
+// erf-GELU with erf from Abramowitz & Stegun 7.1.26 (|error| < 1.5e-7), cheap enough that
+// eight epilogue warps keep up with the tensor core; the result is rounded to bf16 anyway.
+__device__ __forceinline__ float gelu_fast(float x) {
+    const float z = fabsf(x) * 0.70710678118654752440f;
+    const float t = __frcp_rn(fmaf(0.3275911f, z, 1.0f));
+    float p = fmaf(1.061405429f, t, -1.453152027f);
+    p = fmaf(p, t, 1.421413741f);
+    p = fmaf(p, t, -0.284496736f);
+    p = fmaf(p, t, 0.254829592f);
+    const float erf_abs = 1.0f - p * t * __expf(-z * z);
+    return 0.5f * x * (1.0f + copysignf(erf_abs, x));
+}
+
 template <int BN, int STAGES, typename OutT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                 const float* __restrict__ bias, const bf16* __restrict__ res, long long ldr,
+                 const __grid_constant__ CUtensorMap tmap_y, int use_tma_store, const float* __restrict__ bias, const bf16* __restrict__ res, long long ldr,
                  OutT* __restrict__ y, long long ldy, int m_max, const int32_t* __restrict__ m_dev, int N,
                  int K, unsigned flags, RowMap rm, int* status) {
     using S = TcSmem<BN, STAGES>;
     int M = m_max;
     if (m_dev) M = min(__ldg(m_dev), m_max);
-    const int m0 = blockIdx.y * TBM;
-    const int n0 = blockIdx.x * BN;
-    if (m0 >= M) return;
+    const int n_tiles = (N + BN - 1) / BN;
+    const int total = ((M + TBM - 1) / TBM) * n_tiles;
+    if ((int)blockIdx.x >= total) return;
     // once any CTA has given up on a wait the launch is void: do not queue up more waits
     if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
 
@@ -70,10 +101,17 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = base;
     uint8_t* smem_b = base + STAGES * S::A_BYTES;
-    uint64_t* full = reinterpret_cast<uint64_t*>(base + S::RING);
+    if (static_cast<int>(base - smem_raw) + S::USED > S::TOTAL) {
+        if (threadIdx.x == 0 && status) atomicOr(status, STATUS_GEMM_PRODUCER);
+        return;
+    }
+    uint8_t* smem_out = base + S::RING;
+    float* bias_s = reinterpret_cast<float*>(base + S::RING + S::STAGE_OUT);
+    uint64_t* full = reinterpret_cast<uint64_t*>(base + S::RING + S::STAGE_OUT + S::BIAS);
     uint64_t* empty = full + STAGES;
-    uint64_t* accum = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    uint64_t* acc_full = empty + STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;        // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -82,12 +120,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(accum, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
         *abort_flag = 0;
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, BN);
+        tmem_alloc(tmem_slot, S::TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -95,85 +133,199 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0 && lane == 0) {
-        // ---------------------------------------------------------------- TMA producer
-        prefetch_tmap(&tmap_a);
-        prefetch_tmap(&tmap_w);
-        for (int kb = 0; kb < num_kb; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, status, STATUS_GEMM_PRODUCER)) break;
-            mbar_arrive_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
-            tma_load_2d(smem_a + s * S::A_BYTES, &tmap_a, &full[s], kb * TBK, m0);
-            tma_load_2d(smem_b + s * S::B_BYTES, &tmap_w, &full[s], kb * TBK, n0);
+    if (warp == 0) {
+        if (lane == 0) {
+            // ------------------------------------------------------------ TMA producer
+            prefetch_tmap(&tmap_a);
+            prefetch_tmap(&tmap_w);
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                const int m0 = (t / n_tiles) * TBM;
+                const int n0 = (t % n_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, status, STATUS_GEMM_PRODUCER);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
+                    tma_load_2d(smem_a + s * S::A_BYTES, &tmap_a, &full[s], kb * TBK, m0);
+                    tma_load_2d(smem_b + s * S::B_BYTES, &tmap_w, &full[s], kb * TBK, n0);
+                }
+            }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ------------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc = idesc_bf16_f32(TBM, BN, 0, 0);
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // -------------------------------------------------------------- MMA issuer
+            constexpr uint32_t idesc = idesc_bf16_f32(TBM, BN, 0, 0);
+            int it = 0, lt = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++lt) {
+                const int buf = lt & 1;
+                const uint32_t aph = (lt >> 1) & 1;
+                ok = mbar_wait(&acc_empty[buf], aph ^ 1, abort_flag, status, STATUS_GEMM_MMA);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    ok = mbar_wait(&full[s], ph, abort_flag, status, STATUS_GEMM_MMA);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint64_t adesc = smem_desc_sw128(smem_u32(smem_a + s * S::A_BYTES));
+                    const uint64_t bdesc = smem_desc_sw128(smem_u32(smem_b + s * S::B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < TBK / 16; ++k) {
+                        // 16 bf16 of K = 32 bytes = 2 descriptor address units inside the swizzle row
+                        umma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;             // which of the two warps of that quarter
+        const bool elected = threadIdx.x == 64;       // issues the TMA stores
+        const int row = quarter * 32 + lane;          // tile row = TMEM lane
+        constexpr int COLS = BN / 2;
+        constexpr int NSLAB = BN / 64;
+        int lt = 0, slab_no = 0;
         bool ok = true;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            ok = mbar_wait(&full[s], ph, abort_flag, status, STATUS_GEMM_MMA);
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++lt) {
+            const int m0 = (t / n_tiles) * TBM;
+            const int nt0 = (t % n_tiles) * BN;
+            const int buf = lt & 1;
+            const uint32_t aph = (lt >> 1) & 1;
+            const bool tma_path = use_tma_store && m0 + TBM <= M;
+            if (tma_path) {
+                // this tile's bias slice -> shared memory (one value per thread), so the column
+                // loop reads it as a broadcast instead of through the global-load path
+                const int te = threadIdx.x - 64;
+                if (te < BN) bias_s[buf * BN + te] = (bias && nt0 + te < N) ? __ldg(bias + nt0 + te) : 0.f;
+            }
+            ok = mbar_wait(&acc_full[buf], aph, abort_flag, status, STATUS_GEMM_EPILOGUE);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint64_t adesc = smem_desc_sw128(smem_u32(smem_a + s * S::A_BYTES));
-            const uint64_t bdesc = smem_desc_sw128(smem_u32(smem_b + s * S::B_BYTES));
-#pragma unroll
-            for (int k = 0; k < TBK / 16; ++k) {
-                // 16 bf16 of K = 32 bytes = 2 descriptor address units inside the swizzle row
-                umma_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-            }
-            umma_commit(&empty[s]);
-        }
-        if (ok) umma_commit(accum);
-    }
-    __syncwarp();
-
-    // ------------------------------------------------------------------------ epilogue
-    const bool have_acc = mbar_wait(accum, 0, abort_flag, status, STATUS_GEMM_EPILOGUE);
-    tc_fence_after_sync();
-    if (have_acc) {
-        const int m = m0 + warp * 32 + lane;
-        const bool row_ok = m < M;
-        const long long orow = map_out_row(rm, row_ok ? m : m0);
-        const long long rrow = map_res_row(rm, row_ok ? m : m0);
-        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+            const int m = m0 + row;
+            const bool row_ok = m < M;
+            const long long orow = map_out_row(rm, row_ok ? m : m0);
+            const long long rrow = map_res_row(rm, row_ok ? m : m0);
+            const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            if (tma_path) {
+                // ---- full tile: registers -> swizzled staging slab -> TMA store
+                named_barrier(1, 256);                       // bias slice complete
+                uint32_t r[32];
+                __syncwarp();
+                tmem_ld_32x32(tacc + half * 32, r);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t r[32];
-            __syncwarp();                 // tcgen05.ld is warp-collective
-            tmem_ld_32x32(lane_base + c0, r);
-            tmem_ld_wait();
+                for (int sl = 0; sl < NSLAB; ++sl, ++slab_no) {
+                    tmem_ld_wait();
+                    float v[32];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int n = n0 + c0 + 8 * j;
-                if (n >= N || !row_ok) continue;
-                float v[8];
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    if (sl + 1 < NSLAB) {
+                        __syncwarp();
+                        tmem_ld_32x32(tacc + (sl + 1) * 64 + half * 32, r);     // next slab in flight
+                    } else {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[buf]);            // accumulator is free
+                    }
+                    const int n = nt0 + sl * 64 + half * 32;                    // first of this thread's 32 columns
+                    uint8_t* srow = smem_out + (slab_no & 1) * (TBM * 128) + row * 128;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * j + i]);
-                if (bias) {
-                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + n));
-                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + n) + 1);
-                    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                    v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                    for (int j = 0; j < 4; ++j) {
+                        float* vj = v + 8 * j;
+                        const int nj = n + 8 * j;
+                        if (nj < N) {
+                            {
+                                const float4* bs = reinterpret_cast<const float4*>(bias_s + buf * BN + sl * 64 + half * 32 + 8 * j);
+                                const float4 b0 = bs[0];
+                                const float4 b1 = bs[1];
+                                vj[0] += b0.x; vj[1] += b0.y; vj[2] += b0.z; vj[3] += b0.w;
+                                vj[4] += b1.x; vj[5] += b1.y; vj[6] += b1.z; vj[7] += b1.w;
+                            }
+                            if (flags & VTP_FLAG_GELU) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) vj[i] = gelu_fast(vj[i]);
+                            }
+                            if (res) {
+                                Vec<bf16> rv;
+                                float rf[8];
+                                rv.load(res + rrow * ldr + nj);
+                                rv.to_float(rf);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) vj[i] += rf[i];
+                            }
+                        }
+                        Vec<bf16> ov;
+                        ov.from_float(vj);
+                        const int chunk = half * 4 + j;                          // 16-byte chunk within the 128-byte row
+                        *reinterpret_cast<uint4*>(srow + ((chunk ^ (row & 7)) << 4)) = ov.raw;
+                    }
+                    fence_proxy_async_smem();
+                    if (elected) bulk_wait_group_read0();      // the other slab buffer is free again
+                    named_barrier(1, 256);
+                    if (elected) {
+                        tma_store_2d(&tmap_y, smem_out + (slab_no & 1) * (TBM * 128), nt0 + sl * 64, m0);
+                        bulk_commit_group();
+                    }
                 }
-                if (flags & VTP_FLAG_GELU) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = gelu_erf(v[i]);
+                continue;
+            }
+            // ---- boundary tile / row-remapped / fp32 output: store straight from registers
+            const int n0 = nt0 + half * COLS;
+            const uint32_t taddr = tacc + half * COLS;
+#pragma unroll 1
+            for (int c0 = 0; c0 < COLS; c0 += 32) {
+                uint32_t r[32];
+                __syncwarp();                 // tcgen05.ld is warp-collective
+                tmem_ld_32x32(taddr + c0, r);
+                tmem_ld_wait();
+                if (c0 + 32 >= COLS) {
+                    // every column of this warp's slice is in registers: release the accumulator
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
                 }
-                if (res) {
-                    Vec<bf16> rv;
-                    float rf[8];
-                    rv.load(res + rrow * ldr + n);
-                    rv.to_float(rf);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] += rf[i];
+                for (int j = 0; j < 4; ++j) {
+                    const int n = n0 + c0 + 8 * j;
+                    if (n >= N || !row_ok) continue;
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * j + i]);
+                    if (bias) {
+                        const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + n));
+                        const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + n) + 1);
+                        v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                        v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                    }
+                    if (flags & VTP_FLAG_GELU) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] = gelu_fast(v[i]);
+                    }
+                    if (res) {
+                        Vec<bf16> rv;
+                        float rf[8];
+                        rv.load(res + rrow * ldr + n);
+                        rv.to_float(rf);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] += rf[i];
+                    }
+                    OutVec<OutT>::store8(y + orow * ldy + n, v);
                 }
-                OutVec<OutT>::store8(y + orow * ldy + n, v);
             }
         }
-    } else {
+        if (elected) bulk_wait_group0();      // every TMA store has landed before the CTA retires
+    }
+    if (*abort_flag) {
         // Unwinding after a wait gave up: give copies still in flight time to land before
         // shared memory and TMEM are released.
         const long long t0 = clock64();
@@ -181,7 +333,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, BN);
+    if (warp == 1) tmem_dealloc(tmem_base, S::TMEM_COLS);
 }
 
 // ------------------------------------------------------------------------------ host
@@ -237,6 +389,15 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
         const unsigned box[2] = {TBK, BN};
         if (int rc = make_tmap_bf16(&tw, p.w, 2, dims, strides, box)) return rc;
     }
+    // Output map for the TMA-store epilogue (bf16 output, rows not remapped).
+    const int use_tma_store = (sizeof(OutT) == 2 && p.out_grp == 0) ? 1 : 0;
+    CUtensorMap ty = tw;
+    if (use_tma_store) {
+        const unsigned long long dims[2] = {(unsigned long long)p.N, (unsigned long long)p.m_max};
+        const unsigned long long strides[1] = {(unsigned long long)p.ldy * 2ull};
+        const unsigned box[2] = {64, TBM};
+        if (int rc = make_tmap_bf16(&ty, p.y, 2, dims, strides, box)) return rc;
+    }
     auto kern = linear_tc_kernel<BN, STAGES, OutT>;
     static bool attr_set[64] = {};   // per instantiation and device
     int dev = 0;
@@ -250,9 +411,10 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
         }
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    const dim3 grid(ceil_div(p.N, BN), ceil_div(p.m_max, TBM));
+    const long long tiles = (long long)ceil_div(p.N, BN) * ceil_div(p.m_max, TBM);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const RowMap rm{p.out_grp, p.out_skip, p.res_mod, p.res_off};
-    kern<<<grid, 128, S::TOTAL, st>>>(ta, tw, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
+    kern<<<grid, TC_THREADS, S::TOTAL, st>>>(ta, tw, ty, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
                                       p.m_dev, p.N, p.K, p.flags, rm, device_status_ptr());
     return check_launch("linear (tcgen05)");
 }
@@ -264,8 +426,15 @@ int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
     VTP_REQUIRE(p.N % 8 == 0, VTP_ERR_SHAPE, "linear (tcgen05): N=%d must be a multiple of 8", p.N);
     VTP_REQUIRE(p.lda % 8 == 0 && p.ldy % 8 == 0 && (!p.res || p.ldr % 8 == 0), VTP_ERR_ALIGN,
                 "linear (tcgen05): row strides must be multiples of 16 bytes");
-    if (p.flags & VTP_FLAG_OUT_F32) return launch_tc<128, 3, float>(p, st);
-    return launch_tc<128, 3, bf16>(p, st);
+    // widest tile that does not pad N more than a narrower one would
+    auto padded = [&](int bn) { return ceil_div(p.N, bn) * bn; };
+    int bn = 256;
+    if (padded(192) < padded(bn)) bn = 192;
+    if (padded(128) < padded(bn)) bn = 128;
+    const bool f32 = (p.flags & VTP_FLAG_OUT_F32) != 0;
+    if (bn == 256) return f32 ? launch_tc<256, 4, float>(p, st) : launch_tc<256, 4, bf16>(p, st);
+    if (bn == 192) return f32 ? launch_tc<192, 4, float>(p, st) : launch_tc<192, 4, bf16>(p, st);
+    return f32 ? launch_tc<128, 5, float>(p, st) : launch_tc<128, 5, bf16>(p, st);
 }
 
 }  // namespace vtp
