@@ -10,8 +10,8 @@
 //                        stream in during the current tile's epilogue
 //   warp 1   (one lane)  issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
 //                        accumulators and commits each stage back to the producer
-//   warps 2-9            epilogue: read the finished accumulator with tcgen05.ld (warp w may
-//                        touch TMEM lanes 32*(w%4)..+31 = tile rows; two warps share a lane
+//   warps 2-17           epilogue: read the finished accumulator with tcgen05.ld (warp w may
+//                        touch TMEM lanes 32*(w%4)..+31 = tile rows; four warps share a lane
 //                        quarter and split the columns), apply bias / GELU / residual, then
 //                        write the tile 64 columns at a time into a swizzled staging buffer
 //                        that one thread hands to a TMA store (full 128-byte lines, no partial
@@ -37,7 +37,8 @@ using namespace sm100;
 
 constexpr int TBM = 128;   // tile rows = TMEM lanes
 constexpr int TBK = 64;    // 64 bf16 = one 128-byte swizzle row
-constexpr int TC_THREADS = 320;
+constexpr int EPI_THREADS = 512;  // 16 epilogue warps, four per TMEM lane quarter
+constexpr int TC_THREADS = 64 + EPI_THREADS;
 
 template <int BN, int STAGES>
 struct TcSmem {
@@ -45,11 +46,12 @@ struct TcSmem {
     static constexpr int B_BYTES = BN * TBK * 2;
     static constexpr int RING = STAGES * (A_BYTES + B_BYTES);
     static constexpr int STAGE_OUT = 2 * TBM * 128;   // two 128-row x 64-column bf16 slabs
-    static constexpr int BIAS = 2 * BN * 4;           // the bias slice of two tiles in flight
+    static constexpr int BIAS = BN * 4;               // the bias slice of the tile in the epilogue
     static constexpr int USED = RING + STAGE_OUT + BIAS + 256 /* barriers */;
     // Dynamic shared memory is only promised 16-byte alignment; the ring wants 1024.  In
     // practice the base is already aligned; the kernel checks that what is left fits.
     static constexpr int TOTAL = (USED + 1024 <= 232448) ? USED + 1024 : 232448;
+    static_assert(USED <= 232448, "shared memory budget");
     static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
 };
 
@@ -69,23 +71,25 @@ template <> struct OutVec<float> {
     }
 };
 
-// erf-GELU with erf from Abramowitz & Stegun 7.1.26 (|error| < 1.5e-7), cheap enough that
-// eight epilogue warps keep up with the tensor core; the result is rounded to bf16 anyway.
+// erf-GELU as x * sigmoid(x * (c0 + c1 x^2 + c2 x^4)), coefficients fitted to
+// 0.5 x (1 + erf(x / sqrt 2)) on [-8, 8]: max abs error 2.6e-5, far below the bf16 rounding
+// of the result.  Ten instructions, so sixteen epilogue warps keep up with the tensor core.
 __device__ __forceinline__ float gelu_fast(float x) {
-    const float z = fabsf(x) * 0.70710678118654752440f;
-    const float t = __frcp_rn(fmaf(0.3275911f, z, 1.0f));
-    float p = fmaf(1.061405429f, t, -1.453152027f);
-    p = fmaf(p, t, 1.421413741f);
-    p = fmaf(p, t, -0.284496736f);
-    p = fmaf(p, t, 0.254829592f);
-    const float erf_abs = 1.0f - p * t * __expf(-z * z);
-    return 0.5f * x * (1.0f + copysignf(erf_abs, x));
+    const float xc = fminf(fmaxf(x, -8.f), 8.f);
+    const float u = xc * xc;
+    // -log2(e) * (c0 + c1 u + c2 u^2)
+    const float p = fmaf(fmaf(1.01426515e-3f, u, -1.06775736e-1f), u, -2.30112135f);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(xc * p));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return x * r;
 }
 
 template <int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                 const __grid_constant__ CUtensorMap tmap_y, int use_tma_store, const float* __restrict__ bias, const bf16* __restrict__ res, long long ldr,
+                 const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_r,
+                 int use_tma_store, const float* __restrict__ bias, const bf16* __restrict__ res, long long ldr,
                  OutT* __restrict__ y, long long ldy, int m_max, const int32_t* __restrict__ m_dev, int N,
                  int K, unsigned flags, RowMap rm, int* status) {
     using S = TcSmem<BN, STAGES>;
@@ -111,7 +115,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;       // [2]
     uint64_t* acc_empty = acc_full + 2;        // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* res_full = acc_empty + 2;        // [2] residual slab landed in the staging buffer
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_full + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -120,7 +125,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], EPI_THREADS / 32);
+            mbar_init(&res_full[b], 1);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -190,12 +199,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else {
         // ------------------------------------------------------------------- epilogue
         const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
-        const int half = (warp - 2) >> 2;             // which of the two warps of that quarter
-        const bool elected = threadIdx.x == 64;       // issues the TMA stores
+        const int qsub = (warp - 2) >> 2;             // which of the four warps of that quarter
+        const bool elected = threadIdx.x == 64;       // issues the TMA stores / residual loads
         const int row = quarter * 32 + lane;          // tile row = TMEM lane
-        constexpr int COLS = BN / 2;
+        constexpr int COLS = BN / 4;                  // columns per warp in the register path
         constexpr int NSLAB = BN / 64;
         int lt = 0, slab_no = 0;
+        int res_issued = -1;                          // elected thread: last slab whose residual load was issued
         bool ok = true;
         for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++lt) {
             const int m0 = (t / n_tiles) * TBM;
@@ -207,95 +217,115 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 // this tile's bias slice -> shared memory (one value per thread), so the column
                 // loop reads it as a broadcast instead of through the global-load path
                 const int te = threadIdx.x - 64;
-                if (te < BN) bias_s[buf * BN + te] = (bias && nt0 + te < N) ? __ldg(bias + nt0 + te) : 0.f;
+                if (te < BN) bias_s[te] = (bias && nt0 + te < N) ? __ldg(bias + nt0 + te) : 0.f;
+                if (res && elected && res_issued < slab_no) {
+                    // first slab of a run of TMA tiles: nobody prefetched its residual
+                    bulk_wait_group_read0();
+                    mbar_arrive_expect_tx(&res_full[slab_no & 1], TBM * 128);
+                    tma_load_2d(smem_out + (slab_no & 1) * (TBM * 128), &tmap_r, &res_full[slab_no & 1], nt0, m0);
+                    res_issued = slab_no;
+                }
             }
             ok = mbar_wait(&acc_full[buf], aph, abort_flag, status, STATUS_GEMM_EPILOGUE);
             if (!ok) break;
             tc_fence_after_sync();
-            const int m = m0 + row;
-            const bool row_ok = m < M;
-            const long long orow = map_out_row(rm, row_ok ? m : m0);
-            const long long rrow = map_res_row(rm, row_ok ? m : m0);
             const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             if (tma_path) {
                 // ---- full tile: registers -> swizzled staging slab -> TMA store
-                named_barrier(1, 256);                       // bias slice complete
-                uint32_t r[32];
+                named_barrier(1, EPI_THREADS);                       // bias slice complete
+                uint32_t r[16];
                 __syncwarp();
-                tmem_ld_32x32(tacc + half * 32, r);
+                tmem_ld_32x16(tacc + qsub * 16, r);
 #pragma unroll 1
                 for (int sl = 0; sl < NSLAB; ++sl, ++slab_no) {
                     tmem_ld_wait();
-                    float v[32];
+                    float v[16];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
                     if (sl + 1 < NSLAB) {
                         __syncwarp();
-                        tmem_ld_32x32(tacc + (sl + 1) * 64 + half * 32, r);     // next slab in flight
+                        tmem_ld_32x16(tacc + (sl + 1) * 64 + qsub * 16, r);     // next slab in flight
                     } else {
                         tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&acc_empty[buf]);            // accumulator is free
                     }
-                    const int n = nt0 + sl * 64 + half * 32;                    // first of this thread's 32 columns
                     uint8_t* srow = smem_out + (slab_no & 1) * (TBM * 128) + row * 128;
+                    if (res) {
+                        ok = mbar_wait(&res_full[slab_no & 1], (slab_no >> 1) & 1, abort_flag, status,
+                                       STATUS_GEMM_EPILOGUE);
+                        if (!ok) break;
+                    }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int j = 0; j < 2; ++j) {
                         float* vj = v + 8 * j;
-                        const int nj = n + 8 * j;
-                        if (nj < N) {
-                            {
-                                const float4* bs = reinterpret_cast<const float4*>(bias_s + buf * BN + sl * 64 + half * 32 + 8 * j);
-                                const float4 b0 = bs[0];
-                                const float4 b1 = bs[1];
-                                vj[0] += b0.x; vj[1] += b0.y; vj[2] += b0.z; vj[3] += b0.w;
-                                vj[4] += b1.x; vj[5] += b1.y; vj[6] += b1.z; vj[7] += b1.w;
-                            }
-                            if (flags & VTP_FLAG_GELU) {
+                        const int chunk = qsub * 2 + j;                          // 16-byte chunk within the 128-byte row
+                        uint4* cell = reinterpret_cast<uint4*>(srow + ((chunk ^ (row & 7)) << 4));
+                        const float4* bs = reinterpret_cast<const float4*>(bias_s + sl * 64 + chunk * 8);
+                        const float4 b0 = bs[0];
+                        const float4 b1 = bs[1];
+                        vj[0] += b0.x; vj[1] += b0.y; vj[2] += b0.z; vj[3] += b0.w;
+                        vj[4] += b1.x; vj[5] += b1.y; vj[6] += b1.z; vj[7] += b1.w;
+                        if (flags & VTP_FLAG_GELU) {
 #pragma unroll
-                                for (int i = 0; i < 8; ++i) vj[i] = gelu_fast(vj[i]);
-                            }
-                            if (res) {
-                                Vec<bf16> rv;
-                                float rf[8];
-                                rv.load(res + rrow * ldr + nj);
-                                rv.to_float(rf);
+                            for (int i = 0; i < 8; ++i) vj[i] = gelu_fast(vj[i]);
+                        }
+                        if (res) {
+                            Vec<bf16> rv;
+                            float rf[8];
+                            rv.raw = *cell;                                      // residual slab, same layout
+                            rv.to_float(rf);
 #pragma unroll
-                                for (int i = 0; i < 8; ++i) vj[i] += rf[i];
-                            }
+                            for (int i = 0; i < 8; ++i) vj[i] += rf[i];
                         }
                         Vec<bf16> ov;
                         ov.from_float(vj);
-                        const int chunk = half * 4 + j;                          // 16-byte chunk within the 128-byte row
-                        *reinterpret_cast<uint4*>(srow + ((chunk ^ (row & 7)) << 4)) = ov.raw;
+                        *cell = ov.raw;
                     }
                     fence_proxy_async_smem();
                     if (elected) bulk_wait_group_read0();      // the other slab buffer is free again
-                    named_barrier(1, 256);
+                    named_barrier(1, EPI_THREADS);
                     if (elected) {
                         tma_store_2d(&tmap_y, smem_out + (slab_no & 1) * (TBM * 128), nt0 + sl * 64, m0);
                         bulk_commit_group();
+                        if (res) {
+                            // prefetch the residual of the next slab into the buffer that just became free
+                            int nsl = sl + 1, nt = t;
+                            if (nsl == NSLAB) { nsl = 0; nt = t + gridDim.x; }
+                            const int nm0 = (nt / n_tiles) * TBM;
+                            if (nt < total && nm0 + TBM <= M) {
+                                const int nb = (slab_no + 1) & 1;
+                                mbar_arrive_expect_tx(&res_full[nb], TBM * 128);
+                                tma_load_2d(smem_out + nb * (TBM * 128), &tmap_r, &res_full[nb],
+                                            (nt % n_tiles) * BN + nsl * 64, nm0);
+                                res_issued = slab_no + 1;
+                            }
+                        }
                     }
                 }
                 continue;
             }
             // ---- boundary tile / row-remapped / fp32 output: store straight from registers
-            const int n0 = nt0 + half * COLS;
-            const uint32_t taddr = tacc + half * COLS;
+            const int m = m0 + row;
+            const bool row_ok = m < M;
+            const long long orow = map_out_row(rm, row_ok ? m : m0);
+            const long long rrow = map_res_row(rm, row_ok ? m : m0);
+            const int n0 = nt0 + qsub * COLS;
+            const uint32_t taddr = tacc + qsub * COLS;
 #pragma unroll 1
-            for (int c0 = 0; c0 < COLS; c0 += 32) {
-                uint32_t r[32];
+            for (int c0 = 0; c0 < COLS; c0 += 16) {
+                uint32_t r[16];
                 __syncwarp();                 // tcgen05.ld is warp-collective
-                tmem_ld_32x32(taddr + c0, r);
+                tmem_ld_32x16(taddr + c0, r);
                 tmem_ld_wait();
-                if (c0 + 32 >= COLS) {
+                if (c0 + 16 >= COLS) {
                     // every column of this warp's slice is in registers: release the accumulator
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&acc_empty[buf]);
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < 2; ++j) {
                     const int n = n0 + c0 + 8 * j;
                     if (n >= N || !row_ok) continue;
                     float v[8];
@@ -391,12 +421,16 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
     }
     // Output map for the TMA-store epilogue (bf16 output, rows not remapped).
     const int use_tma_store = (sizeof(OutT) == 2 && p.out_grp == 0) ? 1 : 0;
-    CUtensorMap ty = tw;
+    CUtensorMap ty = tw, tr = tw;
     if (use_tma_store) {
         const unsigned long long dims[2] = {(unsigned long long)p.N, (unsigned long long)p.m_max};
         const unsigned long long strides[1] = {(unsigned long long)p.ldy * 2ull};
         const unsigned box[2] = {64, TBM};
         if (int rc = make_tmap_bf16(&ty, p.y, 2, dims, strides, box)) return rc;
+        if (p.res) {
+            const unsigned long long rstrides[1] = {(unsigned long long)p.ldr * 2ull};
+            if (int rc = make_tmap_bf16(&tr, p.res, 2, dims, rstrides, box)) return rc;
+        }
     }
     auto kern = linear_tc_kernel<BN, STAGES, OutT>;
     static bool attr_set[64] = {};   // per instantiation and device
@@ -414,7 +448,7 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
     const long long tiles = (long long)ceil_div(p.N, BN) * ceil_div(p.m_max, TBM);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const RowMap rm{p.out_grp, p.out_skip, p.res_mod, p.res_off};
-    kern<<<grid, TC_THREADS, S::TOTAL, st>>>(ta, tw, ty, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
+    kern<<<grid, TC_THREADS, S::TOTAL, st>>>(ta, tw, ty, tr, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
                                       p.m_dev, p.N, p.K, p.flags, rm, device_status_ptr());
     return check_launch("linear (tcgen05)");
 }
