@@ -134,6 +134,18 @@ int vtp_linear(const void* a, long long lda, const void* w, const float* bias,
                int m_max, const int32_t* m_dev, int N, int K, unsigned flags, void* stream);
 
 /*
+ * Weight preparation for a Linear that follows a LayerNorm (run once per model):
+ *   w_out[n,k] = W[n,k]*gamma[k] (rounded to dtype), s[n] = sum_k w_out[n,k],
+ *   c[n] = sum_k beta[k]*W[n,k] + bias[n]   (bias may be null).
+ * Then LN(x) W^T + b = rstd*(x w_out^T - mean*s) + c, which is what the block forward
+ * evaluates when vtp_block_weights carries the folded fields.  The reference keeps
+ * nn.LayerNorm and nn.Linear separate (vtpack/models/dge/deit_dge.py:127-128).
+ */
+int vtp_fold_layernorm(const void* w, int dtype, int N, int K, const float* gamma,
+                       const float* beta, const float* bias, void* w_out, float* s_out,
+                       float* c_out, void* stream);
+
+/*
  * Variable-length-query attention: for image i, head h,
  *   out[rows of i] = softmax(scale * Q_i K_i^T) V_i   over all n_keys keys.
  * q/out rows are the packed queries (offsets[i] .. offsets[i+1]); strides are in
@@ -174,6 +186,14 @@ typedef struct {
     const void* fc1_w; const float* fc1_b;      /* mlp.fc1   [hidden, C] */
     const void* fc2_w; const float* fc2_b;      /* mlp.fc2   [C, hidden] */
     const float* gate_w; const float* gate_b;   /* dge.router.gate [n_splits, C] fp32 */
+    /* Optional (bf16 tensor-core path): the three Linears that follow a LayerNorm with the
+     * LayerNorm folded in by vtp_fold_layernorm (norm1 -> q, norm1 -> kv, norm2 -> fc1).
+     * *_wf = W*diag(gamma) in the model dtype, *_s / *_c fp32 [out features].  When all nine
+     * are set the block never materialises normalised rows: its GEMMs read raw rows and apply
+     * rstd*(acc - mean*s) + c in their epilogues.  Leave null to run explicit LayerNorms. */
+    const void* q_wf; const float* q_s; const float* q_c;
+    const void* kv_wf; const float* kv_s; const float* kv_c;
+    const void* fc1_wf; const float* fc1_s; const float* fc1_c;
 } vtp_block_weights;
 
 /* Shapes shared by the block and model entry points. */

@@ -89,15 +89,21 @@ def test_layer_512px_skewed_fp32():
     assert rel_err(out, ref) < 1e-4
 
 
-@pytest.mark.parametrize("cuda_cores", [True, False])
-def test_layer_bf16_vs_fp32_oracle(cuda_cores):
-    """bf16 device path vs fp32 math on the bf16-rounded weights and input."""
+@pytest.mark.parametrize("cuda_cores,fold", [(True, False), (False, False), (False, True)])
+def test_layer_bf16_vs_fp32_oracle(cuda_cores, fold):
+    """bf16 device path vs fp32 math on the bf16-rounded weights and input; with the
+    tcgen05 kernels both with explicit LayerNorms and with LayerNorm folded into the GEMMs."""
     from vtpack_b200 import _lib
     sd = O.round_bf16(O.make_state_dict(384, 1, 6, seed=12))
-    x = O.make_tokens(4, 257, 384, seed=13).bfloat16().float()
+    g = torch.Generator().manual_seed(15)
+    for k in ("norm1", "norm2"):     # non-trivial LayerNorm affine so that folding is exercised
+        sd[f"blocks.0.{k}.weight"] = (1 + 0.2 * torch.randn(384, generator=g)).bfloat16().float()
+        sd[f"blocks.0.{k}.bias"] = (0.2 * torch.randn(384, generator=g)).bfloat16().float()
+    x = (O.make_tokens(4, 257, 384, seed=13) + 0.5).bfloat16().float()
     gate = O.make_gate_logits(4, 4, 4, 3, seed=14)
     ref = O.dge_block_forward(x, O.block_weights(sd, 0), 6, (4, 2, 1), forced_gate=gate)
     blk = _block(384, 6, sd, torch.bfloat16)
+    blk.fold_layernorm = fold
     blk.flags = _lib.FLAG_CUDA_CORES if cuda_cores else 0
     out = blk(x.bfloat16().to(DEV), forced_gate=gate)
     assert _lib.device_status() == 0

@@ -18,7 +18,8 @@ c_void_p, c_int, c_ll, c_float, c_uint = C.c_void_p, C.c_int, C.c_longlong, C.c_
 class BlockWeights(C.Structure):
     _fields_ = [(n, c_void_p) for n in (
         "norm1_w", "norm1_b", "q_w", "q_b", "kv_w", "kv_b", "proj_w", "proj_b",
-        "norm2_w", "norm2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b", "gate_w", "gate_b")]
+        "norm2_w", "norm2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b", "gate_w", "gate_b",
+        "q_wf", "q_s", "q_c", "kv_wf", "kv_s", "kv_c", "fc1_wf", "fc1_s", "fc1_c")]
 
 
 class DgeShape(C.Structure):
@@ -52,6 +53,8 @@ PROTOTYPES = {
                               c_void_p, c_void_p]),
     "vtp_linear": (c_int, [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_ll, c_int,
                            c_int, c_void_p, c_int, c_int, c_uint, c_void_p]),
+    "vtp_fold_layernorm": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_void_p]),
     "vtp_sparse_attention": (c_int, [c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_void_p,
                                      c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                      c_int, c_float, c_uint, c_void_p]),

@@ -7,6 +7,7 @@
 // Block.forward of vtpack/models/standard/deit.py:79-83.
 #include "attention.h"
 #include "linear.h"
+#include "region_ops.h"
 
 namespace vtp {
 
@@ -22,8 +23,9 @@ struct Carver {
 };
 
 struct BlockScratch {
-    int32_t *idx, *counts, *offsets, *patches;
+    int32_t *idx, *counts, *offsets, *patches, *region_first;
     float* logits;
+    float2 *stats_x, *stats_q, *stats_acc;
     void *comp, *xn, *qn, *qp, *kv, *ao, *q1, *hid;
     long long bytes;
 };
@@ -39,7 +41,11 @@ static BlockScratch carve_block(const vtp_dge_shape& s, void* ws) {
     b.counts = (int32_t*)c.take((long long)s.B * 4);
     b.offsets = (int32_t*)c.take((long long)(s.B + 1) * 4);
     b.patches = (int32_t*)c.take(rows * 16);
+    b.region_first = (int32_t*)c.take((long long)s.B * R * 4);
     b.logits = (float*)c.take((long long)s.B * R * s.n_splits * 4);
+    b.stats_x = (float2*)c.take(rows * 8);
+    b.stats_q = (float2*)c.take(rows * 8);
+    b.stats_acc = (float2*)c.take(rows * 8);
     b.comp = c.take(rows * s.C * e);
     b.xn = c.take(rows * s.C * e);
     b.qn = c.take(rows * s.C * e);
@@ -90,31 +96,58 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     int rc;
     if ((rc = marks.mark(0))) return rc;
 
-    if (forced_logits)
+    Splits sp;
+    if ((rc = make_splits(&sp, s.splits, s.n_splits, s.region))) return rc;
+    RegionGeom g;
+    g.B = s.B; g.Hr = Hr; g.Wr = Wr; g.W = s.W; g.N = N; g.C = C; g.num_extra = s.num_extra; g.region = s.region;
+    // Region-parallel gate / pool / unpool when the region is 4x4 tokens, else one warp per patch.
+    const bool by_region = region_ops_supported(g, s.dtype);
+    // LayerNorm folded into the q / kv / fc1 GEMM epilogues (bf16 tensor-core path with prepared weights).
+    const bool fold = by_region && s.dtype == VTP_BF16 && !kflag && w.q_wf && w.q_s && w.q_c && w.kv_wf && w.kv_s &&
+                      w.kv_c && w.fc1_wf && w.fc1_s && w.fc1_c;
+
+    if (forced_logits) {
         rc = vtp_gate_argmax(forced_logits, s.B * Hr * Wr, s.n_splits, b.idx, st);
-    else
+    } else if (by_region) {
+        RegionGateArgs ga;
+        ga.g = g; ga.x = x_in; ga.gw = w.gate_w; ga.gb = w.gate_b; ga.S = s.n_splits; ga.logits_out = b.logits;
+        ga.idx_out = b.idx;
+        rc = region_gate(ga, s.dtype, st);
+    } else {
         rc = vtp_router_gate(x_in, s.dtype, s.B, s.H, s.W, C, s.num_extra, s.region, w.gate_w, w.gate_b,
                              s.n_splits, b.logits, b.idx, st);
+    }
     if (rc || (rc = marks.mark(1))) return rc;
-    rc = vtp_index_to_patch(b.idx, 0, s.splits, s.n_splits, s.B, Hr, Wr, s.region, s.num_extra, b.counts,
-                            b.offsets, b.patches, nullptr, st);
+    rc = index_to_patch(b.idx, 0, sp, s.B, Hr, Wr, s.region, s.num_extra, b.counts, b.offsets,
+                        by_region ? nullptr : b.patches, nullptr, b.region_first, st);
     if (rc || (rc = marks.mark(2))) return rc;
     if (counts_out) {
         const cudaError_t e = cudaMemcpyAsync(counts_out, b.counts, (size_t)s.B * 4, cudaMemcpyDeviceToDevice, st);
         if (e != cudaSuccess) return fail((int)e, "block: counts copy: %s", cudaGetErrorString(e));
     }
-    rc = vtp_pool(x_in, s.dtype, s.B, N, C, s.W, s.num_extra, b.patches, L_dev, rows, b.comp, w.norm1_w,
-                  w.norm1_b, s.eps, b.xn, b.qn, st);
+    if (by_region) {
+        RegionPoolArgs pa;
+        pa.g = g; pa.sp = sp; pa.x = x_in; pa.idx = b.idx; pa.region_first = b.region_first; pa.offsets = b.offsets;
+        pa.comp = b.comp; pa.eps = s.eps;
+        if (fold) { pa.stats_x = b.stats_x; pa.stats_q = b.stats_q; pa.stats_acc = b.stats_acc; }
+        else { pa.lnw = w.norm1_w; pa.lnb = w.norm1_b; pa.xn = b.xn; pa.qn = b.qn; }
+        rc = region_pool(pa, s.dtype, st);
+    } else {
+        rc = vtp_pool(x_in, s.dtype, s.B, N, C, s.W, s.num_extra, b.patches, L_dev, rows, b.comp, w.norm1_w,
+                      w.norm1_b, s.eps, b.xn, b.qn, st);
+    }
     if (rc || (rc = marks.mark(3))) return rc;
 
     LinearArgs lq;   // q = LN(comp) Wq^T + b
-    lq.a = b.qn; lq.lda = C; lq.w = w.q_w; lq.bias = w.q_b; lq.y = b.qp; lq.ldy = C; lq.dtype = s.dtype;
-    lq.m_max = rows; lq.m_dev = L_dev; lq.N = C; lq.K = C; lq.flags = kflag;
+    lq.a = fold ? b.comp : b.qn; lq.lda = C; lq.w = fold ? w.q_wf : w.q_w; lq.bias = fold ? w.q_c : w.q_b;
+    lq.y = b.qp; lq.ldy = C; lq.dtype = s.dtype; lq.m_max = rows; lq.m_dev = L_dev; lq.N = C; lq.K = C; lq.flags = kflag;
+    if (fold) { lq.ln_mode = 1; lq.ln_stats = b.stats_q; lq.ln_s = w.q_s; }
     if ((rc = linear(lq, st)) || (rc = marks.mark(4))) return rc;
 
     LinearArgs lkv;  // kv = LN(x) Wkv^T + b, rows stay [b, token, {k,v}, head, d]
-    lkv.a = b.xn; lkv.lda = C; lkv.w = w.kv_w; lkv.bias = w.kv_b; lkv.y = b.kv; lkv.ldy = 2 * C;
-    lkv.dtype = s.dtype; lkv.m_max = rows; lkv.N = 2 * C; lkv.K = C; lkv.flags = kflag;
+    lkv.a = fold ? x_in : b.xn; lkv.lda = C; lkv.w = fold ? w.kv_wf : w.kv_w; lkv.bias = fold ? w.kv_c : w.kv_b;
+    lkv.y = b.kv; lkv.ldy = 2 * C; lkv.dtype = s.dtype; lkv.m_max = rows; lkv.N = 2 * C; lkv.K = C; lkv.flags = kflag;
+    if (fold) { lkv.ln_mode = 1; lkv.ln_stats = b.stats_x; lkv.ln_s = w.kv_s; }
     if ((rc = linear(lkv, st)) || (rc = marks.mark(5))) return rc;
 
     AttnArgs at;
@@ -127,18 +160,23 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     at.offsets = b.offsets; at.l_max = rows; at.max_q = N; at.scale = 1.0f / sqrtf((float)d); at.flags = kflag;
     if ((rc = attention(at, st)) || (rc = marks.mark(6))) return rc;
 
-    LinearArgs lp;   // q1 = comp + attn_out Wp^T + b
+    LinearArgs lp;   // q1 = comp + attn_out Wp^T + b   (and, when folding, the row sums LN2 needs)
     lp.a = b.ao; lp.lda = C; lp.w = w.proj_w; lp.bias = w.proj_b; lp.res = b.comp; lp.ldr = C; lp.y = b.q1;
     lp.ldy = C; lp.dtype = s.dtype; lp.m_max = rows; lp.m_dev = L_dev; lp.N = C; lp.K = C; lp.flags = kflag;
+    if (fold) lp.emit_stats = b.stats_acc;
     if ((rc = linear(lp, st)) || (rc = marks.mark(7))) return rc;
 
-    rc = vtp_layernorm(b.q1, s.dtype, rows, L_dev, C, C, w.norm2_w, w.norm2_b, s.eps, b.qn, st);
-    if (rc || (rc = marks.mark(8))) return rc;
+    if (!fold) {
+        rc = vtp_layernorm(b.q1, s.dtype, rows, L_dev, C, C, w.norm2_w, w.norm2_b, s.eps, b.qn, st);
+        if (rc) return rc;
+    }
+    if ((rc = marks.mark(8))) return rc;
 
     LinearArgs l1;   // hid = GELU(LN2(q1) W1^T + b)
-    l1.a = b.qn; l1.lda = C; l1.w = w.fc1_w; l1.bias = w.fc1_b; l1.y = b.hid; l1.ldy = s.hidden;
-    l1.dtype = s.dtype; l1.m_max = rows; l1.m_dev = L_dev; l1.N = s.hidden; l1.K = C;
+    l1.a = fold ? b.q1 : b.qn; l1.lda = C; l1.w = fold ? w.fc1_wf : w.fc1_w; l1.bias = fold ? w.fc1_c : w.fc1_b;
+    l1.y = b.hid; l1.ldy = s.hidden; l1.dtype = s.dtype; l1.m_max = rows; l1.m_dev = L_dev; l1.N = s.hidden; l1.K = C;
     l1.flags = kflag | VTP_FLAG_GELU;
+    if (fold) { l1.ln_mode = 2; l1.ln_stats = b.stats_acc; l1.ln_s = w.fc1_s; l1.ln_dim = C; l1.ln_eps = s.eps; }
     if ((rc = linear(l1, st)) || (rc = marks.mark(9))) return rc;
 
     LinearArgs l2;   // q2 = q1 + hid W2^T + b   (into the q-projection buffer, dead by now)
@@ -146,8 +184,15 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     l2.ldy = C; l2.dtype = s.dtype; l2.m_max = rows; l2.m_dev = L_dev; l2.N = C; l2.K = s.hidden; l2.flags = kflag;
     if ((rc = linear(l2, st)) || (rc = marks.mark(10))) return rc;
 
-    rc = vtp_unpool_add(b.qp, b.comp, s.dtype, s.B, N, C, s.W, s.num_extra, b.patches, L_dev, rows, x_in,
-                        x_out, st);
+    if (by_region) {
+        RegionUnpoolArgs ua;
+        ua.g = g; ua.sp = sp; ua.q = b.qp; ua.comp = b.comp; ua.ref = x_in; ua.out = x_out; ua.idx = b.idx;
+        ua.region_first = b.region_first; ua.offsets = b.offsets;
+        rc = region_unpool(ua, s.dtype, st);
+    } else {
+        rc = vtp_unpool_add(b.qp, b.comp, s.dtype, s.B, N, C, s.W, s.num_extra, b.patches, L_dev, rows, x_in,
+                            x_out, st);
+    }
     if (rc) return rc;
     return marks.mark(11);
 }

@@ -4,11 +4,9 @@
 // grained_sample_index_to_patch (vtpack/layers/csrc/grained_sample/grained_sample.cu:146-196,
 // 302-345).  Unlike the reference nothing is copied to the host: the per-image counts and
 // their exclusive prefix stay in device memory for the kernels that follow.
-#include "common.cuh"
+#include "region_ops.h"
 
 namespace vtp {
-
-struct Splits { int v[8]; int n; };
 
 // One warp per region.  Lanes stride over 16-byte channel chunks, sum the region's
 // tokens in (dy, dx) order in fp32, divide by the token count, then take n_splits dot
@@ -119,7 +117,7 @@ __global__ void __launch_bounds__(128)
 write_patches_kernel(const I* __restrict__ idx, int B, int Hr, int Wr, Splits sp, int region,
                      int num_extra, const int32_t* __restrict__ counts,
                      int32_t* __restrict__ offsets, int32_t* __restrict__ patches,
-                     int64_t* __restrict__ patches64) {
+                     int64_t* __restrict__ patches64, int32_t* __restrict__ region_first) {
     extern __shared__ int s_start[];   // [R + 1] first row of each region within the image
     __shared__ int s_warp[4];
     __shared__ int s_base;
@@ -153,8 +151,10 @@ write_patches_kernel(const I* __restrict__ idx, int B, int Hr, int Wr, Splits sp
     }
     __syncthreads();
     const int base = s_base;
+    if (region_first)
+        for (int r = tid; r < R; r += blockDim.x) region_first[(size_t)b * R + r] = base + s_start[r];
 
-    for (int e = tid; e < num_extra; e += blockDim.x) {
+    for (int e = tid; e < num_extra && patches; e += blockDim.x) {
         const int row = base + e;
         reinterpret_cast<int4*>(patches)[row] = make_int4(b, -e - 1, 0, 1);
         if (patches64) {
@@ -164,6 +164,7 @@ write_patches_kernel(const I* __restrict__ idx, int B, int Hr, int Wr, Splits sp
         }
     }
     const int items = R * region;           // (region, dy) with dy < split
+    if (!patches) return;
     for (int it = tid; it < items; it += blockDim.x) {
         const int r = it / region;
         const int dy = it % region;
@@ -246,39 +247,50 @@ extern "C" int vtp_gate_argmax(const float* logits, int rows, int n_splits, int3
     return check_launch("gate_argmax");
 }
 
-extern "C" int vtp_index_to_patch(const void* indices, int idx_is_i64, const int* splits,
-                                  int n_splits, int B, int Hr, int Wr, int region, int num_extra,
-                                  int32_t* counts, int32_t* offsets, int32_t* patches,
-                                  int64_t* patches64, void* stream) {
-    VTP_REQUIRE(indices && splits && counts && offsets && patches, VTP_ERR_NULL,
-                "index_to_patch: null pointer");
-    VTP_REQUIRE(B > 0 && Hr > 0 && Wr > 0 && region > 0 && num_extra >= 0, VTP_ERR_SHAPE,
-                "index_to_patch: bad shape");
-    VTP_REQUIRE(n_splits >= 1 && n_splits <= 8, VTP_ERR_SHAPE, "index_to_patch: n_splits %d", n_splits);
-    VTP_REQUIRE(Hr * Wr <= 8192, VTP_ERR_SHAPE, "index_to_patch: %d regions per image", Hr * Wr);
-    Splits sp;
-    sp.n = n_splits;
-    for (int i = 0; i < 8; ++i) sp.v[i] = 1;
-    for (int i = 0; i < n_splits; ++i) {
-        VTP_REQUIRE(splits[i] >= 1 && splits[i] <= region && region % splits[i] == 0, VTP_ERR_SHAPE,
-                    "index_to_patch: split %d does not divide region %d", splits[i], region);
-        sp.v[i] = splits[i];
-    }
-    VTP_REQUIRE(aligned16(patches) && (!patches64 || aligned16(patches64)), VTP_ERR_ALIGN,
-                "index_to_patch: unaligned patch buffer");
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+namespace vtp {
+int index_to_patch(const void* indices, int idx_is_i64, const Splits& sp, int B, int Hr, int Wr, int region,
+                   int num_extra, int32_t* counts, int32_t* offsets, int32_t* patches, int64_t* patches64,
+                   int32_t* region_first, cudaStream_t st) {
     const int R = Hr * Wr;
     const size_t smem = (size_t)(R + 1) * sizeof(int);
     if (idx_is_i64) {
         const int64_t* ip = static_cast<const int64_t*>(indices);
         count_kernel<int64_t><<<ceil_div(B, 4), 128, 0, st>>>(ip, B, R, sp, num_extra, counts);
-        write_patches_kernel<int64_t><<<B, 128, smem, st>>>(ip, B, Hr, Wr, sp, region, num_extra,
-                                                            counts, offsets, patches, patches64);
+        write_patches_kernel<int64_t><<<B, 128, smem, st>>>(ip, B, Hr, Wr, sp, region, num_extra, counts, offsets,
+                                                            patches, patches64, region_first);
     } else {
         const int32_t* ip = static_cast<const int32_t*>(indices);
         count_kernel<int32_t><<<ceil_div(B, 4), 128, 0, st>>>(ip, B, R, sp, num_extra, counts);
-        write_patches_kernel<int32_t><<<B, 128, smem, st>>>(ip, B, Hr, Wr, sp, region, num_extra,
-                                                            counts, offsets, patches, patches64);
+        write_patches_kernel<int32_t><<<B, 128, smem, st>>>(ip, B, Hr, Wr, sp, region, num_extra, counts, offsets,
+                                                            patches, patches64, region_first);
     }
     return check_launch("index_to_patch");
+}
+
+int make_splits(Splits* sp, const int* splits, int n_splits, int region) {
+    VTP_REQUIRE(n_splits >= 1 && n_splits <= 8, VTP_ERR_SHAPE, "index_to_patch: n_splits %d", n_splits);
+    sp->n = n_splits;
+    for (int i = 0; i < 8; ++i) sp->v[i] = 1;
+    for (int i = 0; i < n_splits; ++i) {
+        VTP_REQUIRE(splits[i] >= 1 && splits[i] <= region && region % splits[i] == 0, VTP_ERR_SHAPE,
+                    "index_to_patch: split %d does not divide region %d", splits[i], region);
+        sp->v[i] = splits[i];
+    }
+    return VTP_OK;
+}
+}  // namespace vtp
+
+extern "C" int vtp_index_to_patch(const void* indices, int idx_is_i64, const int* splits, int n_splits, int B,
+                                  int Hr, int Wr, int region, int num_extra, int32_t* counts, int32_t* offsets,
+                                  int32_t* patches, int64_t* patches64, void* stream) {
+    VTP_REQUIRE(indices && splits && counts && offsets && patches, VTP_ERR_NULL, "index_to_patch: null pointer");
+    VTP_REQUIRE(B > 0 && Hr > 0 && Wr > 0 && region > 0 && num_extra >= 0, VTP_ERR_SHAPE,
+                "index_to_patch: bad shape");
+    VTP_REQUIRE(Hr * Wr <= 8192, VTP_ERR_SHAPE, "index_to_patch: %d regions per image", Hr * Wr);
+    Splits sp;
+    if (int rc = make_splits(&sp, splits, n_splits, region)) return rc;
+    VTP_REQUIRE(aligned16(patches) && (!patches64 || aligned16(patches64)), VTP_ERR_ALIGN,
+                "index_to_patch: unaligned patch buffer");
+    return index_to_patch(indices, idx_is_i64, sp, B, Hr, Wr, region, num_extra, counts, offsets, patches,
+                          patches64, nullptr, static_cast<cudaStream_t>(stream));
 }

@@ -18,10 +18,53 @@ int linear_validate(const LinearArgs& p) {
 int linear(const LinearArgs& p, cudaStream_t st) {
     if (int rc = linear_validate(p)) return rc;
     if (p.dtype == VTP_BF16 && !(p.flags & VTP_FLAG_CUDA_CORES)) return linear_tcgen05(p, st);
+    VTP_REQUIRE(p.ln_mode == 0 && !p.emit_stats, VTP_ERR_UNSUPPORTED,
+                "linear (CUDA cores): folded LayerNorm is a feature of the tcgen05 kernel");
     return linear_cuda_cores(p, st);
 }
 
+// One warp per output row n of W [N,K]:
+//   w_out[n,k] = round(W[n,k] * gamma[k]),  s[n] = sum_k w_out[n,k],  c[n] = sum_k beta[k] W[n,k] + bias[n]
+template <typename T>
+__global__ void __launch_bounds__(256)
+fold_ln_kernel(const T* __restrict__ w, int N, int K, const float* __restrict__ gamma,
+               const float* __restrict__ beta, const float* __restrict__ bias, T* __restrict__ w_out,
+               float* __restrict__ s_out, float* __restrict__ c_out) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= N) return;
+    float s = 0.f, c = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const float wv = to_f32(w[(size_t)n * K + k]);
+        const T folded = from_f32<T>(wv * __ldg(gamma + k));
+        w_out[(size_t)n * K + k] = folded;
+        s += to_f32(folded);
+        c = fmaf(__ldg(beta + k), wv, c);
+    }
+    s = warp_sum(s);
+    c = warp_sum(c);
+    if (lane == 0) {
+        s_out[n] = s;
+        c_out[n] = c + (bias ? __ldg(bias + n) : 0.f);
+    }
+}
+
 }  // namespace vtp
+
+extern "C" int vtp_fold_layernorm(const void* w, int dtype, int N, int K, const float* gamma, const float* beta,
+                                  const float* bias, void* w_out, float* s_out, float* c_out, void* stream) {
+    VTP_REQUIRE(w && gamma && beta && w_out && s_out && c_out, VTP_ERR_NULL, "fold_layernorm: null pointer");
+    VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "fold_layernorm: dtype %d", dtype);
+    VTP_REQUIRE(N > 0 && K > 0, VTP_ERR_SHAPE, "fold_layernorm: bad shape");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = vtp::ceil_div(N, 8);
+    if (dtype == VTP_F32)
+        vtp::fold_ln_kernel<float><<<grid, 256, 0, st>>>((const float*)w, N, K, gamma, beta, bias, (float*)w_out, s_out, c_out);
+    else
+        vtp::fold_ln_kernel<vtp::bf16><<<grid, 256, 0, st>>>((const vtp::bf16*)w, N, K, gamma, beta, bias,
+                                                             (vtp::bf16*)w_out, s_out, c_out);
+    return vtp::check_launch("fold_layernorm");
+}
 
 extern "C" int vtp_linear(const void* a, long long lda, const void* w, const float* bias,
                           const void* residual, long long ldr, void* y, long long ldy, int dtype, int m_max,

@@ -22,7 +22,19 @@ struct LinearArgs {
     unsigned flags = 0;
     int out_grp = 0, out_skip = 0;
     int res_mod = 0, res_off = 0;
+    // LayerNorm folded into the GEMM (tcgen05 kernel only): `a` holds the raw rows, `w` holds
+    // W*diag(gamma), ln_s[n] = sum_k w[n,k], bias[n] = sum_k beta[k] W[n,k] + b[n]; then
+    //   LN(a) W^T + b = rstd[m] * (acc[m,n] - mean[m] * ln_s[n]) + bias[n].
+    // ln_mode 1: ln_stats[m] = (mean, rstd).  ln_mode 2: ln_stats[m] = (sum, sum of squares)
+    // over ln_dim elements, variance = E[x^2] - mean^2, rstd = rsqrt(var + ln_eps).
+    const float2* ln_stats = nullptr; const float* ln_s = nullptr;
+    int ln_mode = 0, ln_dim = 0; float ln_eps = 0.f;
+    // When set, every stored row adds (sum, sum of squares) of its outputs here (atomics), the
+    // ln_mode 2 input of the next GEMM.
+    float2* emit_stats = nullptr;
 };
+
+struct LnFold { const float2* stats; const float* s; int mode, dim; float eps; float2* emit; };
 
 int linear_validate(const LinearArgs& p);
 int linear_cuda_cores(const LinearArgs& p, cudaStream_t st);   // fp32 or bf16 inputs, CUDA cores

@@ -46,7 +46,7 @@ struct TcSmem {
     static constexpr int B_BYTES = BN * TBK * 2;
     static constexpr int RING = STAGES * (A_BYTES + B_BYTES);
     static constexpr int STAGE_OUT = 2 * TBM * 128;   // two 128-row x 64-column bf16 slabs
-    static constexpr int BIAS = BN * 4;               // the bias slice of the tile in the epilogue
+    static constexpr int BIAS = 2 * BN * 4;           // the bias and LayerNorm-fold slices of the tile in the epilogue
     static constexpr int USED = RING + STAGE_OUT + BIAS + 256 /* barriers */;
     // Dynamic shared memory is only promised 16-byte alignment; the ring wants 1024.  In
     // practice the base is already aligned; the kernel checks that what is left fits.
@@ -91,7 +91,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_r,
                  int use_tma_store, const float* __restrict__ bias, const bf16* __restrict__ res, long long ldr,
                  OutT* __restrict__ y, long long ldy, int m_max, const int32_t* __restrict__ m_dev, int N,
-                 int K, unsigned flags, RowMap rm, int* status) {
+                 int K, unsigned flags, RowMap rm, LnFold ln, int* status) {
     using S = TcSmem<BN, STAGES>;
     int M = m_max;
     if (m_dev) M = min(__ldg(m_dev), m_max);
@@ -217,7 +217,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 // this tile's bias slice -> shared memory (one value per thread), so the column
                 // loop reads it as a broadcast instead of through the global-load path
                 const int te = threadIdx.x - 64;
-                if (te < BN) bias_s[te] = (bias && nt0 + te < N) ? __ldg(bias + nt0 + te) : 0.f;
+                if (te < BN) {
+                    bias_s[te] = (bias && nt0 + te < N) ? __ldg(bias + nt0 + te) : 0.f;
+                    if (ln.mode) bias_s[BN + te] = (nt0 + te < N) ? __ldg(ln.s + nt0 + te) : 0.f;
+                }
                 if (res && elected && res_issued < slab_no) {
                     // first slab of a run of TMA tiles: nobody prefetched its residual
                     bulk_wait_group_read0();
@@ -230,6 +233,19 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            // folded LayerNorm: out = ln_a * acc + ln_b * s[n] + bias[n]
+            float ln_a = 1.f, ln_b = 0.f;
+            if (ln.mode && m0 + row < M) {
+                const float2 st = __ldg(ln.stats + m0 + row);
+                float mean = st.x, rstd = st.y;
+                if (ln.mode == 2) {
+                    mean = st.x / (float)ln.dim;
+                    rstd = rsqrtf(fmaxf(st.y / (float)ln.dim - mean * mean, 0.f) + ln.eps);
+                }
+                ln_a = rstd;
+                ln_b = -rstd * mean;
+            }
+            float e1 = 0.f, e2 = 0.f;     // sum and sum of squares of this thread's outputs
             if (tma_path) {
                 // ---- full tile: registers -> swizzled staging slab -> TMA store
                 named_barrier(1, EPI_THREADS);                       // bias slice complete
@@ -264,8 +280,17 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         const float4* bs = reinterpret_cast<const float4*>(bias_s + sl * 64 + chunk * 8);
                         const float4 b0 = bs[0];
                         const float4 b1 = bs[1];
-                        vj[0] += b0.x; vj[1] += b0.y; vj[2] += b0.z; vj[3] += b0.w;
-                        vj[4] += b1.x; vj[5] += b1.y; vj[6] += b1.z; vj[7] += b1.w;
+                        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                        if (ln.mode) {
+                            const float4 s0 = bs[BN / 4];
+                            const float4 s1 = bs[BN / 4 + 1];
+                            const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) vj[i] = fmaf(ln_a, vj[i], fmaf(ln_b, ss[i], bb[i]));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) vj[i] += bb[i];
+                        }
                         if (flags & VTP_FLAG_GELU) {
 #pragma unroll
                             for (int i = 0; i < 8; ++i) vj[i] = gelu_fast(vj[i]);
@@ -277,6 +302,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                             rv.to_float(rf);
 #pragma unroll
                             for (int i = 0; i < 8; ++i) vj[i] += rf[i];
+                        }
+                        if (ln.emit && nt0 + sl * 64 + chunk * 8 < N) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) { e1 += vj[i]; e2 = fmaf(vj[i], vj[i], e2); }
                         }
                         Vec<bf16> ov;
                         ov.from_float(vj);
@@ -302,6 +331,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                             }
                         }
                     }
+                }
+                if (ln.emit) {
+                    atomicAdd(&ln.emit[m0 + row].x, e1);
+                    atomicAdd(&ln.emit[m0 + row].y, e2);
                 }
                 continue;
             }
@@ -331,11 +364,22 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     float v[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * j + i]);
+                    float bb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                     if (bias) {
                         const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + n));
                         const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + n) + 1);
-                        v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                        v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                        bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w;
+                        bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
+                    }
+                    if (ln.mode) {
+                        const float4 s0 = __ldg(reinterpret_cast<const float4*>(ln.s + n));
+                        const float4 s1 = __ldg(reinterpret_cast<const float4*>(ln.s + n) + 1);
+                        const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] = fmaf(ln_a, v[i], fmaf(ln_b, ss[i], bb[i]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] += bb[i];
                     }
                     if (flags & VTP_FLAG_GELU) {
 #pragma unroll
@@ -349,8 +393,16 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                         for (int i = 0; i < 8; ++i) v[i] += rf[i];
                     }
+                    if (ln.emit) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) { e1 += v[i]; e2 = fmaf(v[i], v[i], e2); }
+                    }
                     OutVec<OutT>::store8(y + orow * ldy + n, v);
                 }
+            }
+            if (ln.emit && row_ok) {
+                atomicAdd(&ln.emit[m].x, e1);
+                atomicAdd(&ln.emit[m].y, e2);
             }
         }
         if (elected) bulk_wait_group0();      // every TMA store has landed before the CTA retires
@@ -448,8 +500,9 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
     const long long tiles = (long long)ceil_div(p.N, BN) * ceil_div(p.m_max, TBM);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const RowMap rm{p.out_grp, p.out_skip, p.res_mod, p.res_off};
+    const LnFold ln{p.ln_stats, p.ln_s, p.ln_mode, p.ln_dim, p.ln_eps, p.emit_stats};
     kern<<<grid, TC_THREADS, S::TOTAL, st>>>(ta, tw, ty, tr, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
-                                      p.m_dev, p.N, p.K, p.flags, rm, device_status_ptr());
+                                      p.m_dev, p.N, p.K, p.flags, rm, ln, device_status_ptr());
     return check_launch("linear (tcgen05)");
 }
 
@@ -458,6 +511,8 @@ int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
     VTP_REQUIRE(p.dtype == VTP_BF16, VTP_ERR_DTYPE, "linear (tcgen05): bf16 operands only");
     VTP_REQUIRE(p.K % TBK == 0, VTP_ERR_SHAPE, "linear (tcgen05): K=%d must be a multiple of %d", p.K, TBK);
     VTP_REQUIRE(p.N % 8 == 0, VTP_ERR_SHAPE, "linear (tcgen05): N=%d must be a multiple of 8", p.N);
+    VTP_REQUIRE(p.ln_mode == 0 || (p.ln_stats && p.ln_s && p.out_grp == 0 && (p.ln_mode == 1 || p.ln_dim > 0)),
+                VTP_ERR_NULL, "linear (tcgen05): folded LayerNorm needs row statistics and the column sums");
     VTP_REQUIRE(p.lda % 8 == 0 && p.ldy % 8 == 0 && (!p.res || p.ldr % 8 == 0), VTP_ERR_ALIGN,
                 "linear (tcgen05): row strides must be multiples of 16 bytes");
     // widest tile that does not pad N more than a narrower one would

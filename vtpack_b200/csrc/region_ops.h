@@ -1,0 +1,56 @@
+// Internal interface of the region-parallel kernels (router gate, pooling, unpooling).
+#pragma once
+
+#include "common.cuh"
+
+namespace vtp {
+
+struct Splits { int v[8]; int n; };
+
+struct RegionGeom {
+    int B, Hr, Wr;      // images, regions per column / row
+    int W, N, C;        // token grid width, tokens per image (extra + H*W), channels
+    int num_extra;      // cls tokens in front of the grid
+    int region;         // tokens per region side
+};
+
+struct RegionPoolArgs {
+    RegionGeom g; Splits sp;
+    const void* x = nullptr;
+    const int32_t* idx = nullptr;            // grain index per region
+    const int32_t* region_first = nullptr;   // packed row of each region's first query
+    const int32_t* offsets = nullptr;        // packed row of each image's first query
+    void* comp = nullptr;
+    // LayerNorm applied later, in a GEMM epilogue: per-row (mean, rstd) of x and of comp, and a
+    // per-query accumulator to clear.  Leave null for explicit LayerNorm rows instead.
+    float2* stats_x = nullptr; float2* stats_q = nullptr; float2* stats_acc = nullptr;
+    const float* lnw = nullptr; const float* lnb = nullptr; float eps = 1e-6f;
+    void* xn = nullptr; void* qn = nullptr;
+};
+
+struct RegionUnpoolArgs {
+    RegionGeom g; Splits sp;
+    const void* q = nullptr; const void* comp = nullptr; const void* ref = nullptr; void* out = nullptr;
+    const int32_t* idx = nullptr; const int32_t* region_first = nullptr; const int32_t* offsets = nullptr;
+};
+
+struct RegionGateArgs {
+    RegionGeom g;
+    const void* x = nullptr;
+    const float* gw = nullptr; const float* gb = nullptr; int S = 0;
+    float* logits_out = nullptr; int32_t* idx_out = nullptr;
+};
+
+bool region_ops_supported(const RegionGeom& g, int dtype);
+int region_pool(const RegionPoolArgs& a, int dtype, cudaStream_t st);
+int region_unpool(const RegionUnpoolArgs& a, int dtype, cudaStream_t st);
+int region_gate(const RegionGateArgs& a, int dtype, cudaStream_t st);
+
+// Patch list + per-region first rows (internal form of vtp_index_to_patch).
+int index_to_patch(const void* indices, int idx_is_i64, const Splits& sp, int B, int Hr, int Wr, int region,
+                   int num_extra, int32_t* counts, int32_t* offsets, int32_t* patches, int64_t* patches64,
+                   int32_t* region_first, cudaStream_t st);
+
+int make_splits(Splits* sp, const int* splits, int n_splits, int region);
+
+}  // namespace vtp

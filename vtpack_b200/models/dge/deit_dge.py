@@ -118,7 +118,7 @@ class _WeightPack:
 
 
 def _param_key(mod: nn.Module, dtype):
-    return (dtype,) + tuple((p.data_ptr(), p._version, p.dtype) for p in mod.parameters())
+    return (dtype, getattr(mod, "fold_layernorm", None)) + tuple((p.data_ptr(), p._version, p.dtype) for p in mod.parameters())
 
 
 def _pack_block(blk, dtype) -> _lib.BlockWeights:
@@ -140,6 +140,18 @@ def _pack_block(blk, dtype) -> _lib.BlockWeights:
             fc2_w=mat(m.fc2.weight), fc2_b=vec(m.fc2.bias),
             gate_w=vec(blk.dge.router.gate.weight), gate_b=vec(blk.dge.router.gate.bias),
         )
+        if dtype == torch.bfloat16 and blk.fold_layernorm:
+            # LayerNorm folded into the Linear that follows it (weight preparation, once)
+            for name, lin_w, lin_b, gw, gb in (("q", t["q_w"], t["q_b"], t["norm1_w"], t["norm1_b"]),
+                                               ("kv", t["kv_w"], t["kv_b"], t["norm1_w"], t["norm1_b"]),
+                                               ("fc1", t["fc1_w"], t["fc1_b"], t["norm2_w"], t["norm2_b"])):
+                wf = torch.empty_like(lin_w)
+                sv = torch.empty(lin_w.shape[0], dtype=torch.float32, device=lin_w.device)
+                cv = torch.empty_like(sv)
+                _lib.check(_lib.lib().vtp_fold_layernorm(
+                    ptr(lin_w), dtype_code(dtype), lin_w.shape[0], lin_w.shape[1], ptr(gw), ptr(gb), ptr(lin_b),
+                    ptr(wf), ptr(sv), ptr(cv), stream_ptr(lin_w.device)))
+                t[name + "_wf"], t[name + "_s"], t[name + "_c"] = wf, sv, cv
         s = _lib.BlockWeights()
         for k, v in t.items():
             setattr(s, k, v.data_ptr())
@@ -178,6 +190,7 @@ class Block(nn.Module):
                                          complexity_handler=self.complexity)
         self.split_sizes = list(split_sizes)
         self.flags = 0                          # _lib.FLAG_CUDA_CORES selects the CUDA-core kernels
+        self.fold_layernorm = True              # bf16: LayerNorm applied inside the q / kv / fc1 GEMM epilogues
         self._pack = _WeightPack()
 
     def complexity(self, num_inputs, num_queries):
@@ -274,6 +287,7 @@ class VisionTransformer(nn.Module):
         self.img_size, self.patch_size, self.depth = img_size, patch_size, depth
         self.split_sizes = list(split_sizes)
         self.flags = 0
+        self.fold_layernorm = True
         self._pack = _WeightPack()
         self.last_counts = None
         self._init_weights()
@@ -323,6 +337,7 @@ class VisionTransformer(nn.Module):
             blocks = (_lib.BlockWeights * self.depth)()
             for i, blk in enumerate(self.blocks):
                 blk.flags = self.flags
+                blk.fold_layernorm = self.fold_layernorm
                 blocks[i] = _pack_block(blk, dtype)
             pk.key, pk.tensors, pk.struct = key, t, (m, blocks)
         return pk.struct
