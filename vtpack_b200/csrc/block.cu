@@ -23,9 +23,9 @@ struct Carver {
 };
 
 struct BlockScratch {
-    int32_t *idx, *counts, *offsets, *patches, *region_first;
-    float* logits;
-    float2 *stats_x, *stats_q, *stats_acc;
+    int32_t *idx[2], *counts, *offsets, *patches, *region_first;   // idx / logits / stats_x: this block's and the
+    float* logits[2];                                              // next block's (written by this block's unpool)
+    float2 *stats_x[2], *stats_q, *stats_acc;
     void *comp, *xn, *qn, *qp, *kv, *ao, *q1, *hid;
     long long bytes;
 };
@@ -37,13 +37,16 @@ static BlockScratch carve_block(const vtp_dge_shape& s, void* ws) {
     const int R = (s.H / s.region) * (s.W / s.region);
     Carver c(ws);
     BlockScratch b;
-    b.idx = (int32_t*)c.take((long long)s.B * R * 4);
+    b.idx[0] = (int32_t*)c.take((long long)s.B * R * 4);
+    b.idx[1] = (int32_t*)c.take((long long)s.B * R * 4);
     b.counts = (int32_t*)c.take((long long)s.B * 4);
     b.offsets = (int32_t*)c.take((long long)(s.B + 1) * 4);
     b.patches = (int32_t*)c.take(rows * 16);
     b.region_first = (int32_t*)c.take((long long)s.B * R * 4);
-    b.logits = (float*)c.take((long long)s.B * R * s.n_splits * 4);
-    b.stats_x = (float2*)c.take(rows * 8);
+    b.logits[0] = (float*)c.take((long long)s.B * R * s.n_splits * 4);
+    b.logits[1] = (float*)c.take((long long)s.B * R * s.n_splits * 4);
+    b.stats_x[0] = (float2*)c.take(rows * 8);
+    b.stats_x[1] = (float2*)c.take(rows * 8);
     b.stats_q = (float2*)c.take(rows * 8);
     b.stats_acc = (float2*)c.take(rows * 8);
     b.comp = c.take(rows * s.C * e);
@@ -83,9 +86,22 @@ struct StageMarks {
     }
 };
 
+static bool has_folded_weights(const vtp_block_weights& w) {
+    return w.q_wf && w.q_s && w.q_c && w.kv_wf && w.kv_s && w.kv_c && w.fc1_wf && w.fc1_s && w.fc1_c;
+}
+
+// Position of a block inside a model forward: whether the previous block's unpool already
+// produced this block's gate decisions and token statistics (in scratch slot `parity`), and
+// the block that follows, whose gate and statistics this block's unpool can produce.
+struct BlockChain {
+    bool have_gate = false;
+    int parity = 0;
+    const vtp_block_weights* next = nullptr;
+};
+
 static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, const void* x_in, void* x_out,
                          const float* forced_logits, int32_t* counts_out, void* ws, cudaStream_t st,
-                         const StageMarks& marks = StageMarks()) {
+                         const StageMarks& marks = StageMarks(), const BlockChain& chain = BlockChain()) {
     const int N = s.num_extra + s.H * s.W;
     const int rows = s.B * N;
     const int Hr = s.H / s.region, Wr = s.W / s.region;
@@ -103,22 +119,29 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     // Region-parallel gate / pool / unpool when the region is 4x4 tokens, else one warp per patch.
     const bool by_region = region_ops_supported(g, s.dtype);
     // LayerNorm folded into the q / kv / fc1 GEMM epilogues (bf16 tensor-core path with prepared weights).
-    const bool fold = by_region && s.dtype == VTP_BF16 && !kflag && w.q_wf && w.q_s && w.q_c && w.kv_wf && w.kv_s &&
-                      w.kv_c && w.fc1_wf && w.fc1_s && w.fc1_c;
+    const bool fold = by_region && s.dtype == VTP_BF16 && !kflag && has_folded_weights(w);
+    const int par = chain.parity & 1;
+    int32_t* idx = b.idx[par];
+    float2* stats_x = b.stats_x[par];
+    bool stats_x_ready = false;
 
-    if (forced_logits) {
-        rc = vtp_gate_argmax(forced_logits, s.B * Hr * Wr, s.n_splits, b.idx, st);
+    if (chain.have_gate && fold && !forced_logits) {
+        stats_x_ready = true;          // gate decisions and token statistics came from the previous block's unpool
+        rc = VTP_OK;
+    } else if (forced_logits) {
+        rc = vtp_gate_argmax(forced_logits, s.B * Hr * Wr, s.n_splits, idx, st);
     } else if (by_region) {
         RegionGateArgs ga;
-        ga.g = g; ga.x = x_in; ga.gw = w.gate_w; ga.gb = w.gate_b; ga.S = s.n_splits; ga.logits_out = b.logits;
-        ga.idx_out = b.idx;
+        ga.g = g; ga.x = x_in; ga.gw = w.gate_w; ga.gb = w.gate_b; ga.S = s.n_splits; ga.logits_out = b.logits[par];
+        ga.idx_out = idx; ga.eps = s.eps;
+        if (fold) { ga.stats_x = stats_x; stats_x_ready = true; }
         rc = region_gate(ga, s.dtype, st);
     } else {
         rc = vtp_router_gate(x_in, s.dtype, s.B, s.H, s.W, C, s.num_extra, s.region, w.gate_w, w.gate_b,
-                             s.n_splits, b.logits, b.idx, st);
+                             s.n_splits, b.logits[par], idx, st);
     }
     if (rc || (rc = marks.mark(1))) return rc;
-    rc = index_to_patch(b.idx, 0, sp, s.B, Hr, Wr, s.region, s.num_extra, b.counts, b.offsets,
+    rc = index_to_patch(idx, 0, sp, s.B, Hr, Wr, s.region, s.num_extra, b.counts, b.offsets,
                         by_region ? nullptr : b.patches, nullptr, b.region_first, st);
     if (rc || (rc = marks.mark(2))) return rc;
     if (counts_out) {
@@ -127,9 +150,12 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     }
     if (by_region) {
         RegionPoolArgs pa;
-        pa.g = g; pa.sp = sp; pa.x = x_in; pa.idx = b.idx; pa.region_first = b.region_first; pa.offsets = b.offsets;
+        pa.g = g; pa.sp = sp; pa.x = x_in; pa.idx = idx; pa.region_first = b.region_first; pa.offsets = b.offsets;
         pa.comp = b.comp; pa.eps = s.eps;
-        if (fold) { pa.stats_x = b.stats_x; pa.stats_q = b.stats_q; pa.stats_acc = b.stats_acc; }
+        if (fold) {
+            pa.stats_x = stats_x; pa.stats_q = b.stats_q; pa.stats_acc = b.stats_acc;
+            pa.stats_x_ready = stats_x_ready;
+        }
         else { pa.lnw = w.norm1_w; pa.lnb = w.norm1_b; pa.xn = b.xn; pa.qn = b.qn; }
         rc = region_pool(pa, s.dtype, st);
     } else {
@@ -147,7 +173,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     LinearArgs lkv;  // kv = LN(x) Wkv^T + b, rows stay [b, token, {k,v}, head, d]
     lkv.a = fold ? x_in : b.xn; lkv.lda = C; lkv.w = fold ? w.kv_wf : w.kv_w; lkv.bias = fold ? w.kv_c : w.kv_b;
     lkv.y = b.kv; lkv.ldy = 2 * C; lkv.dtype = s.dtype; lkv.m_max = rows; lkv.N = 2 * C; lkv.K = C; lkv.flags = kflag;
-    if (fold) { lkv.ln_mode = 1; lkv.ln_stats = b.stats_x; lkv.ln_s = w.kv_s; }
+    if (fold) { lkv.ln_mode = 1; lkv.ln_stats = stats_x; lkv.ln_s = w.kv_s; }
     if ((rc = linear(lkv, st)) || (rc = marks.mark(5))) return rc;
 
     AttnArgs at;
@@ -186,8 +212,15 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
 
     if (by_region) {
         RegionUnpoolArgs ua;
-        ua.g = g; ua.sp = sp; ua.q = b.qp; ua.comp = b.comp; ua.ref = x_in; ua.out = x_out; ua.idx = b.idx;
+        ua.g = g; ua.sp = sp; ua.q = b.qp; ua.comp = b.comp; ua.ref = x_in; ua.out = x_out; ua.idx = idx;
         ua.region_first = b.region_first; ua.offsets = b.offsets;
+        if (fold && chain.next && has_folded_weights(*chain.next)) {
+            // the rows being written are the next block's input: leave its LayerNorm statistics and
+            // its router gate's decisions in the other scratch slot
+            ua.next.stats_x = b.stats_x[par ^ 1]; ua.next.eps = s.eps;
+            ua.next.gw = chain.next->gate_w; ua.next.gb = chain.next->gate_b; ua.next.S = s.n_splits;
+            ua.next.logits = b.logits[par ^ 1]; ua.next.idx = b.idx[par ^ 1];
+        }
         rc = region_unpool(ua, s.dtype, st);
     } else {
         rc = vtp_unpool_add(b.qp, b.comp, s.dtype, s.B, N, C, s.W, s.num_extra, b.patches, L_dev, rows, x_in,
@@ -342,10 +375,20 @@ extern "C" int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weig
     pe.flags = s->flags & VTP_FLAG_CUDA_CORES;
     pe.out_grp = HW; pe.out_skip = 1; pe.res_mod = HW; pe.res_off = 1;
     if ((rc = linear(pe, st))) return rc;
+    bool chained = false;      // block i-1's unpool prepared block i's gate
     for (int i = 0; i < m->depth; ++i) {
+        BlockChain chain;
+        chain.have_gate = chained;
+        chain.parity = i & 1;
+        chain.next = (i + 1 < m->depth) ? &blocks[i + 1] : nullptr;
         rc = block_forward(*s, blocks[i], ms.x, ms.x, nullptr, counts_out ? counts_out + (size_t)i * s->B : nullptr,
-                           ms.block_ws, st);
+                           ms.block_ws, st, StageMarks(), chain);
         if (rc) return rc;
+        RegionGeom g;
+        g.B = s->B; g.Hr = s->H / s->region; g.Wr = s->W / s->region; g.W = s->W; g.N = N; g.C = C;
+        g.num_extra = s->num_extra; g.region = s->region;
+        chained = chain.next && region_ops_supported(g, s->dtype) && s->dtype == VTP_BF16 &&
+                  !(s->flags & VTP_FLAG_CUDA_CORES) && has_folded_weights(blocks[i]) && has_folded_weights(*chain.next);
     }
     rc = vtp_layernorm(ms.x, s->dtype, s->B, nullptr, C, (long long)N * C, m->norm_w, m->norm_b, s->eps, ms.cls_n, st);
     if (rc) return rc;

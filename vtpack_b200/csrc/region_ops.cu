@@ -4,8 +4,9 @@
 // the gate picked for it: warp w loads the four tokens of grid row w (each lane 16-byte
 // channel chunks), so all 16 rows of the region (12 KB at C=384 bf16) are in flight at
 // once, every region costs the same, and nothing depends on walking the patch list.
-// Sums that span grid rows are chained through shared memory in the reference's order
-// (dy outer, dx inner), so fp32 results stay bit-identical to the sequential sum.
+// Sums that span grid rows go through shared memory: each grid row is summed in token order,
+// then the rows of a patch are added top to bottom (the reference adds the same tokens in one
+// sequential chain; the results differ by fp32 rounding only).
 //
 // Replaces DynamicRouter.forward (vtpack/layers/dge.py:145-150), grained_sample_compress /
 // grained_sample_decompress (vtpack/layers/csrc/grained_sample/grained_sample.cu:31-69,
@@ -134,10 +135,10 @@ __global__ void __launch_bounds__(128)
 pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restrict__ idx,
                    const int32_t* __restrict__ region_first, const int32_t* __restrict__ offsets, Splits sp,
                    T* __restrict__ comp, float2* __restrict__ stats_x, float2* __restrict__ stats_q,
-                   float2* __restrict__ stats_acc, const float* __restrict__ lnw, const float* __restrict__ lnb,
-                   float eps, T* __restrict__ xn, T* __restrict__ qn) {
+                   float2* __restrict__ stats_acc, int write_stats_x, const float* __restrict__ lnw,
+                   const float* __restrict__ lnb, float eps, T* __restrict__ xn, T* __restrict__ qn) {
     constexpr int VN = Vec<T>::N;
-    extern __shared__ float part[];          // [4][C] partial sums handed from one grid row to the next
+    extern __shared__ float part[];          // [4 grid rows][2 patch columns][C] row sums
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int nchunks = g.C / VN;
     const int R = g.Hr * g.Wr;
@@ -161,7 +162,11 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
             if (lane + 32 * ch < nchunks) row[ch].store(comp + (size_t)dst_row * g.C + (lane + 32 * ch) * VN);
         if (STATS) {
             const float2 st = row_stats_1pass<MAXCH, VN>(f, lane, nchunks, g.C, eps);
-            if (lane == 0) { stats_x[src_row] = st; stats_q[dst_row] = st; stats_acc[dst_row] = make_float2(0.f, 0.f); }
+            if (lane == 0) {
+                if (write_stats_x) stats_x[src_row] = st;
+                stats_q[dst_row] = st;
+                stats_acc[dst_row] = make_float2(0.f, 0.f);
+            }
         } else {
             ln_store<T, MAXCH>(f, lane, nchunks, g.C, lnw, lnb, eps, xn + src_row * g.C);
             ln_store<T, MAXCH>(f, lane, nchunks, g.C, lnw, lnb, eps, qn + (size_t)dst_row * g.C);
@@ -187,11 +192,13 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
         float f[MAXCH][VN];
         row_to_float<T, MAXCH>(f, rows.raw[j], lane, nchunks);
         if (STATS) {
-            const float2 st = row_stats_1pass<MAXCH, VN>(f, lane, nchunks, g.C, eps);
-            if (lane == 0) stats_x[tok0 + j] = st;
-            if (step == 1 && lane == 0) {                     // the token is its own patch
-                stats_q[first + w * RG + j] = st;
-                stats_acc[first + w * RG + j] = make_float2(0.f, 0.f);
+            if (write_stats_x || step == 1) {
+                const float2 st = row_stats_1pass<MAXCH, VN>(f, lane, nchunks, g.C, eps);
+                if (lane == 0 && write_stats_x) stats_x[tok0 + j] = st;
+                if (step == 1 && lane == 0) {                     // the token is its own patch
+                    stats_q[first + w * RG + j] = st;
+                    stats_acc[first + w * RG + j] = make_float2(0.f, 0.f);
+                }
             }
         } else {
             ln_store<T, MAXCH>(f, lane, nchunks, g.C, lnw, lnb, eps, xn + (tok0 + j) * g.C);
@@ -210,58 +217,73 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
         return;
     }
 
-    // step 2: two patches per pair of grid rows; step 4: one patch for the region.  Grid row
-    // (w % step) continues the sum the row above it left in shared memory.
-    const int dy = w / step, ph = w % step;
-    const int npx = s;                         // patches this warp contributes to (1 or 2)
-    for (int p = 0; p < step; ++p) {
-        if (ph == p) {
-            for (int dx = 0; dx < npx; ++dx) {
-                float acc[MAXCH][VN];
-                float* slot = part + (size_t)(dy * 2 + dx) * g.C;
+    // step 2: two patches per pair of grid rows; step 4: one patch for the region.  Every warp
+    // leaves the in-order sum of its grid row's tokens (per patch column) in shared memory;
+    // after one barrier the rows of a patch are added top to bottom.
+    const int npx = s;                         // patch columns: 2 (step 2) or 1 (step 4)
+    for (int dx = 0; dx < npx; ++dx) {
+        float acc[MAXCH][VN];
 #pragma unroll
-                for (int ch = 0; ch < MAXCH; ++ch) {
-                    const int chunk = lane + 32 * ch;
+        for (int ch = 0; ch < MAXCH; ++ch)
 #pragma unroll
-                    for (int i = 0; i < VN; ++i)
-                        acc[ch][i] = (p > 0 && chunk < nchunks) ? slot[chunk * VN + i] : 0.f;
-                }
-                if (step == 2) {
-                    if (dx == 0) { add_row<T, MAXCH>(acc, rows.raw[0], lane, nchunks); add_row<T, MAXCH>(acc, rows.raw[1], lane, nchunks); }
-                    else         { add_row<T, MAXCH>(acc, rows.raw[2], lane, nchunks); add_row<T, MAXCH>(acc, rows.raw[3], lane, nchunks); }
-                } else {
+            for (int i = 0; i < VN; ++i) acc[ch][i] = 0.f;
+        if (step == 2) {
+            if (dx == 0) { add_row<T, MAXCH>(acc, rows.raw[0], lane, nchunks); add_row<T, MAXCH>(acc, rows.raw[1], lane, nchunks); }
+            else         { add_row<T, MAXCH>(acc, rows.raw[2], lane, nchunks); add_row<T, MAXCH>(acc, rows.raw[3], lane, nchunks); }
+        } else {
 #pragma unroll
-                    for (int j = 0; j < RG; ++j) add_row<T, MAXCH>(acc, rows.raw[j], lane, nchunks);
-                }
-                if (p < step - 1) {
-#pragma unroll
-                    for (int ch = 0; ch < MAXCH; ++ch) {
-                        const int chunk = lane + 32 * ch;
-                        if (chunk < nchunks)
-#pragma unroll
-                            for (int i = 0; i < VN; ++i) slot[chunk * VN + i] = acc[ch][i];
-                    }
-                } else {
-                    const float denom = (float)(step * step);
-#pragma unroll
-                    for (int ch = 0; ch < MAXCH; ++ch)
-#pragma unroll
-                        for (int i = 0; i < VN; ++i) acc[ch][i] = acc[ch][i] / denom;
-                    const int row = first + dy * s + dx;
-                    if (STATS) {
-                        round_store<T, MAXCH>(acc, lane, nchunks, comp + (size_t)row * g.C);
-                        const float2 st = row_stats_1pass<MAXCH, VN>(acc, lane, nchunks, g.C, eps);
-                        if (lane == 0) { stats_q[row] = st; stats_acc[row] = make_float2(0.f, 0.f); }
-                    } else {
-                        ln_store<T, MAXCH>(acc, lane, nchunks, g.C, lnw, lnb, eps, qn + (size_t)row * g.C);
-                        round_store<T, MAXCH>(acc, lane, nchunks, comp + (size_t)row * g.C);
-                    }
-                }
-            }
+            for (int j = 0; j < RG; ++j) add_row<T, MAXCH>(acc, rows.raw[j], lane, nchunks);
         }
-        if (p < step - 1) __syncthreads();
+        float* slot = part + (size_t)(w * 2 + dx) * g.C;
+#pragma unroll
+        for (int ch = 0; ch < MAXCH; ++ch) {
+            const int chunk = lane + 32 * ch;
+            if (chunk < nchunks)
+#pragma unroll
+                for (int i = 0; i < VN; ++i) slot[chunk * VN + i] = acc[ch][i];
+        }
+    }
+    __syncthreads();
+    // step 2: warp w finishes patch (dy = w / 2, dx = w % 2); step 4: warp 0 finishes the patch
+    if (step == 4 && w != 0) return;
+    const int dy = (step == 2) ? (w >> 1) : 0;
+    const int dx = (step == 2) ? (w & 1) : 0;
+    float acc[MAXCH][VN];
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch)
+#pragma unroll
+        for (int i = 0; i < VN; ++i) acc[ch][i] = 0.f;
+    for (int p = 0; p < step; ++p) {
+        const float* slot = part + (size_t)((dy * step + p) * 2 + dx) * g.C;
+#pragma unroll
+        for (int ch = 0; ch < MAXCH; ++ch) {
+            const int chunk = lane + 32 * ch;
+            if (chunk < nchunks)
+#pragma unroll
+                for (int i = 0; i < VN; ++i) acc[ch][i] += slot[chunk * VN + i];
+        }
+    }
+    const float denom = (float)(step * step);
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch)
+#pragma unroll
+        for (int i = 0; i < VN; ++i) acc[ch][i] = acc[ch][i] / denom;
+    const int row = first + dy * s + dx;
+    if (STATS) {
+        round_store<T, MAXCH>(acc, lane, nchunks, comp + (size_t)row * g.C);
+        const float2 st = row_stats_1pass<MAXCH, VN>(acc, lane, nchunks, g.C, eps);
+        if (lane == 0) { stats_q[row] = st; stats_acc[row] = make_float2(0.f, 0.f); }
+    } else {
+        ln_store<T, MAXCH>(acc, lane, nchunks, g.C, lnw, lnb, eps, qn + (size_t)row * g.C);
+        round_store<T, MAXCH>(acc, lane, nchunks, comp + (size_t)row * g.C);
     }
 }
+
+template <typename T, int MAXCH>
+__device__ __forceinline__ void gate_from_row_sums(const float* part, int C, int lane, int nchunks,
+                                                   const float* __restrict__ gw, const float* __restrict__ gb, int S,
+                                                   float* __restrict__ logits_out, int32_t* __restrict__ idx_out,
+                                                   int rid);
 
 // ----------------------------------------------------------------------------- unpool
 // out[b,tok] = ref[b,tok] + (q[p] - comp[p]) for the patch p that covers the token.
@@ -269,8 +291,9 @@ template <typename T, int MAXCH>
 __global__ void __launch_bounds__(128)
 unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const T* ref, T* out, RegionGeom g,
                      const int32_t* __restrict__ idx, const int32_t* __restrict__ region_first,
-                     const int32_t* __restrict__ offsets, Splits sp) {
+                     const int32_t* __restrict__ offsets, Splits sp, NextBlock nx) {
     constexpr int VN = Vec<T>::N;
+    extern __shared__ float part[];          // [4 grid rows][C] row sums of the output (next block's gate)
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int nchunks = g.C / VN;
     const int R = g.Hr * g.Wr;
@@ -282,6 +305,7 @@ unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const 
         const int b = e / g.num_extra, t = e % g.num_extra;
         const size_t tok = (size_t)b * g.N + t;
         const size_t p = (size_t)(__ldg(offsets + b) + t);
+        float e1 = 0.f, e2 = 0.f;
 #pragma unroll
         for (int ch = 0; ch < MAXCH; ++ch) {
             const int chunk = lane + 32 * ch;
@@ -296,7 +320,21 @@ unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const 
                 for (int i = 0; i < VN; ++i) rf[i] = (qf[i] - cf[i]) + rf[i];
                 rv.from_float(rf);
                 rv.store(out + tok * g.C + chunk * VN);
+                if (nx.stats_x) {
+                    rv.to_float(rf);
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) { e1 += rf[i]; e2 = fmaf(rf[i], rf[i], e2); }
+                }
             }
+        }
+        if (nx.stats_x) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                e1 += __shfl_xor_sync(0xffffffffu, e1, o);
+                e2 += __shfl_xor_sync(0xffffffffu, e2, o);
+            }
+            const float mean = e1 / (float)g.C;
+            if (lane == 0) nx.stats_x[tok] = make_float2(mean, rsqrtf(fmaxf(e2 / (float)g.C - mean * mean, 0.f) + nx.eps));
         }
         return;
     }
@@ -309,12 +347,18 @@ unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const 
     const int first = __ldg(region_first + rid);
     const size_t tok0 = (size_t)b * g.N + g.num_extra + (size_t)(ry * RG + w) * g.W + rx * RG;
     const int prow = first + (w / step) * s;            // packed row of this grid row's first patch
+    float rowsum[MAXCH][VN];                            // sum of this grid row's four output tokens
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch)
+#pragma unroll
+        for (int i = 0; i < VN; ++i) rowsum[ch][i] = 0.f;
 
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         // two tokens per pass: their reference rows and the one or two patch rows they map to
         const int j0 = 2 * h;
         const int p0 = prow + j0 / step, p1 = prow + (j0 + 1) / step;
+        float s1a = 0.f, s2a = 0.f, s1b = 0.f, s2b = 0.f;
         Vec<T> r0[MAXCH], r1[MAXCH], q0[MAXCH], c0[MAXCH], q1[MAXCH], c1[MAXCH];
 #pragma unroll
         for (int ch = 0; ch < MAXCH; ++ch) {
@@ -352,59 +396,76 @@ unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const 
                 Vec<T> o;
                 o.from_float(a);
                 o.store(out + (tok0 + j0) * g.C + chunk * VN);
+                if (nx.stats_x) {
+                    o.to_float(a);                      // the rounded values the next block will read
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) { s1a += a[i]; s2a = fmaf(a[i], a[i], s2a); rowsum[ch][i] += a[i]; }
+                }
                 r1[ch].to_float(a);
 #pragma unroll
                 for (int i = 0; i < VN; ++i) a[i] = d1[i] + a[i];
                 o.from_float(a);
                 o.store(out + (tok0 + j0 + 1) * g.C + chunk * VN);
-            }
-        }
-    }
-}
-
-// ------------------------------------------------------------------------ router gate
-// Region mean of the raw tokens (sum in (dy, dx) order, then / 16), n_splits fp32 dot
-// products, argmax with the lowest index winning ties.
-template <typename T, int MAXCH>
-__global__ void __launch_bounds__(128)
-gate_region_kernel(const T* __restrict__ x, RegionGeom g, const float* __restrict__ gw,
-                   const float* __restrict__ gb, int S, float* __restrict__ logits_out,
-                   int32_t* __restrict__ idx_out) {
-    constexpr int VN = Vec<T>::N;
-    extern __shared__ float part[];          // [C]
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int nchunks = g.C / VN;
-    const int R = g.Hr * g.Wr;
-    const int rid = blockIdx.x;
-    const int b = rid / R, rr = rid % R;
-    const int ry = rr / g.Wr, rx = rr % g.Wr;
-    const size_t tok0 = (size_t)b * g.N + g.num_extra + (size_t)(ry * RG + w) * g.W + rx * RG;
-    Rows4<T, MAXCH> rows;
-    rows.load(x + tok0 * g.C, g.C, lane, nchunks);
-    float acc[MAXCH][VN];
-    for (int p = 0; p < RG; ++p) {
-        if (w == p) {
+                if (nx.stats_x) {
+                    o.to_float(a);
 #pragma unroll
-            for (int ch = 0; ch < MAXCH; ++ch) {
-                const int chunk = lane + 32 * ch;
-#pragma unroll
-                for (int i = 0; i < VN; ++i) acc[ch][i] = (p > 0 && chunk < nchunks) ? part[chunk * VN + i] : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < RG; ++j) add_row<T, MAXCH>(acc, rows.raw[j], lane, nchunks);
-            if (p < RG - 1) {
-#pragma unroll
-                for (int ch = 0; ch < MAXCH; ++ch) {
-                    const int chunk = lane + 32 * ch;
-                    if (chunk < nchunks)
-#pragma unroll
-                        for (int i = 0; i < VN; ++i) part[chunk * VN + i] = acc[ch][i];
+                    for (int i = 0; i < VN; ++i) { s1b += a[i]; s2b = fmaf(a[i], a[i], s2b); rowsum[ch][i] += a[i]; }
                 }
             }
         }
-        if (p < RG - 1) __syncthreads();
+        if (nx.stats_x) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                s1a += __shfl_xor_sync(0xffffffffu, s1a, o);
+                s2a += __shfl_xor_sync(0xffffffffu, s2a, o);
+                s1b += __shfl_xor_sync(0xffffffffu, s1b, o);
+                s2b += __shfl_xor_sync(0xffffffffu, s2b, o);
+            }
+            if (lane < 2) {
+                const float e1 = lane == 0 ? s1a : s1b, e2 = lane == 0 ? s2a : s2b;
+                const float mean = e1 / (float)g.C;
+                nx.stats_x[tok0 + j0 + lane] = make_float2(mean, rsqrtf(fmaxf(e2 / (float)g.C - mean * mean, 0.f) + nx.eps));
+            }
+        }
     }
-    if (w != RG - 1) return;
+    if (!nx.gw) return;
+    // ---- the next block's router gate on the region this CTA has just written
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch) {
+        const int chunk = lane + 32 * ch;
+        if (chunk < nchunks)
+#pragma unroll
+            for (int i = 0; i < VN; ++i) part[(size_t)w * g.C + chunk * VN + i] = rowsum[ch][i];
+    }
+    __syncthreads();
+    if (w != 0) return;
+    gate_from_row_sums<T, MAXCH>(part, g.C, lane, nchunks, nx.gw, nx.gb, nx.S, nx.logits, nx.idx, rid);
+}
+
+// ------------------------------------------------------------------------ router gate
+// Region mean of the raw tokens (each grid row summed in order, rows added top to bottom,
+// then / 16), n_splits fp32 dot products, argmax with the lowest index winning ties.
+// `part` holds the four grid-row sums [4][C]; executed by one warp.
+template <typename T, int MAXCH>
+__device__ __forceinline__ void gate_from_row_sums(const float* part, int C, int lane, int nchunks,
+                                                   const float* __restrict__ gw, const float* __restrict__ gb, int S,
+                                                   float* __restrict__ logits_out, int32_t* __restrict__ idx_out,
+                                                   int rid) {
+    constexpr int VN = Vec<T>::N;
+    float acc[MAXCH][VN];
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch)
+#pragma unroll
+        for (int i = 0; i < VN; ++i) acc[ch][i] = 0.f;
+    for (int p = 0; p < RG; ++p) {
+#pragma unroll
+        for (int ch = 0; ch < MAXCH; ++ch) {
+            const int chunk = lane + 32 * ch;
+            if (chunk < nchunks)
+#pragma unroll
+                for (int i = 0; i < VN; ++i) acc[ch][i] += part[(size_t)p * C + chunk * VN + i];
+        }
+    }
     const float denom = (float)(RG * RG);
     float best = 0.f;
     int best_i = 0;
@@ -414,7 +475,7 @@ gate_region_kernel(const T* __restrict__ x, RegionGeom g, const float* __restric
         for (int ch = 0; ch < MAXCH; ++ch) {
             const int chunk = lane + 32 * ch;
             if (chunk < nchunks) {
-                const float4* wp = reinterpret_cast<const float4*>(gw + (size_t)sI * g.C + chunk * VN);
+                const float4* wp = reinterpret_cast<const float4*>(gw + (size_t)sI * C + chunk * VN);
 #pragma unroll
                 for (int i4 = 0; i4 < VN / 4; ++i4) {
                     const float4 w4 = __ldg(wp + i4);
@@ -432,36 +493,97 @@ gate_region_kernel(const T* __restrict__ x, RegionGeom g, const float* __restric
     if (lane == 0) idx_out[rid] = best_i;
 }
 
+// Stand-alone gate (first block of a model, or a block called on its own); optionally also
+// writes the LayerNorm statistics of every token row it reads.
+template <typename T, int MAXCH>
+__global__ void __launch_bounds__(128)
+gate_region_kernel(const T* __restrict__ x, RegionGeom g, const float* __restrict__ gw,
+                   const float* __restrict__ gb, int S, float* __restrict__ logits_out,
+                   int32_t* __restrict__ idx_out, float2* __restrict__ stats_x, float eps) {
+    constexpr int VN = Vec<T>::N;
+    extern __shared__ float part[];          // [4][C]
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int nchunks = g.C / VN;
+    const int R = g.Hr * g.Wr;
+    const int rid = blockIdx.x;
+    if (rid >= g.B * R) {
+        // extra (cls) tokens only matter for the statistics
+        const int e = (rid - g.B * R) * RG + w;
+        if (!stats_x || e >= g.B * g.num_extra) return;
+        const size_t tok = (size_t)(e / g.num_extra) * g.N + e % g.num_extra;
+        Vec<T> row[MAXCH];
+#pragma unroll
+        for (int ch = 0; ch < MAXCH; ++ch)
+            if (lane + 32 * ch < nchunks) row[ch].load(x + tok * g.C + (lane + 32 * ch) * VN);
+        float f[MAXCH][VN];
+        row_to_float<T, MAXCH>(f, row, lane, nchunks);
+        const float2 st = row_stats_1pass<MAXCH, VN>(f, lane, nchunks, g.C, eps);
+        if (lane == 0) stats_x[tok] = st;
+        return;
+    }
+    const int b = rid / R, rr = rid % R;
+    const int ry = rr / g.Wr, rx = rr % g.Wr;
+    const size_t tok0 = (size_t)b * g.N + g.num_extra + (size_t)(ry * RG + w) * g.W + rx * RG;
+    Rows4<T, MAXCH> rows;
+    rows.load(x + tok0 * g.C, g.C, lane, nchunks);
+    float acc[MAXCH][VN];
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch)
+#pragma unroll
+        for (int i = 0; i < VN; ++i) acc[ch][i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < RG; ++j) {
+        add_row<T, MAXCH>(acc, rows.raw[j], lane, nchunks);
+        if (stats_x) {
+            float f[MAXCH][VN];
+            row_to_float<T, MAXCH>(f, rows.raw[j], lane, nchunks);
+            const float2 st = row_stats_1pass<MAXCH, VN>(f, lane, nchunks, g.C, eps);
+            if (lane == 0) stats_x[tok0 + j] = st;
+        }
+    }
+#pragma unroll
+    for (int ch = 0; ch < MAXCH; ++ch) {
+        const int chunk = lane + 32 * ch;
+        if (chunk < nchunks)
+#pragma unroll
+            for (int i = 0; i < VN; ++i) part[(size_t)w * g.C + chunk * VN + i] = acc[ch][i];
+    }
+    __syncthreads();
+    if (w != 0) return;
+    gate_from_row_sums<T, MAXCH>(part, g.C, lane, nchunks, gw, gb, S, logits_out, idx_out, rid);
+}
+
 // ------------------------------------------------------------------------------- host
 
 template <typename T, int MAXCH>
 static void launch_pool_t(const RegionPoolArgs& a, cudaStream_t st) {
     const int R = a.g.Hr * a.g.Wr;
     const int grid = a.g.B * R + ceil_div(a.g.B * a.g.num_extra, RG);
-    const size_t smem = (size_t)4 * a.g.C * sizeof(float);
-    if (a.stats_x)
+    const size_t smem = (size_t)8 * a.g.C * sizeof(float);
+    if (a.stats_q)
         pool_region_kernel<T, MAXCH, true><<<grid, 128, smem, st>>>(
             (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.sp, (T*)a.comp, a.stats_x, a.stats_q, a.stats_acc,
-            nullptr, nullptr, a.eps, nullptr, nullptr);
+            a.stats_x_ready ? 0 : 1, nullptr, nullptr, a.eps, nullptr, nullptr);
     else
         pool_region_kernel<T, MAXCH, false><<<grid, 128, smem, st>>>(
-            (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.sp, (T*)a.comp, nullptr, nullptr, nullptr, a.lnw,
-            a.lnb, a.eps, (T*)a.xn, (T*)a.qn);
+            (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.sp, (T*)a.comp, nullptr, nullptr, nullptr, 0,
+            a.lnw, a.lnb, a.eps, (T*)a.xn, (T*)a.qn);
 }
 
 template <typename T, int MAXCH>
 static void launch_unpool_t(const RegionUnpoolArgs& a, cudaStream_t st) {
     const int R = a.g.Hr * a.g.Wr;
     const int grid = a.g.B * R + ceil_div(a.g.B * a.g.num_extra, RG);
-    unpool_region_kernel<T, MAXCH><<<grid, 128, 0, st>>>((const T*)a.q, (const T*)a.comp, (const T*)a.ref, (T*)a.out, a.g,
-                                                         a.idx, a.region_first, a.offsets, a.sp);
+    unpool_region_kernel<T, MAXCH><<<grid, 128, (size_t)4 * a.g.C * sizeof(float), st>>>(
+        (const T*)a.q, (const T*)a.comp, (const T*)a.ref, (T*)a.out, a.g, a.idx, a.region_first, a.offsets, a.sp, a.next);
 }
 
 template <typename T, int MAXCH>
 static void launch_gate_t(const RegionGateArgs& a, cudaStream_t st) {
     const int R = a.g.Hr * a.g.Wr;
-    gate_region_kernel<T, MAXCH><<<a.g.B * R, 128, (size_t)a.g.C * sizeof(float), st>>>(
-        (const T*)a.x, a.g, a.gw, a.gb, a.S, a.logits_out, a.idx_out);
+    const int grid = a.g.B * R + (a.stats_x ? ceil_div(a.g.B * a.g.num_extra, RG) : 0);
+    gate_region_kernel<T, MAXCH><<<grid, 128, (size_t)4 * a.g.C * sizeof(float), st>>>(
+        (const T*)a.x, a.g, a.gw, a.gb, a.S, a.logits_out, a.idx_out, a.stats_x, a.eps);
 }
 
 #define VTP_DISPATCH_MAXCH(FN, T, ARGS, ST)                      \

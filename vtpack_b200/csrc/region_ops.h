@@ -24,14 +24,24 @@ struct RegionPoolArgs {
     // LayerNorm applied later, in a GEMM epilogue: per-row (mean, rstd) of x and of comp, and a
     // per-query accumulator to clear.  Leave null for explicit LayerNorm rows instead.
     float2* stats_x = nullptr; float2* stats_q = nullptr; float2* stats_acc = nullptr;
+    bool stats_x_ready = false;              // stats_x was already written (by the previous block's unpool)
     const float* lnw = nullptr; const float* lnb = nullptr; float eps = 1e-6f;
     void* xn = nullptr; void* qn = nullptr;
+};
+
+// What the unpool kernel can prepare for the block that follows, from the rows it has just
+// written: their LayerNorm statistics and the next router gate's decisions.
+struct NextBlock {
+    float2* stats_x = nullptr; float eps = 1e-6f;
+    const float* gw = nullptr; const float* gb = nullptr; int S = 0;
+    float* logits = nullptr; int32_t* idx = nullptr;
 };
 
 struct RegionUnpoolArgs {
     RegionGeom g; Splits sp;
     const void* q = nullptr; const void* comp = nullptr; const void* ref = nullptr; void* out = nullptr;
     const int32_t* idx = nullptr; const int32_t* region_first = nullptr; const int32_t* offsets = nullptr;
+    NextBlock next;
 };
 
 struct RegionGateArgs {
@@ -39,6 +49,7 @@ struct RegionGateArgs {
     const void* x = nullptr;
     const float* gw = nullptr; const float* gb = nullptr; int S = 0;
     float* logits_out = nullptr; int32_t* idx_out = nullptr;
+    float2* stats_x = nullptr; float eps = 1e-6f;     // optional: also the token rows' (mean, rstd)
 };
 
 bool region_ops_supported(const RegionGeom& g, int dtype);
