@@ -88,6 +88,34 @@ int vtp_index_to_patch(const void* indices, int idx_is_i64, const int* splits, i
                        int32_t* offsets, int32_t* patches, int64_t* patches64, void* stream);
 
 /*
+ * vtp_router_gate + vtp_index_to_patch in one call that needs no scratch from the caller.
+ * It has no counterpart in the reference.  It exists for hosts that can hand over input and
+ * output buffers but cannot allocate device memory themselves: a plugin inside an inference
+ * server that only receives its tensors, a host runtime in another language whose FFI can
+ * pass device pointers but has no CUDA allocator, or a real-time loop where cudaMalloc (which
+ * synchronises the device) is off limits.  The grain index of every region and the query
+ * count of every image are kept in a fixed array inside the library's device image instead:
+ *   - limits: B <= 4096 images and B*(H/region)*(W/region) <= 65536 regions; larger calls
+ *     return VTP_ERR_SHAPE and launch nothing;
+ *   - the array (278,528 bytes) occupies device memory on every GPU that loads the library
+ *     until the process exits;
+ *   - the first call on each device looks up the array's device address; make that first
+ *     call outside any stream capture;
+ *   - all calls share the array and it keeps the last call's contents.  Nothing in it needs
+ *     clearing (every entry is written before it is read), but two calls whose kernels can
+ *     run at the same time (different streams, different host threads) race on it: order
+ *     them on one stream or with events;
+ *   - no cudaMalloc / cudaFree or other allocating call is made.
+ * Inputs and outputs as in vtp_router_gate / vtp_index_to_patch: x [B, num_extra+H*W, C],
+ * gate_w/gate_b fp32, splits a HOST array; offsets int32 [B+1] and patches int32 [L_max,4]
+ * (L_max = B*(num_extra+H*W)) are written.
+ */
+int vtp_gate_compact_static(const void* x, int dtype, int B, int H, int W, int C, int num_extra,
+                            int region, const float* gate_w, const float* gate_b,
+                            const int* splits, int n_splits, int32_t* offsets, int32_t* patches,
+                            void* stream);
+
+/*
  * Multi-grain average pooling, optionally fused with the two LayerNorms that follow it.
  * Replaces grained_sample_compress (grained_sample.cu:198-239, kernel :31-69) and, when
  * ln_w != null, norm1(x) and norm1(q) (vtpack/models/dge/deit_dge.py:127).

@@ -45,6 +45,8 @@ PROTOTYPES = {
     "vtp_gate_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "vtp_index_to_patch": (c_int, [c_void_p, c_int, C.POINTER(c_int), c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "vtp_gate_compact_static": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                        c_void_p, C.POINTER(c_int), c_int, c_void_p, c_void_p, c_void_p]),
     "vtp_pool": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                          c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p]),
     "vtp_unpool_add": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
