@@ -201,6 +201,9 @@ def main():
     ap.add_argument("--cpu-batch", type=int, default=8, help="images per step of the CPU arm")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
     ap.add_argument("--cuda-cores", action="store_true", help="bf16: CUDA-core GEMM/attention instead of tcgen05")
+    ap.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a CUDA graph")
+    ap.add_argument("--host-image-dtype", default="bf16", choices=["bf16", "f32"],
+                    help="element type of the pinned host images of the end-to-end leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-stage-profile", action="store_true")
     args = ap.parse_args()
@@ -226,8 +229,13 @@ def main():
     logits = torch.empty(B, 1000, device=device)
     gathered = torch.empty(world * B, 1000, device=device) if world > 1 else None
 
+    use_graph = not args.no_graph
+
     def step():
-        model(img_dev, logits_out=logits)
+        if use_graph:
+            model.forward_graph(img_dev, logits)
+        else:
+            model(img_dev, logits_out=logits)
         if world > 1:
             dist.all_gather_into_tensor(gathered, logits)
 
@@ -256,8 +264,9 @@ def main():
     value = world * B * args.steps / (ms_total * 1e-3)
 
     # end to end: pinned host images -> device -> forward -> (gather) -> host logits, copies overlapped
-    pipe = HostPipeline(model, B, 256, device, world=world)
-    host = [synthetic.images(B, 256, seed=100 + rank + 7 * i, pin=True) for i in range(2)]
+    host_dt = torch.bfloat16 if (args.host_image_dtype == "bf16" and dtype == torch.bfloat16) else torch.float32
+    pipe = HostPipeline(model, B, 256, device, world=world, image_dtype=host_dt, use_graph=use_graph)
+    host = [synthetic.images(B, 256, seed=100 + rank + 7 * i).to(host_dt).pin_memory() for i in range(2)]
     batches = [host[i & 1] for i in range(args.steps)]
     pipe.run(batches[:max(args.warmup, 3)])
     barrier()
@@ -283,7 +292,8 @@ def main():
             "config": {"workload": f"DeiT-{args.model}+DGE s124 (budget 0.5 stand-in: free-running random-init gate) "
                                    f"256px eval forward, batch {B}/GPU, logits all-gathered",
                        "batch_per_gpu": B, "global_batch": B * world, "parallelism": f"dp{world}",
-                       "l2": "inputs larger than L2 (fp32 images 201 MB/step at B=256)"},
+                       "l2": "inputs larger than L2 (fp32 images 201 MB/step at B=256)",
+                       "cuda_graph": use_graph, "e2e_host_images": str(host_dt).replace("torch.", "")},
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": pipe.h2d_bytes,
                     "d2h_bytes_per_step": pipe.d2h_bytes},
             # per forward: im2col, cls rows, patch-embed GEMM, final LayerNorm, head GEMM, first block's gate,

@@ -194,12 +194,12 @@ int vtp_sparse_attention(const void* q, long long q_row_stride, long long q_head
                          void* stream);
 
 /*
- * Patch embedding front end: images fp32 [B,3,S,S] -> im2col rows [B*(S/P)^2, 3*P*P] in
+ * Patch embedding front end: images [B,3,S,S] (fp32 or bf16, image_dtype) -> im2col rows [B*(S/P)^2, 3*P*P] in
  * `dtype` (column = c*P*P + py*P + px, the flattening of the conv weight), and writes the
  * cls row x[b,0,:] = cls_token + pos_embed[0].  The GEMM itself is vtp_linear.
  * Replaces PatchEmbed + cls/pos add (vtpack/models/dge/deit_dge.py:268-275).
  */
-int vtp_patch_im2col(const float* images, int B, int S, int P, int dtype, void* cols,
+int vtp_patch_im2col(const void* images, int image_dtype, int B, int S, int P, int dtype, void* cols,
                      const void* cls_token, const void* pos_embed, int C, void* x,
                      void* stream);
 
@@ -278,17 +278,19 @@ typedef struct {
     const float* norm_w; const float* norm_b;
     const void* head_w; const float* head_b;    /* head [classes, C] */
     int depth, patch, img_size, num_classes;
+    int image_dtype;                            /* VTP_F32 or VTP_BF16: element type of the images */
 } vtp_model_weights;
 
 long long vtp_model_workspace_bytes(const vtp_dge_shape* s, const vtp_model_weights* m);
 
 /*
- * Eval forward of DeiT+DGE: images fp32 [B,3,S,S] (device) -> logits fp32 [B,classes].
+ * Eval forward of DeiT+DGE: images [B,3,S,S] (device; fp32, or bf16 when
+ * m->image_dtype = VTP_BF16) -> logits fp32 [B,classes].
  * counts_out int32 [depth,B] optional.
  * Replaces VisionTransformer.forward (vtpack/models/dge/deit_dge.py:267-299).
  */
 int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weights* m,
-                         const vtp_block_weights* blocks, const float* images, float* logits,
+                         const vtp_block_weights* blocks, const void* images, float* logits,
                          int32_t* counts_out, void* workspace, long long workspace_bytes,
                          void* stream);
 

@@ -32,7 +32,7 @@ class ModelWeights(C.Structure):
     _fields_ = [("patch_w", c_void_p), ("patch_b", c_void_p), ("cls_token", c_void_p),
                 ("pos_embed", c_void_p), ("norm_w", c_void_p), ("norm_b", c_void_p),
                 ("head_w", c_void_p), ("head_b", c_void_p), ("depth", c_int), ("patch", c_int),
-                ("img_size", c_int), ("num_classes", c_int)]
+                ("img_size", c_int), ("num_classes", c_int), ("image_dtype", c_int)]
 
 
 # name -> (restype, argtypes); every symbol include/vtpack_b200.h declares
@@ -60,7 +60,7 @@ PROTOTYPES = {
     "vtp_sparse_attention": (c_int, [c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_void_p,
                                      c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                      c_int, c_float, c_uint, c_void_p]),
-    "vtp_patch_im2col": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+    "vtp_patch_im2col": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                  c_int, c_void_p, c_void_p]),
     "vtp_block_workspace_bytes": (c_ll, [C.POINTER(DgeShape)]),
     "vtp_dge_block_forward": (c_int, [C.POINTER(DgeShape), C.POINTER(BlockWeights), c_void_p, c_void_p,

@@ -349,7 +349,7 @@ extern "C" long long vtp_model_workspace_bytes(const vtp_dge_shape* s, const vtp
 }
 
 extern "C" int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weights* m,
-                                    const vtp_block_weights* blocks, const float* images, float* logits,
+                                    const vtp_block_weights* blocks, const void* images, float* logits,
                                     int32_t* counts_out, void* workspace, long long workspace_bytes,
                                     void* stream) {
     if (int rc = check_shape(s)) return rc;
@@ -366,8 +366,8 @@ extern "C" int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weig
     const int HW = s->H * s->W, N = HW + 1, C = s->C;
     const int KP = 3 * m->patch * m->patch;
     const long long e = (long long)elem_size(s->dtype);
-    int rc = vtp_patch_im2col(images, s->B, m->img_size, m->patch, s->dtype, ms.cols, m->cls_token, m->pos_embed,
-                              C, ms.x, st);
+    int rc = vtp_patch_im2col(images, m->image_dtype, s->B, m->img_size, m->patch, s->dtype, ms.cols, m->cls_token,
+                              m->pos_embed, C, ms.x, st);
     if (rc) return rc;
     LinearArgs pe;   // token (b, 1+t) = cols(b,t) Wp^T + bias + pos_embed[1+t]
     pe.a = ms.cols; pe.lda = KP; pe.w = m->patch_w; pe.bias = m->patch_b; pe.res = m->pos_embed; pe.ldr = C;

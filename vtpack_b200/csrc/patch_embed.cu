@@ -10,9 +10,21 @@ namespace vtp {
 
 // One thread moves 8 horizontally adjacent pixels: two coalesced float4 loads, one
 // 16-byte (bf16) or two 16-byte (fp32) stores.
-template <typename T>
+// 8 consecutive pixels as floats, from fp32 or bf16 images
+__device__ __forceinline__ void load8(const float* p, float* f) {
+    const float4 v0 = __ldg(reinterpret_cast<const float4*>(p));
+    const float4 v1 = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    f[0] = v0.x; f[1] = v0.y; f[2] = v0.z; f[3] = v0.w; f[4] = v1.x; f[5] = v1.y; f[6] = v1.z; f[7] = v1.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float* f) {
+    Vec<bf16> v;
+    v.raw = __ldg(reinterpret_cast<const uint4*>(p));
+    v.to_float(f);
+}
+
+template <typename I, typename T>
 __global__ void __launch_bounds__(256)
-im2col_kernel(const float* __restrict__ img, long long total8, int S, int P, T* __restrict__ cols) {
+im2col_kernel(const I* __restrict__ img, long long total8, int S, int P, T* __restrict__ cols) {
     const int G = S / P;
     const int KP = 3 * P * P;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total8;
@@ -22,18 +34,17 @@ im2col_kernel(const float* __restrict__ img, long long total8, int S, int P, T* 
         const int iy = (int)((pix / S) % S);
         const int c = (int)((pix / ((long long)S * S)) % 3);
         const long long b = pix / ((long long)3 * S * S);
-        const float4 v0 = __ldg(reinterpret_cast<const float4*>(img + pix));
-        const float4 v1 = __ldg(reinterpret_cast<const float4*>(img + pix) + 1);
+        float f[8];
+        load8(img + pix, f);
         const int gy = iy / P, py = iy % P, gx = ix / P, px = ix % P;
-        const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
         T* dst = cols + ((b * G + gy) * G + gx) * KP + c * P * P + py * P + px;
         if (sizeof(T) == 2) {
             Vec<bf16> o;
             o.from_float(f);
             o.store(reinterpret_cast<bf16*>(dst));
         } else {
-            reinterpret_cast<float4*>(dst)[0] = v0;
-            reinterpret_cast<float4*>(dst)[1] = v1;
+            reinterpret_cast<float4*>(dst)[0] = make_float4(f[0], f[1], f[2], f[3]);
+            reinterpret_cast<float4*>(dst)[1] = make_float4(f[4], f[5], f[6], f[7]);
         }
     }
 }
@@ -50,10 +61,11 @@ __global__ void cls_row_kernel(const T* __restrict__ cls, const T* __restrict__ 
 
 using namespace vtp;
 
-extern "C" int vtp_patch_im2col(const float* images, int B, int S, int P, int dtype, void* cols,
+extern "C" int vtp_patch_im2col(const void* images, int image_dtype, int B, int S, int P, int dtype, void* cols,
                                 const void* cls_token, const void* pos_embed, int C, void* x, void* stream) {
     VTP_REQUIRE(images && cols, VTP_ERR_NULL, "im2col: null pointer");
     VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "im2col: dtype %d", dtype);
+    VTP_REQUIRE(image_dtype == VTP_F32 || image_dtype == VTP_BF16, VTP_ERR_DTYPE, "im2col: image dtype %d", image_dtype);
     VTP_REQUIRE(B > 0 && S > 0 && P > 0 && S % P == 0 && P % 8 == 0, VTP_ERR_SHAPE,
                 "im2col: image %d / patch %d (patch must be a multiple of 8)", S, P);
     VTP_REQUIRE(aligned16(images) && aligned16(cols), VTP_ERR_ALIGN, "im2col: unaligned pointer");
@@ -61,10 +73,14 @@ extern "C" int vtp_patch_im2col(const float* images, int B, int S, int P, int dt
     const long long total8 = (long long)B * 3 * S * S / 8;
     const int grid = (int)((total8 + 255) / 256 < (long long)sm_count() * 16 ? (total8 + 255) / 256
                                                                              : (long long)sm_count() * 16);
-    if (dtype == VTP_F32)
-        im2col_kernel<float><<<grid, 256, 0, st>>>(images, total8, S, P, (float*)cols);
+    if (image_dtype == VTP_F32 && dtype == VTP_F32)
+        im2col_kernel<float, float><<<grid, 256, 0, st>>>((const float*)images, total8, S, P, (float*)cols);
+    else if (image_dtype == VTP_F32)
+        im2col_kernel<float, bf16><<<grid, 256, 0, st>>>((const float*)images, total8, S, P, (bf16*)cols);
+    else if (dtype == VTP_F32)
+        im2col_kernel<bf16, float><<<grid, 256, 0, st>>>((const bf16*)images, total8, S, P, (float*)cols);
     else
-        im2col_kernel<bf16><<<grid, 256, 0, st>>>(images, total8, S, P, (bf16*)cols);
+        im2col_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)images, total8, S, P, (bf16*)cols);
     if (int rc = check_launch("im2col")) return rc;
     if (x) {
         VTP_REQUIRE(cls_token && pos_embed && C > 0, VTP_ERR_NULL, "im2col: cls row needs cls_token and pos_embed");

@@ -289,6 +289,7 @@ class VisionTransformer(nn.Module):
         self.flags = 0
         self.fold_layernorm = True
         self._pack = _WeightPack()
+        self._graphs = {}
         self.last_counts = None
         self._init_weights()
 
@@ -342,13 +343,21 @@ class VisionTransformer(nn.Module):
             pk.key, pk.tensors, pk.struct = key, t, (m, blocks)
         return pk.struct
 
+    def forward_graph(self, x, logits_out):
+        """forward() through a CUDA graph captured for these input / output buffers (contents
+        may change between calls, addresses and shapes may not)."""
+        return _graph_forward(self, x, logits_out)
+
     def forward(self, x, logits_out=None):
-        """images fp32 [B,3,S,S] on the device -> logits fp32 [B,num_classes]
-        (``deit_dge.py:267-299``) in one C-ABI call."""
+        """images [B,3,S,S] on the device (fp32, or bf16 to halve the host-to-device copy of
+        a bf16 model: the kernel rounds fp32 pixels to bf16 anyway) -> logits fp32
+        [B,num_classes] (``deit_dge.py:267-299``) in one C-ABI call."""
         if self.training:
             raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
         require_cuda(x)
-        x = x.float().contiguous()
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.float()
+        x = x.contiguous()
         B = x.shape[0]
         dtype = self.compute_dtype()
         G = self.img_size // self.patch_size
@@ -356,6 +365,7 @@ class VisionTransformer(nn.Module):
         s = _shape_struct(dtype, B, G, G, 1, self.embed_dim, blk0.attn.num_heads, blk0.mlp.fc1.out_features,
                           self.split_sizes, self.norm.eps, self.flags)
         m, blocks = self._pack_model(dtype)
+        m.image_dtype = dtype_code(x.dtype)
         lib = _lib.lib()
         nbytes = lib.vtp_model_workspace_bytes(ctypes.byref(s), ctypes.byref(m))
         ws = scratch(x.device, nbytes)
@@ -366,6 +376,28 @@ class VisionTransformer(nn.Module):
                                             ptr(counts), ptr(ws), nbytes, stream_ptr(x.device)))
         self.last_counts = counts
         return logits
+
+
+def _graph_forward(model, x, logits_out):
+    """Replay (capturing on first use) a CUDA graph of model.forward(x, logits_out) for these
+    exact buffers: removes per-launch host work and shortens the gaps between kernels."""
+    key = (x.data_ptr(), tuple(x.shape), x.dtype, logits_out.data_ptr())
+    g = model._graphs.get(key)
+    if g is None:
+        cur = torch.cuda.current_stream(x.device)
+        side = torch.cuda.Stream(x.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):          # warm-up outside capture: scratch, attributes, weight packs
+            for _ in range(2):
+                model.forward(x, logits_out)
+        cur.wait_stream(side)
+        torch.cuda.synchronize(x.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            model.forward(x, logits_out)
+        model._graphs[key] = g
+    g.replay()
+    return logits_out
 
 
 def _make(embed_dim, num_heads, **kwargs):
