@@ -23,7 +23,7 @@ struct Carver {
 };
 
 struct BlockScratch {
-    int32_t *idx[2], *counts, *offsets, *patches, *region_first;   // idx / logits / stats_x: this block's and the
+    int32_t *idx[2], *counts[2], *offsets, *patches, *region_first; // idx / counts / logits / stats_x: this block's and the
     float* logits[2];                                              // next block's (written by this block's unpool)
     float2 *stats_x[2], *stats_q, *stats_acc;
     void *comp, *xn, *qn, *qp, *kv, *ao, *q1, *hid;
@@ -39,7 +39,8 @@ static BlockScratch carve_block(const vtp_dge_shape& s, void* ws) {
     BlockScratch b;
     b.idx[0] = (int32_t*)c.take((long long)s.B * R * 4);
     b.idx[1] = (int32_t*)c.take((long long)s.B * R * 4);
-    b.counts = (int32_t*)c.take((long long)s.B * 4);
+    b.counts[0] = (int32_t*)c.take((long long)s.B * 4);
+    b.counts[1] = (int32_t*)c.take((long long)s.B * 4);
     b.offsets = (int32_t*)c.take((long long)(s.B + 1) * 4);
     b.patches = (int32_t*)c.take(rows * 16);
     b.region_first = (int32_t*)c.take((long long)s.B * R * 4);
@@ -86,6 +87,11 @@ struct StageMarks {
     }
 };
 
+__global__ void fill_i32_kernel(int32_t* p, int n, int v) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
 static bool has_folded_weights(const vtp_block_weights& w) {
     return w.q_wf && w.q_s && w.q_c && w.kv_wf && w.kv_s && w.kv_c && w.fc1_wf && w.fc1_s && w.fc1_c;
 }
@@ -122,11 +128,15 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     const bool fold = by_region && s.dtype == VTP_BF16 && !kflag && has_folded_weights(w);
     const int par = chain.parity & 1;
     int32_t* idx = b.idx[par];
+    int32_t* counts = b.counts[par];
     float2* stats_x = b.stats_x[par];
     bool stats_x_ready = false;
+    // chained: gate decisions, per-image counts and token statistics came from the previous
+    // block's unpool; the pool kernel then also derives the row offsets itself
+    const bool chained = chain.have_gate && fold && !forced_logits;
 
-    if (chain.have_gate && fold && !forced_logits) {
-        stats_x_ready = true;          // gate decisions and token statistics came from the previous block's unpool
+    if (chained) {
+        stats_x_ready = true;
         rc = VTP_OK;
     } else if (forced_logits) {
         rc = vtp_gate_argmax(forced_logits, s.B * Hr * Wr, s.n_splits, idx, st);
@@ -141,17 +151,21 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
                              s.n_splits, b.logits[par], idx, st);
     }
     if (rc || (rc = marks.mark(1))) return rc;
-    rc = index_to_patch(idx, 0, sp, s.B, Hr, Wr, s.region, s.num_extra, b.counts, b.offsets,
-                        by_region ? nullptr : b.patches, nullptr, b.region_first, st);
+    if (!chained)
+        rc = index_to_patch(idx, 0, sp, s.B, Hr, Wr, s.region, s.num_extra, counts, b.offsets,
+                            by_region ? nullptr : b.patches, nullptr, b.region_first, st);
     if (rc || (rc = marks.mark(2))) return rc;
     if (counts_out) {
-        const cudaError_t e = cudaMemcpyAsync(counts_out, b.counts, (size_t)s.B * 4, cudaMemcpyDeviceToDevice, st);
+        const cudaError_t e = cudaMemcpyAsync(counts_out, counts, (size_t)s.B * 4, cudaMemcpyDeviceToDevice, st);
         if (e != cudaSuccess) return fail((int)e, "block: counts copy: %s", cudaGetErrorString(e));
     }
     if (by_region) {
         RegionPoolArgs pa;
-        pa.g = g; pa.sp = sp; pa.x = x_in; pa.idx = idx; pa.region_first = b.region_first; pa.offsets = b.offsets;
-        pa.comp = b.comp; pa.eps = s.eps;
+        pa.g = g; pa.sp = sp; pa.x = x_in; pa.idx = idx; pa.comp = b.comp; pa.eps = s.eps;
+        pa.region_first = chained ? nullptr : b.region_first;
+        pa.offsets = b.offsets; pa.counts = counts; pa.offsets_out = b.offsets; pa.region_first_out = b.region_first;
+        const bool will_chain = fold && chain.next && has_folded_weights(*chain.next);
+        pa.counts_next = (chained && will_chain) ? b.counts[par ^ 1] : nullptr;
         if (fold) {
             pa.stats_x = stats_x; pa.stats_q = b.stats_q; pa.stats_acc = b.stats_acc;
             pa.stats_x_ready = stats_x_ready;
@@ -220,6 +234,12 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
             ua.next.stats_x = b.stats_x[par ^ 1]; ua.next.eps = s.eps;
             ua.next.gw = chain.next->gate_w; ua.next.gb = chain.next->gate_b; ua.next.S = s.n_splits;
             ua.next.logits = b.logits[par ^ 1]; ua.next.idx = b.idx[par ^ 1];
+            ua.next.counts = b.counts[par ^ 1];
+            if (!chained) {
+                // this block's pool did not reset the next block's counts: start them at the extra tokens
+                fill_i32_kernel<<<ceil_div(s.B, 256), 256, 0, st>>>(b.counts[par ^ 1], s.B, s.num_extra);
+                if ((rc = check_launch("counts reset"))) return rc;
+            }
         }
         rc = region_unpool(ua, s.dtype, st);
     } else {

@@ -27,6 +27,8 @@
 //
 // Replaces nn.Linear q/kv/proj/fc1/fc2/head, nn.GELU and the residual adds of
 // vtpack/models/dge/deit_dge.py:38-44,72-74,96,127-128 (cuBLAS + ATen kernels there).
+#include <stdlib.h>
+
 #include "linear.h"
 #include "runtime.h"
 #include "sm100.cuh"
@@ -520,6 +522,7 @@ int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
     int bn = 256;
     if (padded(192) < padded(bn)) bn = 192;
     if (padded(128) < padded(bn)) bn = 128;
+    if (getenv("VTP_BN")) bn = atoi(getenv("VTP_BN"));
     const bool f32 = (p.flags & VTP_FLAG_OUT_F32) != 0;
     if (bn == 256) return f32 ? launch_tc<256, 4, float>(p, st) : launch_tc<256, 4, bf16>(p, st);
     if (bn == 192) return f32 ? launch_tc<192, 4, float>(p, st) : launch_tc<192, 4, bf16>(p, st);

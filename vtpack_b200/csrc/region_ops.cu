@@ -133,7 +133,9 @@ __device__ __forceinline__ void round_store(float (&f)[MAXCH][Vec<T>::N], int la
 template <typename T, int MAXCH, bool STATS>
 __global__ void __launch_bounds__(128)
 pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restrict__ idx,
-                   const int32_t* __restrict__ region_first, const int32_t* __restrict__ offsets, Splits sp,
+                   const int32_t* __restrict__ region_first, const int32_t* __restrict__ offsets,
+                   const int32_t* __restrict__ counts, int32_t* __restrict__ offsets_out,
+                   int32_t* __restrict__ region_first_out, int32_t* __restrict__ counts_next, Splits sp,
                    T* __restrict__ comp, float2* __restrict__ stats_x, float2* __restrict__ stats_q,
                    float2* __restrict__ stats_acc, int write_stats_x, const float* __restrict__ lnw,
                    const float* __restrict__ lnb, float eps, T* __restrict__ xn, T* __restrict__ qn) {
@@ -150,7 +152,18 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
         if (e >= g.B * g.num_extra) return;
         const int b = e / g.num_extra, t = e % g.num_extra;
         const size_t src_row = (size_t)b * g.N + t;
-        const int dst_row = __ldg(offsets + b) + t;
+        int dst_row;
+        if (region_first) {
+            dst_row = __ldg(offsets + b) + t;
+        } else {
+            int part_sum = 0;
+            for (int j = lane; j < b; j += 32) part_sum += __ldg(counts + j);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) part_sum += __shfl_xor_sync(0xffffffffu, part_sum, o);
+            dst_row = part_sum + t;
+            // start the next block's per-image count at the extra tokens; its gate adds the rest
+            if (t == 0 && lane == 0 && counts_next) counts_next[b] = g.num_extra;
+        }
         Vec<T> row[MAXCH];
 #pragma unroll
         for (int ch = 0; ch < MAXCH; ++ch)
@@ -180,11 +193,38 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
     k = min(max(k, 0), sp.n - 1);
     const int s = sp.v[k];                     // sub-patches per region side: 4, 2 or 1
     const int step = RG / s;
-    const int first = __ldg(region_first + rid);
     const size_t tok0 = (size_t)b * g.N + g.num_extra + (size_t)(ry * RG + w) * g.W + rx * RG;
 
     Rows4<T, MAXCH> rows;
     rows.load(x + tok0 * g.C, g.C, lane, nchunks);
+
+    int first;
+    if (region_first) {
+        first = __ldg(region_first + rid);
+    } else {
+        // No patch-list kernel ran: this region's first packed row = queries of the images in
+        // front (per-image counts, accumulated by whoever computed the gate) + extra tokens +
+        // queries of this image's earlier regions.  Every warp computes it redundantly.
+        int part_sum = 0;
+        for (int j = lane; j < b; j += 32) part_sum += __ldg(counts + j);
+        int own = 0;
+        for (int r = lane; r < rr; r += 32) {
+            int kk = __ldg(idx + b * R + r);
+            kk = min(max(kk, 0), sp.n - 1);
+            own += sp.v[kk] * sp.v[kk];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            part_sum += __shfl_xor_sync(0xffffffffu, part_sum, o);
+            own += __shfl_xor_sync(0xffffffffu, own, o);
+        }
+        first = part_sum + g.num_extra + own;
+        if (w == 0 && lane == 0) region_first_out[rid] = first;
+        if (rr == 0 && w == 0 && lane == 0) {
+            offsets_out[b] = part_sum;
+            if (b == g.B - 1) offsets_out[g.B] = part_sum + __ldg(counts + b);
+        }
+    }
 
     // per-token LayerNorm statistics or rows
 #pragma unroll
@@ -283,7 +323,7 @@ template <typename T, int MAXCH>
 __device__ __forceinline__ void gate_from_row_sums(const float* part, int C, int lane, int nchunks,
                                                    const float* __restrict__ gw, const float* __restrict__ gb, int S,
                                                    float* __restrict__ logits_out, int32_t* __restrict__ idx_out,
-                                                   int rid);
+                                                   int rid, int32_t* counts_img, const Splits& sp);
 
 // ----------------------------------------------------------------------------- unpool
 // out[b,tok] = ref[b,tok] + (q[p] - comp[p]) for the patch p that covers the token.
@@ -439,7 +479,8 @@ unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const 
     }
     __syncthreads();
     if (w != 0) return;
-    gate_from_row_sums<T, MAXCH>(part, g.C, lane, nchunks, nx.gw, nx.gb, nx.S, nx.logits, nx.idx, rid);
+    gate_from_row_sums<T, MAXCH>(part, g.C, lane, nchunks, nx.gw, nx.gb, nx.S, nx.logits, nx.idx, rid,
+                                 nx.counts ? nx.counts + b : nullptr, sp);
 }
 
 // ------------------------------------------------------------------------ router gate
@@ -450,7 +491,7 @@ template <typename T, int MAXCH>
 __device__ __forceinline__ void gate_from_row_sums(const float* part, int C, int lane, int nchunks,
                                                    const float* __restrict__ gw, const float* __restrict__ gb, int S,
                                                    float* __restrict__ logits_out, int32_t* __restrict__ idx_out,
-                                                   int rid) {
+                                                   int rid, int32_t* counts_img, const Splits& sp) {
     constexpr int VN = Vec<T>::N;
     float acc[MAXCH][VN];
 #pragma unroll
@@ -490,7 +531,11 @@ __device__ __forceinline__ void gate_from_row_sums(const float* part, int C, int
         if (lane == 0 && logits_out) logits_out[(size_t)rid * S + sI] = pdot;
         if (sI == 0 || pdot > best) { best = pdot; best_i = sI; }
     }
-    if (lane == 0) idx_out[rid] = best_i;
+    if (lane == 0) {
+        idx_out[rid] = best_i;
+        // queries this region contributes to its image (the image's slot starts at num_extra)
+        if (counts_img) atomicAdd(counts_img, sp.v[min(best_i, sp.n - 1)] * sp.v[min(best_i, sp.n - 1)]);
+    }
 }
 
 // Stand-alone gate (first block of a model, or a block called on its own); optionally also
@@ -550,7 +595,9 @@ gate_region_kernel(const T* __restrict__ x, RegionGeom g, const float* __restric
     }
     __syncthreads();
     if (w != 0) return;
-    gate_from_row_sums<T, MAXCH>(part, g.C, lane, nchunks, gw, gb, S, logits_out, idx_out, rid);
+    Splits none;
+    none.n = 1; none.v[0] = 0;
+    gate_from_row_sums<T, MAXCH>(part, g.C, lane, nchunks, gw, gb, S, logits_out, idx_out, rid, nullptr, none);
 }
 
 // ------------------------------------------------------------------------------- host
@@ -562,12 +609,13 @@ static void launch_pool_t(const RegionPoolArgs& a, cudaStream_t st) {
     const size_t smem = (size_t)8 * a.g.C * sizeof(float);
     if (a.stats_q)
         pool_region_kernel<T, MAXCH, true><<<grid, 128, smem, st>>>(
-            (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.sp, (T*)a.comp, a.stats_x, a.stats_q, a.stats_acc,
-            a.stats_x_ready ? 0 : 1, nullptr, nullptr, a.eps, nullptr, nullptr);
+            (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.counts, a.offsets_out, a.region_first_out, a.counts_next, a.sp,
+            (T*)a.comp, a.stats_x, a.stats_q, a.stats_acc, a.stats_x_ready ? 0 : 1, nullptr, nullptr, a.eps, nullptr,
+            nullptr);
     else
         pool_region_kernel<T, MAXCH, false><<<grid, 128, smem, st>>>(
-            (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.sp, (T*)a.comp, nullptr, nullptr, nullptr, 0,
-            a.lnw, a.lnb, a.eps, (T*)a.xn, (T*)a.qn);
+            (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.counts, a.offsets_out, a.region_first_out, a.counts_next, a.sp,
+            (T*)a.comp, nullptr, nullptr, nullptr, 0, a.lnw, a.lnb, a.eps, (T*)a.xn, (T*)a.qn);
 }
 
 template <typename T, int MAXCH>

@@ -18,8 +18,13 @@ struct RegionPoolArgs {
     RegionGeom g; Splits sp;
     const void* x = nullptr;
     const int32_t* idx = nullptr;            // grain index per region
-    const int32_t* region_first = nullptr;   // packed row of each region's first query
-    const int32_t* offsets = nullptr;        // packed row of each image's first query
+    const int32_t* region_first = nullptr;   // packed row of each region's first query; null: derive it
+                                             //   in the kernel from `counts` and write `offsets_out`
+    const int32_t* offsets = nullptr;        // packed row of each image's first query (with region_first)
+    const int32_t* counts = nullptr;         // queries per image (without region_first)
+    int32_t* offsets_out = nullptr;          // [B+1], written when region_first is null
+    int32_t* region_first_out = nullptr;     // [B*R], written when region_first is null (for the unpool)
+    int32_t* counts_next = nullptr;          // [B], reset to num_extra for the next block's gate
     void* comp = nullptr;
     // LayerNorm applied later, in a GEMM epilogue: per-row (mean, rstd) of x and of comp, and a
     // per-query accumulator to clear.  Leave null for explicit LayerNorm rows instead.
@@ -35,6 +40,7 @@ struct NextBlock {
     float2* stats_x = nullptr; float eps = 1e-6f;
     const float* gw = nullptr; const float* gb = nullptr; int S = 0;
     float* logits = nullptr; int32_t* idx = nullptr;
+    int32_t* counts = nullptr;               // [B] per-image query counts, accumulated with atomics
 };
 
 struct RegionUnpoolArgs {
