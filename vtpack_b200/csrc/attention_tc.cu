@@ -66,8 +66,8 @@ __device__ __forceinline__ AttnItem attn_item(int w, int heads, int B, const int
     it.b = lo;
     it.h = w - tg * heads;
     const int t = tg - tile_prefix[lo];
-    it.row0 = __ldg(offsets + lo) + t * QT;
-    it.nq = min(QT, __ldg(offsets + lo + 1) - it.row0);
+    it.row0 = offsets[lo] + t * QT;
+    it.nq = min(QT, offsets[lo + 1] - it.row0);
     return it;
 }
 
@@ -77,7 +77,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                const bf16* __restrict__ vptr, long long q_hs, long long kv_bs, long long kv_rs, long long kv_hs,
                bf16* __restrict__ out, long long o_rs, long long o_hs, int B, int heads, int n_keys, int KC,
                int n_chunks, const int32_t* __restrict__ offsets, float scale_log2e, int* status) {
-    if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + SM_BAR);
@@ -98,6 +97,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    if (threadIdx.x == 32) {
+        for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_free[i], QT); }
+        mbar_init(k_full, 1); mbar_init(k_free, 1);
+        mbar_init(v_full, 1); mbar_init(v_free, 1);
+        mbar_init(s_full, 1); mbar_init(p_full, QT);
+        mbar_init(o_full, 1); mbar_init(o_free, QT);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, ATT_TMEM_COLS);
+        tmem_relinquish();
+    }
+    // Nothing above depends on the kernel in front of this one on the stream; the packed-row
+    // offsets, q, k and v below do.
+    griddep_launch();
+    griddep_wait();
     // tile_prefix[b] = number of 128-query tiles of the images in front of b (serial scan by
     // warp 0 in 32-image steps; B is a few hundred)
     if (warp == 0) {
@@ -105,7 +121,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int b0 = 0; b0 < B; b0 += 32) {
             const int b = b0 + lane;
             int tiles = 0;
-            if (b < B) tiles = (__ldg(offsets + b + 1) - __ldg(offsets + b) + QT - 1) / QT;
+            if (b < B) tiles = (offsets[b + 1] - offsets[b] + QT - 1) / QT;
             int incl = tiles;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -117,26 +133,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
         if (lane == 0) tile_prefix[B] = run;
     }
-    if (threadIdx.x == 32) {
-        for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_free[i], QT); }
-        mbar_init(k_full, 1); mbar_init(k_free, 1);
-        mbar_init(v_full, 1); mbar_init(v_free, 1);
-        mbar_init(s_full, 1); mbar_init(p_full, QT);
-        mbar_init(o_full, 1); mbar_init(o_free, QT);
-        *abort_flag = 0;
-        fence_barrier_init();
-    }
-    __syncthreads();
-    const int n_work = tile_prefix[B] * heads;
-    if ((int)blockIdx.x >= n_work) return;          // uniform: nothing allocated yet
-    if (warp == 0) {
-        tmem_alloc(tmem_slot, ATT_TMEM_COLS);
-        tmem_relinquish();
-    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    const bool void_launch = status && *reinterpret_cast<volatile int*>(status) != 0;
+    const int n_work = void_launch ? 0 : tile_prefix[B] * heads;
     const int n_main = (n_keys / 16) * 16;          // keys handled by the tensor cores
     const int tail = n_keys - n_main;               // 0..15 keys handled on CUDA cores
 
@@ -417,9 +419,15 @@ int attention_tcgen05(const AttnArgs& p, cudaStream_t st) {
     }
     const long long worst = (long long)p.B * ceil_div(p.max_q, QT) * p.heads;
     const int grid = (int)(worst < 2ll * sm_count() ? worst : 2ll * sm_count());
-    attn_tc_kernel<<<grid, 192, smem, st>>>(tq, tk, tv, (const bf16*)p.k, (const bf16*)p.v, p.q_hs, p.kv_bs, p.kv_rs,
-                                            p.kv_hs, (bf16*)p.out, p.o_rs, p.o_hs, p.B, p.heads, p.n_keys, KC, n_chunks,
-                                            p.offsets, p.scale * 1.4426950408889634f, device_status_ptr());
+    const cudaError_t le = launch_pdl(attn_tc_kernel, dim3(grid), dim3(192), (size_t)smem, st, tq, tk, tv,
+                                      (const bf16*)p.k, (const bf16*)p.v, p.q_hs, p.kv_bs, p.kv_rs, p.kv_hs, (bf16*)p.out,
+                                      p.o_rs, p.o_hs, p.B, p.heads, p.n_keys, KC, n_chunks, p.offsets,
+                                      p.scale * 1.4426950408889634f, device_status_ptr());
+    if (le != cudaSuccess) {
+        cudaGetLastError();
+        set_error("attention (tcgen05): %s", cudaGetErrorString(le));
+        return (int)le;
+    }
     return check_launch("attention (tcgen05)");
 }
 

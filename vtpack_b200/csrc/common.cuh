@@ -31,6 +31,28 @@ inline long long round_up(long long a, long long b) { return (a + b - 1) / b * b
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// True when the environment variable VTP_PDL is set.  Off by default: the tensor-core kernels
+// fill an SM's shared memory, so a dependent kernel cannot become resident early and the
+// overlap measured on B200 was nil.
+bool pdl_enabled();
+
+// Launch `kernel` so that it may overlap the tail of the previous kernel on the stream
+// (the kernel must call griddep_wait() before it touches that kernel's results).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---------------------------------------------------------------- device status word
 // Bounded waits OR one of these codes into the device status word (see runtime.h)
 // instead of hanging; vtp_device_status reads it back.
@@ -83,6 +105,14 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+
+// Programmatic dependent launch: a kernel launched with launch_pdl may start while the kernel
+// in front of it on the stream is still running.  griddep_wait() blocks until that kernel
+// has completed and its writes are visible: everything before it (barrier setup, TMEM
+// allocation, descriptor prefetch) overlaps the predecessor's tail.  griddep_launch() lets
+// the kernel behind this one begin its own prologue.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ float gelu_erf(float x) {
     return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));

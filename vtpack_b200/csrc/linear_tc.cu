@@ -95,14 +95,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  OutT* __restrict__ y, long long ldy, int m_max, const int32_t* __restrict__ m_dev, int N,
                  int K, unsigned flags, RowMap rm, LnFold ln, int* status) {
     using S = TcSmem<BN, STAGES>;
-    int M = m_max;
-    if (m_dev) M = min(__ldg(m_dev), m_max);
-    const int n_tiles = (N + BN - 1) / BN;
-    const int total = ((M + TBM - 1) / TBM) * n_tiles;
-    if ((int)blockIdx.x >= total) return;
-    // once any CTA has given up on a wait the launch is void: do not queue up more waits
-    if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
-
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = base;
@@ -143,6 +135,17 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+
+    // Everything above is independent of the kernel in front of this one on the stream; from
+    // here on its results (row count, operands, residual, statistics) are read.
+    griddep_launch();
+    griddep_wait();
+    int M = m_max;
+    if (m_dev) M = min(*reinterpret_cast<const volatile int32_t*>(m_dev), m_max);
+    const int n_tiles = (N + BN - 1) / BN;
+    // no tiles for this CTA, or an earlier CTA gave up on a wait (the launch is void): skip the work
+    const bool void_launch = status && *reinterpret_cast<volatile int*>(status) != 0;
+    const int total = void_launch ? 0 : ((M + TBM - 1) / TBM) * n_tiles;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -503,8 +506,13 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const RowMap rm{p.out_grp, p.out_skip, p.res_mod, p.res_off};
     const LnFold ln{p.ln_stats, p.ln_s, p.ln_mode, p.ln_dim, p.ln_eps, p.emit_stats};
-    kern<<<grid, TC_THREADS, S::TOTAL, st>>>(ta, tw, ty, tr, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
+    const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), (size_t)S::TOTAL, st, ta, tw, ty, tr, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
                                       p.m_dev, p.N, p.K, p.flags, rm, ln, device_status_ptr());
+    if (le != cudaSuccess) {
+        cudaGetLastError();
+        set_error("linear (tcgen05): %s", cudaGetErrorString(le));
+        return (int)le;
+    }
     return check_launch("linear (tcgen05)");
 }
 

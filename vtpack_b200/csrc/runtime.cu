@@ -1,6 +1,7 @@
 // Host-side runtime shared by the entry points: per-thread error text, launch checks,
 // device properties and the device status word of the bounded waits.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -44,6 +45,12 @@ int sm_count() {
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+bool pdl_enabled() {
+    static int cached = -1;
+    if (cached < 0) cached = getenv("VTP_PDL") ? 1 : 0;
+    return cached == 1;
 }
 
 __device__ int g_status_word = 0;
