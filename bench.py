@@ -190,6 +190,114 @@ def stage_profile(model, batch, device, iters, pk):
                         "kernel_weighted_roofline_frac": round(t_roof / (sum(ms) * 1e-3), 3)}
 
 
+def profile_case(which):
+    """A small, self-contained case of one kernel family (three launches) for `ncu`: inputs
+    larger than L2 but well under a GB, so a --set full capture ends within a minute or two."""
+    import ctypes
+    from vtpack_b200 import _lib, synthetic
+    lib = _lib.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if which == "linear_kv":            # the kv projection of DeiT-S at batch 256: M=65792, N=768, K=384
+        M, N, K = 65792, 768, 384
+        x = torch.randn(M, K, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+        b = torch.randn(N, device=dev)
+        y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        for _ in range(3):
+            _lib.check(lib.vtp_linear(x.data_ptr(), K, w.data_ptr(), b.data_ptr(), None, 0, y.data_ptr(), N, 1, M,
+                                      None, N, K, 0, None))
+    elif which == "attention":          # 256 images x 6 heads, 114 queries per image, 257 keys
+        B, N, h, Li, d = 256, 257, 6, 114, 64
+        C, L = h * d, B * Li
+        q = torch.randn(L, C, device=dev).bfloat16()
+        kv = torch.randn(B, N, 2 * C, device=dev).bfloat16()
+        out = torch.empty(L, C, device=dev, dtype=torch.bfloat16)
+        off = (torch.arange(B + 1, device=dev) * Li).int()
+        for _ in range(3):
+            _lib.check(lib.vtp_sparse_attention(q.data_ptr(), C, d, kv.data_ptr(), kv.data_ptr() + C * 2, N * 2 * C,
+                                                2 * C, d, out.data_ptr(), C, d, 1, B, N, h, d, off.data_ptr(), L, 257,
+                                                d ** -0.5, 0, None))
+    elif which == "block":              # one DeiT-S DGE block at batch 256 (gate, pool, GEMMs, attention, unpool)
+        model = synthetic.build_model("small", dev, torch.bfloat16, depth=2)
+        x = torch.randn(256, 257, 384, device=dev).bfloat16()
+        for _ in range(3):
+            model.blocks[0](x)
+    else:
+        raise SystemExit(f"unknown profile case {which}")
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+def _torch_dense_block(x, blk):
+    """The dense DeiT block as the reference runs it (vtpack/models/standard/deit.py:50-83):
+    PyTorch ops on the GPU, explicit softmax(q k^T) v."""
+    import torch.nn.functional as F
+    B, N, C = x.shape
+    h = blk.attn.num_heads
+    xn = F.layer_norm(x, (C,), blk.norm1.weight, blk.norm1.bias, blk.norm1.eps)
+    qkv_w = torch.cat([blk.attn.q.weight, blk.attn.kv.weight], 0)
+    qkv_b = torch.cat([blk.attn.q.bias, blk.attn.kv.bias], 0)
+    qkv = F.linear(xn, qkv_w, qkv_b).reshape(B, N, 3, h, C // h).permute(2, 0, 3, 1, 4)
+    attn = (qkv[0] @ qkv[1].transpose(-2, -1)) * blk.attn.scale
+    attn = attn.softmax(dim=-1)
+    y = (attn @ qkv[2]).transpose(1, 2).reshape(B, N, C)
+    x = x + F.linear(y, blk.attn.proj.weight, blk.attn.proj.bias)
+    hdn = F.gelu(F.linear(F.layer_norm(x, (C,), blk.norm2.weight, blk.norm2.bias, blk.norm2.eps),
+                          blk.mlp.fc1.weight, blk.mlp.fc1.bias))
+    return x + F.linear(hdn, blk.mlp.fc2.weight, blk.mlp.fc2.bias)
+
+
+def layer_sweep(args):
+    """BASELINE config 4: one DeiT-S DGE layer at batch 256, gate logits N(0,1) plus a bias on
+    the finest grain chosen by bisection so that the realised fraction of fine regions is
+    0 / 0.25 / 0.5 / 1; against the dense block (this library's kernels, and PyTorch ops)."""
+    from vtpack_b200 import _lib, synthetic
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    model = synthetic.build_model("small", dev, torch.bfloat16, depth=1)
+    blk = model.blocks[0]
+    B = args.batch
+    x = torch.randn(B, 257, 384, device=dev, generator=torch.Generator(dev).manual_seed(3)).bfloat16()
+    base = torch.randn(B, 4, 4, 3, generator=torch.Generator().manual_seed(2))
+
+    def timeit(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    rows = []
+    for frac in (0.0, 0.25, 0.5, 1.0):
+        lo, hi = -50.0, 50.0
+        for _ in range(60):                    # bisection on the bias of grain 0
+            mid = 0.5 * (lo + hi)
+            g = base.clone()
+            g[..., 0] += mid
+            f = float((g.argmax(-1) == 0).float().mean())
+            lo, hi = (mid, hi) if f < frac else (lo, mid)
+        g = base.clone()
+        g[..., 0] += hi if frac > 0 else -1e4
+        gate = g.to(dev)
+        us = timeit(lambda: blk(x, forced_gate=gate))
+        counts = blk.dge.states["batches_device"].float().mean().item()
+        rows.append({"fine_fraction": round(float((g.argmax(-1) == 0).float().mean()), 3),
+                     "queries_per_image": round(counts, 1), "dge_layer_us": round(us, 1)})
+    dense_us = timeit(lambda: blk(x, dense=True))
+    with torch.no_grad():
+        torch_us = timeit(lambda: _torch_dense_block(x, blk))
+    assert _lib.device_status() == 0
+    print(json.dumps({"layer_sweep": rows, "dense_block_us_this_library": round(dense_us, 1),
+                      "dense_block_us_pytorch_ops": round(torch_us, 1), "batch": B, "dtype": "bf16",
+                      "model": "DeiT-S layer, 16x16 grid, 16 regions"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -206,7 +314,17 @@ def main():
                     help="element type of the pinned host images of the end-to-end leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-stage-profile", action="store_true")
+    ap.add_argument("--profile", default=None, choices=["linear_kv", "attention", "block"],
+                    help="run a small case of one kernel family (for ncu) and exit")
+    ap.add_argument("--layer-sweep", action="store_true",
+                    help="time one DGE layer over gate skew against the dense block and exit")
     args = ap.parse_args()
+    if args.profile:
+        profile_case(args.profile)
+        return
+    if args.layer_sweep:
+        layer_sweep(args)
+        return
     if args.impl == "reference":
         run_reference(args)
         return

@@ -49,7 +49,7 @@ static BlockScratch carve_block(const vtp_dge_shape& s, void* ws) {
     b.stats_x[0] = (float2*)c.take(rows * 8);
     b.stats_x[1] = (float2*)c.take(rows * 8);
     b.stats_q = (float2*)c.take(rows * 8);
-    b.stats_acc = (float2*)c.take(rows * 8);
+    b.stats_acc = (float2*)c.take(rows * 8 * STAT_SLOTS);
     b.comp = c.take(rows * s.C * e);
     b.xn = c.take(rows * s.C * e);
     b.qn = c.take(rows * s.C * e);
@@ -167,7 +167,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
         const bool will_chain = fold && chain.next && has_folded_weights(*chain.next);
         pa.counts_next = (chained && will_chain) ? b.counts[par ^ 1] : nullptr;
         if (fold) {
-            pa.stats_x = stats_x; pa.stats_q = b.stats_q; pa.stats_acc = b.stats_acc;
+            pa.stats_x = stats_x; pa.stats_q = b.stats_q;
             pa.stats_x_ready = stats_x_ready;
         }
         else { pa.lnw = w.norm1_w; pa.lnb = w.norm1_b; pa.xn = b.xn; pa.qn = b.qn; }
@@ -216,7 +216,8 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     l1.a = fold ? b.q1 : b.qn; l1.lda = C; l1.w = fold ? w.fc1_wf : w.fc1_w; l1.bias = fold ? w.fc1_c : w.fc1_b;
     l1.y = b.hid; l1.ldy = s.hidden; l1.dtype = s.dtype; l1.m_max = rows; l1.m_dev = L_dev; l1.N = s.hidden; l1.K = C;
     l1.flags = kflag | VTP_FLAG_GELU;
-    if (fold) { l1.ln_mode = 2; l1.ln_stats = b.stats_acc; l1.ln_s = w.fc1_s; l1.ln_dim = C; l1.ln_eps = s.eps; }
+    if (fold) { l1.ln_mode = 2; l1.ln_stats = b.stats_acc; l1.ln_s = w.fc1_s; l1.ln_dim = C; l1.ln_eps = s.eps;
+                l1.ln_slots = linear_stat_slots(C); }
     if ((rc = linear(l1, st)) || (rc = marks.mark(9))) return rc;
 
     LinearArgs l2;   // q2 = q1 + hid W2^T + b   (into the q-projection buffer, dead by now)

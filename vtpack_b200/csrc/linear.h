@@ -25,16 +25,21 @@ struct LinearArgs {
     // LayerNorm folded into the GEMM (tcgen05 kernel only): `a` holds the raw rows, `w` holds
     // W*diag(gamma), ln_s[n] = sum_k w[n,k], bias[n] = sum_k beta[k] W[n,k] + b[n]; then
     //   LN(a) W^T + b = rstd[m] * (acc[m,n] - mean[m] * ln_s[n]) + bias[n].
-    // ln_mode 1: ln_stats[m] = (mean, rstd).  ln_mode 2: ln_stats[m] = (sum, sum of squares)
-    // over ln_dim elements, variance = E[x^2] - mean^2, rstd = rsqrt(var + ln_eps).
+    // ln_mode 1: ln_stats[m] = (mean, rstd).  ln_mode 2: ln_stats[m * STAT_SLOTS + i], i < ln_slots,
+    // are partial (sum, sum of squares) over ln_dim elements in total (written by the GEMM that
+    // produced the rows, see emit_stats); variance = E[x^2] - mean^2, rstd = rsqrt(var + ln_eps).
     const float2* ln_stats = nullptr; const float* ln_s = nullptr;
-    int ln_mode = 0, ln_dim = 0; float ln_eps = 0.f;
-    // When set, every stored row adds (sum, sum of squares) of its outputs here (atomics), the
-    // ln_mode 2 input of the next GEMM.
+    int ln_mode = 0, ln_dim = 0, ln_slots = 0; float ln_eps = 0.f;
+    // When set, every stored row leaves (sum, sum of squares) of its outputs here, one slot per
+    // (column tile, epilogue warp): plain stores, so the result does not depend on timing.
+    // linear_stat_slots(N) tells the consumer how many slots the producer fills.
     float2* emit_stats = nullptr;
 };
 
-struct LnFold { const float2* stats; const float* s; int mode, dim; float eps; float2* emit; };
+constexpr int STAT_SLOTS = 16;      // float2 slots per row in a row-statistics buffer
+int linear_stat_slots(int N);       // slots a tcgen05 GEMM with N output columns fills
+
+struct LnFold { const float2* stats; const float* s; int mode, dim; float eps; float2* emit; int slots; };
 
 int linear_validate(const LinearArgs& p);
 int linear_cuda_cores(const LinearArgs& p, cudaStream_t st);   // fp32 or bf16 inputs, CUDA cores

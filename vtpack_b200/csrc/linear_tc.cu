@@ -241,7 +241,16 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // folded LayerNorm: out = ln_a * acc + ln_b * s[n] + bias[n]
             float ln_a = 1.f, ln_b = 0.f;
             if (ln.mode && m0 + row < M) {
-                const float2 st = __ldg(ln.stats + m0 + row);
+                float2 st;
+                if (ln.mode == 2) {
+                    // partial (sum, sum of squares) left by the GEMM that produced the rows, one slot
+                    // per (column tile, epilogue warp of the lane quarter); added in a fixed order
+                    st = make_float2(0.f, 0.f);
+                    const float2* sp = ln.stats + (size_t)(m0 + row) * STAT_SLOTS;
+                    for (int i = 0; i < ln.slots; ++i) { st.x += sp[i].x; st.y += sp[i].y; }
+                } else {
+                    st = ln.stats[m0 + row];
+                }
                 float mean = st.x, rstd = st.y;
                 if (ln.mode == 2) {
                     mean = st.x / (float)ln.dim;
@@ -337,10 +346,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         }
                     }
                 }
-                if (ln.emit) {
-                    atomicAdd(&ln.emit[m0 + row].x, e1);
-                    atomicAdd(&ln.emit[m0 + row].y, e2);
-                }
+                if (ln.emit) ln.emit[(size_t)(m0 + row) * STAT_SLOTS + (t % n_tiles) * 4 + qsub] = make_float2(e1, e2);
                 continue;
             }
             // ---- boundary tile / row-remapped / fp32 output: store straight from registers
@@ -405,10 +411,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     OutVec<OutT>::store8(y + orow * ldy + n, v);
                 }
             }
-            if (ln.emit && row_ok) {
-                atomicAdd(&ln.emit[m].x, e1);
-                atomicAdd(&ln.emit[m].y, e2);
-            }
+            if (ln.emit && row_ok) ln.emit[(size_t)m * STAT_SLOTS + (t % n_tiles) * 4 + qsub] = make_float2(e1, e2);
         }
         if (elected) bulk_wait_group0();      // every TMA store has landed before the CTA retires
     }
@@ -505,7 +508,9 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
     const long long tiles = (long long)ceil_div(p.N, BN) * ceil_div(p.m_max, TBM);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     const RowMap rm{p.out_grp, p.out_skip, p.res_mod, p.res_off};
-    const LnFold ln{p.ln_stats, p.ln_s, p.ln_mode, p.ln_dim, p.ln_eps, p.emit_stats};
+    VTP_REQUIRE(!p.emit_stats || ceil_div(p.N, BN) * 4 <= STAT_SLOTS, VTP_ERR_SHAPE,
+                "linear (tcgen05): N=%d has too many column tiles for the row-statistics slots", p.N);
+    const LnFold ln{p.ln_stats, p.ln_s, p.ln_mode, p.ln_dim, p.ln_eps, p.emit_stats, p.ln_slots};
     const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), (size_t)S::TOTAL, st, ta, tw, ty, tr, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
                                       p.m_dev, p.N, p.K, p.flags, rm, ln, device_status_ptr());
     if (le != cudaSuccess) {
@@ -516,21 +521,28 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
     return check_launch("linear (tcgen05)");
 }
 
+static int pick_bn(int N) {
+    // widest tile that does not pad N more than a narrower one would
+    auto padded = [&](int bn) { return ceil_div(N, bn) * bn; };
+    int bn = 256;
+    if (padded(192) < padded(bn)) bn = 192;
+    if (padded(128) < padded(bn)) bn = 128;
+    return bn;
+}
+
+int linear_stat_slots(int N) { return ceil_div(N, pick_bn(N)) * 4; }
+
 int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
     if (p.m_max == 0) return VTP_OK;
     VTP_REQUIRE(p.dtype == VTP_BF16, VTP_ERR_DTYPE, "linear (tcgen05): bf16 operands only");
     VTP_REQUIRE(p.K % TBK == 0, VTP_ERR_SHAPE, "linear (tcgen05): K=%d must be a multiple of %d", p.K, TBK);
     VTP_REQUIRE(p.N % 8 == 0, VTP_ERR_SHAPE, "linear (tcgen05): N=%d must be a multiple of 8", p.N);
-    VTP_REQUIRE(p.ln_mode == 0 || (p.ln_stats && p.ln_s && p.out_grp == 0 && (p.ln_mode == 1 || p.ln_dim > 0)),
+    VTP_REQUIRE(p.ln_mode == 0 || (p.ln_stats && p.ln_s && p.out_grp == 0 &&
+                                   (p.ln_mode == 1 || (p.ln_dim > 0 && p.ln_slots > 0 && p.ln_slots <= STAT_SLOTS))),
                 VTP_ERR_NULL, "linear (tcgen05): folded LayerNorm needs row statistics and the column sums");
     VTP_REQUIRE(p.lda % 8 == 0 && p.ldy % 8 == 0 && (!p.res || p.ldr % 8 == 0), VTP_ERR_ALIGN,
                 "linear (tcgen05): row strides must be multiples of 16 bytes");
-    // widest tile that does not pad N more than a narrower one would
-    auto padded = [&](int bn) { return ceil_div(p.N, bn) * bn; };
-    int bn = 256;
-    if (padded(192) < padded(bn)) bn = 192;
-    if (padded(128) < padded(bn)) bn = 128;
-    if (getenv("VTP_BN")) bn = atoi(getenv("VTP_BN"));
+    const int bn = pick_bn(p.N);
     const bool f32 = (p.flags & VTP_FLAG_OUT_F32) != 0;
     if (bn == 256) return f32 ? launch_tc<256, 4, float>(p, st) : launch_tc<256, 4, bf16>(p, st);
     if (bn == 192) return f32 ? launch_tc<192, 4, float>(p, st) : launch_tc<192, 4, bf16>(p, st);

@@ -241,7 +241,7 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
             } else {
                 st = stats_x[src_row];
             }
-            if (sub == 0) { stats_q[dst_row] = st; stats_acc[dst_row] = make_float2(0.f, 0.f); }
+            if (sub == 0) { stats_q[dst_row] = st; if (stats_acc) stats_acc[dst_row] = make_float2(0.f, 0.f); }
         } else {
             ln_store<T, G, CPL>(f, sub, g.C, lnw, lnb, eps, xn + src_row * g.C);
             ln_store<T, G, CPL>(f, sub, g.C, lnw, lnb, eps, qn + (size_t)dst_row * g.C);
@@ -293,7 +293,7 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
             } else if (step == 1) {
                 st = stats_x[tok0 + j];
             }
-            if (step == 1 && sub == 0) { stats_q[prow] = st; stats_acc[prow] = make_float2(0.f, 0.f); }
+            if (step == 1 && sub == 0) { stats_q[prow] = st; if (stats_acc) stats_acc[prow] = make_float2(0.f, 0.f); }
         } else {
             ln_store<T, G, CPL>(f, sub, g.C, lnw, lnb, eps, xn + (tok0 + j) * g.C);
             if (step == 1) ln_store<T, G, CPL>(f, sub, g.C, lnw, lnb, eps, qn + (size_t)prow * g.C);
@@ -346,7 +346,7 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
     if (STATS) {
         round_store<T, CPL>(acc, comp + (size_t)row * g.C, sub, G);
         const float2 st = mean_rstd(row_sums<T, G, CPL>(acc), g.C, eps);
-        if (sub == 0) { stats_q[row] = st; stats_acc[row] = make_float2(0.f, 0.f); }
+        if (sub == 0) { stats_q[row] = st; if (stats_acc) stats_acc[row] = make_float2(0.f, 0.f); }
     } else {
         ln_store<T, G, CPL>(acc, sub, g.C, lnw, lnb, eps, qn + (size_t)row * g.C);
         round_store<T, CPL>(acc, comp + (size_t)row * g.C, sub, G);
