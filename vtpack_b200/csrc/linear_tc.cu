@@ -87,7 +87,12 @@ __device__ __forceinline__ float gelu_fast(float x) {
     return x * r;
 }
 
-template <int BN, int STAGES, typename OutT>
+// EPI: what the epilogue does besides the bias, fixed at compile time so that a kernel only
+// issues the instructions of the variant it is (a runtime flag would be if-converted and the
+// GELU / LayerNorm arithmetic issued, predicated off, by every GEMM).
+constexpr int EPI_GELU = 1, EPI_LN = 2, EPI_EMIT = 4;
+
+template <int BN, int STAGES, typename OutT, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_r,
@@ -224,7 +229,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int te = threadIdx.x - 64;
                 if (te < BN) {
                     bias_s[te] = (bias && nt0 + te < N) ? __ldg(bias + nt0 + te) : 0.f;
-                    if (ln.mode) bias_s[BN + te] = (nt0 + te < N) ? __ldg(ln.s + nt0 + te) : 0.f;
+                    if (EPI & EPI_LN) bias_s[BN + te] = (nt0 + te < N) ? __ldg(ln.s + nt0 + te) : 0.f;
                 }
                 if (res && elected && res_issued < slab_no) {
                     // first slab of a run of TMA tiles: nobody prefetched its residual
@@ -240,14 +245,19 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             // folded LayerNorm: out = ln_a * acc + ln_b * s[n] + bias[n]
             float ln_a = 1.f, ln_b = 0.f;
-            if (ln.mode && m0 + row < M) {
+            if ((EPI & EPI_LN) && m0 + row < M) {
                 float2 st;
                 if (ln.mode == 2) {
                     // partial (sum, sum of squares) left by the GEMM that produced the rows, one slot
                     // per (column tile, epilogue warp of the lane quarter); added in a fixed order
                     st = make_float2(0.f, 0.f);
-                    const float2* sp = ln.stats + (size_t)(m0 + row) * STAT_SLOTS;
-                    for (int i = 0; i < ln.slots; ++i) { st.x += sp[i].x; st.y += sp[i].y; }
+                    const float4* sp = reinterpret_cast<const float4*>(ln.stats + (size_t)(m0 + row) * STAT_SLOTS);
+                    float4 v4[STAT_SLOTS / 2];
+#pragma unroll
+                    for (int i = 0; i < STAT_SLOTS / 2; ++i)           // independent 16-byte loads, one latency
+                        v4[i] = (2 * i < ln.slots) ? sp[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int i = 0; i < STAT_SLOTS / 2; ++i) { st.x += v4[i].x; st.y += v4[i].y; st.x += v4[i].z; st.y += v4[i].w; }
                 } else {
                     st = ln.stats[m0 + row];
                 }
@@ -258,6 +268,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
                 ln_a = rstd;
                 ln_b = -rstd * mean;
+            }
+            if (EPI & EPI_LN) {
+                // warm L1 with the row statistics the next tile of this CTA will start with
+                const int tn = t + gridDim.x;
+                const int mn = (tn / n_tiles) * TBM + row;
+                if (tn < total && mn < M) {
+                    const float2* nxt = ln.stats + (size_t)mn * (ln.mode == 2 ? STAT_SLOTS : 1);
+                    asm volatile("prefetch.global.L1 [%0];" ::"l"(nxt));
+                }
             }
             float e1 = 0.f, e2 = 0.f;     // sum and sum of squares of this thread's outputs
             if (tma_path) {
@@ -295,7 +314,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         const float4 b0 = bs[0];
                         const float4 b1 = bs[1];
                         const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-                        if (ln.mode) {
+                        if (EPI & EPI_LN) {
                             const float4 s0 = bs[BN / 4];
                             const float4 s1 = bs[BN / 4 + 1];
                             const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
@@ -305,7 +324,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                             for (int i = 0; i < 8; ++i) vj[i] += bb[i];
                         }
-                        if (flags & VTP_FLAG_GELU) {
+                        if (EPI & EPI_GELU) {
 #pragma unroll
                             for (int i = 0; i < 8; ++i) vj[i] = gelu_fast(vj[i]);
                         }
@@ -317,7 +336,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                             for (int i = 0; i < 8; ++i) vj[i] += rf[i];
                         }
-                        if (ln.emit && nt0 + sl * 64 + chunk * 8 < N) {
+                        if ((EPI & EPI_EMIT) && nt0 + sl * 64 + chunk * 8 < N) {
 #pragma unroll
                             for (int i = 0; i < 8; ++i) { e1 += vj[i]; e2 = fmaf(vj[i], vj[i], e2); }
                         }
@@ -346,7 +365,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         }
                     }
                 }
-                if (ln.emit) ln.emit[(size_t)(m0 + row) * STAT_SLOTS + (t % n_tiles) * 4 + qsub] = make_float2(e1, e2);
+                if (EPI & EPI_EMIT) ln.emit[(size_t)(m0 + row) * STAT_SLOTS + (t % n_tiles) * 4 + qsub] = make_float2(e1, e2);
                 continue;
             }
             // ---- boundary tile / row-remapped / fp32 output: store straight from registers
@@ -382,7 +401,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w;
                         bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
                     }
-                    if (ln.mode) {
+                    if (EPI & EPI_LN) {
                         const float4 s0 = __ldg(reinterpret_cast<const float4*>(ln.s + n));
                         const float4 s1 = __ldg(reinterpret_cast<const float4*>(ln.s + n) + 1);
                         const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
@@ -392,7 +411,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                         for (int i = 0; i < 8; ++i) v[i] += bb[i];
                     }
-                    if (flags & VTP_FLAG_GELU) {
+                    if (EPI & EPI_GELU) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) v[i] = gelu_fast(v[i]);
                     }
@@ -404,14 +423,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                         for (int i = 0; i < 8; ++i) v[i] += rf[i];
                     }
-                    if (ln.emit) {
+                    if (EPI & EPI_EMIT) {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) { e1 += v[i]; e2 = fmaf(v[i], v[i], e2); }
                     }
                     OutVec<OutT>::store8(y + orow * ldy + n, v);
                 }
             }
-            if (ln.emit && row_ok) ln.emit[(size_t)m * STAT_SLOTS + (t % n_tiles) * 4 + qsub] = make_float2(e1, e2);
+            if ((EPI & EPI_EMIT) && row_ok) ln.emit[(size_t)m * STAT_SLOTS + (t % n_tiles) * 4 + qsub] = make_float2(e1, e2);
         }
         if (elected) bulk_wait_group0();      // every TMA store has landed before the CTA retires
     }
@@ -463,7 +482,7 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, int rank, const unsigned 
     return VTP_OK;
 }
 
-template <int BN, int STAGES, typename OutT>
+template <int BN, int STAGES, typename OutT, int EPI>
 static int launch_tc(const LinearArgs& p, cudaStream_t st) {
     using S = TcSmem<BN, STAGES>;
     CUtensorMap ta, tw;
@@ -492,7 +511,7 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
             if (int rc = make_tmap_bf16(&tr, p.res, 2, dims, rstrides, box)) return rc;
         }
     }
-    auto kern = linear_tc_kernel<BN, STAGES, OutT>;
+    auto kern = linear_tc_kernel<BN, STAGES, OutT, EPI>;
     static bool attr_set[64] = {};   // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -544,9 +563,26 @@ int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
                 "linear (tcgen05): row strides must be multiples of 16 bytes");
     const int bn = pick_bn(p.N);
     const bool f32 = (p.flags & VTP_FLAG_OUT_F32) != 0;
-    if (bn == 256) return f32 ? launch_tc<256, 4, float>(p, st) : launch_tc<256, 4, bf16>(p, st);
-    if (bn == 192) return f32 ? launch_tc<192, 4, float>(p, st) : launch_tc<192, 4, bf16>(p, st);
-    return f32 ? launch_tc<128, 5, float>(p, st) : launch_tc<128, 5, bf16>(p, st);
+    const int epi = ((p.flags & VTP_FLAG_GELU) ? EPI_GELU : 0) | (p.ln_mode ? EPI_LN : 0) | (p.emit_stats ? EPI_EMIT : 0);
+    if (f32) {
+        VTP_REQUIRE(epi == 0, VTP_ERR_UNSUPPORTED, "linear (tcgen05): fp32 output supports bias and residual only");
+        if (bn == 256) return launch_tc<256, 4, float, 0>(p, st);
+        if (bn == 192) return launch_tc<192, 4, float, 0>(p, st);
+        return launch_tc<128, 5, float, 0>(p, st);
+    }
+#define VTP_TC_CASE(E)                                                  \
+    if (epi == (E)) {                                                   \
+        if (bn == 256) return launch_tc<256, 4, bf16, (E)>(p, st);      \
+        if (bn == 192) return launch_tc<192, 4, bf16, (E)>(p, st);      \
+        return launch_tc<128, 5, bf16, (E)>(p, st);                     \
+    }
+    VTP_TC_CASE(0)
+    VTP_TC_CASE(EPI_GELU)
+    VTP_TC_CASE(EPI_LN)
+    VTP_TC_CASE(EPI_LN | EPI_GELU)
+    VTP_TC_CASE(EPI_EMIT)
+#undef VTP_TC_CASE
+    return fail(VTP_ERR_UNSUPPORTED, "linear (tcgen05): epilogue combination %d is not instantiated", epi);
 }
 
 }  // namespace vtp
