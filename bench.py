@@ -24,8 +24,10 @@ import torch  # noqa: E402
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 STAGES = ["router_gate", "patch_list", "pool_ln1", "q_proj", "kv_proj", "attention", "out_proj", "ln2", "fc1_gelu",
           "fc2", "unpool_add"]
-# DRAM bytes per launch of the dominant kernel from the ncu capture summarised under profiles/ (null until captured)
-NCU_TRAFFIC_BYTES = None
+# DRAM bytes (read + written) of one launch of the dominant kernel on the roofline's workload (the kv
+# projection at batch 256: M=65792, N=768, K=384), from the ncu capture summarised in
+# profiles/linear_tc_kv_projection_m65792_n768_k384.md; scaled by the row count for other batch sizes
+NCU_TRAFFIC_BYTES_PER_ROW = (51148032 + 44581632) / 65792
 
 
 def peaks():
@@ -178,16 +180,32 @@ def stage_profile(model, batch, device, iters, pk):
     gemm = [r for r in rows if r["kernel"] in ("q_proj", "kv_proj", "out_proj", "fc1_gelu", "fc2")]
     gemm_ms = sum(r["ms"] for r in gemm)
     gemm_flops = sum(work[r["kernel"]][1] for r in gemm)
-    ach = gemm_flops / (gemm_ms * 1e-3) / 1e12
-    roof = {"kernel": "linear_tc_kernel (q, kv, out, fc1, fc2 projections of one DGE block)", "bound": "tensor",
-            "achieved": round(ach, 1), "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
-            "frac": round(ach / pk["bf16_tflops_sustained"], 3), "traffic": NCU_TRAFFIC_BYTES,
-            "share_of_block": round(gemm_ms / sum(ms), 3)}
+    # the dominant kernel is the tcgen05 Linear; its roofline line is its largest launch (kv projection)
+    kv = next(r for r in rows if r["kernel"] == "kv_proj")
+    roof = {"kernel": "linear_tc_kernel, kv projection launch (M=B*N tokens, N=2C, K=C)", "bound": "tensor",
+            "achieved": kv["achieved"], "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+            "frac": kv["frac"], "traffic": int(NCU_TRAFFIC_BYTES_PER_ROW * BN),
+            "algorithmic_bytes": (BN * C + 2 * C * C + BN * 2 * C) * e,
+            "all_linear_launches": {"achieved": round(gemm_flops / (gemm_ms * 1e-3) / 1e12, 1),
+                                    "frac": round(gemm_flops / (gemm_ms * 1e-3) / 1e12 / pk["bf16_tflops_sustained"], 3),
+                                    "share_of_block": round(gemm_ms / sum(ms), 3)}}
     t_roof = sum(work[r["kernel"]][1] / ((pk["hbm_gbs"] * 1e9) if r["bound"] == "hbm"
                                          else (pk["bf16_tflops_sustained"] * 1e12)) for r in rows
                  if r["kernel"] != "patch_list")
     return rows, roof, {"queries_per_image": L / batch, "block_ms": round(sum(ms), 4),
                         "kernel_weighted_roofline_frac": round(t_roof / (sum(ms) * 1e-3), 3)}
+
+
+def launches_per_forward(model):
+    """Kernels of this library in one forward: im2col, cls rows, patch-embed Linear, then per block
+    pool, q, kv, attention, proj, fc1, fc2, unpool (LayerNorms are folded into the Linears and the
+    unpool leaves the next block's gate decisions), the first block's gate + count + patch-list +
+    counts reset, and the final LayerNorm + head.  The fp32 / CUDA-core path runs separate
+    LayerNorm and gate kernels per block."""
+    depth = len(model.blocks)
+    if model.compute_dtype() == torch.bfloat16 and not model.flags:
+        return 9 + 8 * depth
+    return 5 + 12 * depth
 
 
 def profile_case(which):
@@ -416,7 +434,7 @@ def main():
                     "d2h_bytes_per_step": pipe.d2h_bytes},
             # per forward: im2col, cls rows, patch-embed GEMM, final LayerNorm, head GEMM, first block's gate,
             # and per block: count, patch list, pool, 5 GEMMs, attention, unpool
-            "gpu_launches": args.steps * (6 + 10 * len(model.blocks)),
+            "gpu_launches": args.steps * launches_per_forward(model),
             "clocks": clocks, "device_status": status, "peaks": pk_src,
         }
         if not args.no_stage_profile and dtype == torch.bfloat16:

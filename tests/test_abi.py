@@ -69,7 +69,7 @@ def test_workspace_size_formula(lib):
     n = lib.vtp_block_workspace_bytes(ctypes.byref(s))
     rows = 4 * 257
     lower = rows * 2 * (192 * 6 + 2 * 192 + 768)
-    assert lower <= n <= lower + rows * 16 + 64 * 1024
+    assert lower <= n <= lower + rows * (16 * 8 + 32) + 64 * 1024   # + row statistics (16 slot pairs) and index lists
 
 
 def test_missing_library_fails_loudly(monkeypatch):
