@@ -42,7 +42,10 @@ constexpr int SM_Q = 0;                               // two Q buffers
 constexpr int SM_K = SM_Q + 2 * QT * HD * 2;          // 32768
 constexpr int SM_V = SM_K + KC_MAX * HD * 2;          // 65536
 constexpr int SM_BAR = SM_V + KC_MAX * HD * 2;        // 98304
-constexpr int SM_PREFIX = SM_BAR + 256;               // int32 [B + 1] tile prefix
+constexpr int SM_ITEM = SM_BAR + 256;                 // two work items (one per Q buffer), written by the producer
+constexpr int SM_TAIL = SM_ITEM + 256;                // per Q buffer: up to 15 tail K rows, then 15 tail V rows
+constexpr int TAIL_ROWS = 15;
+constexpr int SM_PREFIX = SM_TAIL + 2 * 2 * TAIL_ROWS * HD * 2;   // int32 [B + 1] tile prefix
 
 // 2^x on the special-function unit; arguments here are <= 0 (or -inf, giving 0).
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -52,6 +55,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 struct AttnItem { int b, h, row0, nq; };
+
+// Plain bulk copy global -> shared of `bytes` (a multiple of 16, both ends 16-byte aligned), counted on `bar`.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 
 // item w -> (image, head, first packed row, valid rows); tile_prefix is in shared memory
 __device__ __forceinline__ AttnItem attn_item(int w, int heads, int B, const int* tile_prefix,
@@ -93,6 +103,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* tile_prefix = reinterpret_cast<int*>(base + SM_PREFIX);
+    AttnItem* items = reinterpret_cast<AttnItem*>(base + SM_ITEM);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -156,8 +167,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 const int qb = li & 1;
                 ok = mbar_wait(&q_free[qb], ((li >> 1) & 1) ^ 1, abort_flag, status, STATUS_ATTN_LOAD);
                 if (!ok) break;
-                mbar_arrive_expect_tx(&q_full[qb], QT * HD * 2);
+                // the item, its Q tile and the K and V rows of the tail keys all arrive on q_full
+                items[qb] = it;
+                mbar_arrive_expect_tx(&q_full[qb], QT * HD * 2 + 2 * tail * HD * 2);
                 tma_load_2d(base + SM_Q + qb * (QT * HD * 2), &tmap_q, &q_full[qb], (int)(it.h * q_hs), it.row0);
+                for (int t = 0; t < tail; ++t) {
+                    const size_t koff = (size_t)it.b * kv_bs + (size_t)(n_main + t) * kv_rs + (size_t)it.h * kv_hs;
+                    uint8_t* tb = base + SM_TAIL + qb * (2 * TAIL_ROWS * HD * 2) + t * (HD * 2);
+                    bulk_load(tb, kptr + koff, HD * 2, &q_full[qb]);
+                    bulk_load(tb + TAIL_ROWS * HD * 2, vptr + koff, HD * 2, &q_full[qb]);
+                }
                 for (int c = 0; c < n_chunks; ++c, ++g) {
                     const uint32_t ph = g & 1;
                     ok = mbar_wait(k_free, ph ^ 1, abort_flag, status, STATUS_ATTN_LOAD);
@@ -221,14 +240,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         int li = 0, g = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++li) {
-            const AttnItem it = attn_item(w, heads, B, tile_prefix, offsets);
             const int qb = li & 1;
-            if (tail > 0 && lane < tail) {
-                // warm L1 with the tail keys' K and V rows (128 bytes each) for the CUDA-core step
-                const size_t koff = (size_t)it.b * kv_bs + (size_t)(n_main + lane) * kv_rs + (size_t)it.h * kv_hs;
-                asm volatile("prefetch.global.L1 [%0];" ::"l"(kptr + koff));
-                asm volatile("prefetch.global.L1 [%0];" ::"l"(vptr + koff));
-            }
+            // the producer worked out which (image, head, rows) this item is; it arrives with the Q tile
+            ok = mbar_wait(&q_full[qb], (li >> 1) & 1, abort_flag, status, STATUS_ATTN_SOFTMAX);
+            if (!ok) break;
+            const AttnItem it = items[qb];
             float m = -INFINITY, l = 0.f;
             float o[HD];
 #pragma unroll
@@ -319,17 +335,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             if (!ok) break;
             if (tail > 0) {
                 // ---- the last n_keys % 16 keys on CUDA cores, one online-softmax step per key
-                mbar_wait(&q_full[qb], (li >> 1) & 1, abort_flag, status, STATUS_ATTN_SOFTMAX);  // completed long ago
                 const uint8_t* qrow = base + SM_Q + qb * (QT * HD * 2) + r * 128;
+                const uint8_t* tb = base + SM_TAIL + qb * (2 * TAIL_ROWS * HD * 2);
                 for (int t = 0; t < tail; ++t) {
-                    const size_t koff = (size_t)it.b * kv_bs + (size_t)(n_main + t) * kv_rs + (size_t)it.h * kv_hs;
+                    const uint4* krow = reinterpret_cast<const uint4*>(tb + t * (HD * 2));
+                    const uint4* vrow = reinterpret_cast<const uint4*>(tb + (TAIL_ROWS + t) * (HD * 2));
                     float sdot = 0.f;
 #pragma unroll
                     for (int ch = 0; ch < HD / 8; ++ch) {
                         Vec<bf16> qv, kv;
                         float qf[8], kf[8];
                         qv.raw = *reinterpret_cast<const uint4*>(qrow + ((ch ^ (r & 7)) << 4));
-                        kv.raw = __ldg(reinterpret_cast<const uint4*>(kptr + koff) + ch);
+                        kv.raw = krow[ch];
                         qv.to_float(qf);
                         kv.to_float(kf);
 #pragma unroll
@@ -344,7 +361,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     for (int ch = 0; ch < HD / 8; ++ch) {
                         Vec<bf16> vv;
                         float vf[8];
-                        vv.raw = __ldg(reinterpret_cast<const uint4*>(vptr + koff) + ch);
+                        vv.raw = vrow[ch];
                         vv.to_float(vf);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) o[8 * ch + i] = fmaf(o[8 * ch + i], alpha, p * vf[i]);

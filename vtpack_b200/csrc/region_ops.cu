@@ -337,11 +337,12 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
             if (!row_in_one_slot) smem_add<T, CPL>(acc, part + (size_t)(r2 * 2 + 1) * g.C, sub, G);
         }
     }
-    const float denom = (float)(step * step);
+    // step * step is 4 or 16: multiplying by its reciprocal is the division, bit for bit
+    const float inv_denom = 1.0f / (float)(step * step);
 #pragma unroll
     for (int ch = 0; ch < CPL; ++ch)
 #pragma unroll
-        for (int i = 0; i < VN; ++i) acc[ch][i] = acc[ch][i] / denom;
+        for (int i = 0; i < VN; ++i) acc[ch][i] = acc[ch][i] * inv_denom;
     const int row = first + dy * s + dx;
     if (STATS) {
         round_store<T, CPL>(acc, comp + (size_t)row * g.C, sub, G);
@@ -370,7 +371,11 @@ __device__ __forceinline__ void gate_from_partials(const float* part, int C, int
         smem_add<T, CPL>(acc, part + (size_t)(r2 * 2) * C, sub, G);
         if (both_halves) smem_add<T, CPL>(acc, part + (size_t)(r2 * 2 + 1) * C, sub, G);
     }
-    const float denom = (float)(RG * RG);
+    // the region mean: 1/16 is a power of two, so the product equals the quotient
+#pragma unroll
+    for (int ch = 0; ch < CPL; ++ch)
+#pragma unroll
+        for (int i = 0; i < VN; ++i) acc[ch][i] *= 1.0f / (float)(RG * RG);
     float best = 0.f;
     int best_i = 0;
     for (int sI = 0; sI < S; ++sI) {
@@ -381,10 +386,10 @@ __device__ __forceinline__ void gate_from_partials(const float* part, int C, int
 #pragma unroll
             for (int i4 = 0; i4 < VN / 4; ++i4) {
                 const float4 w4 = __ldg(wp + i4);
-                pdot = fmaf(acc[ch][4 * i4 + 0] / denom, w4.x, pdot);
-                pdot = fmaf(acc[ch][4 * i4 + 1] / denom, w4.y, pdot);
-                pdot = fmaf(acc[ch][4 * i4 + 2] / denom, w4.z, pdot);
-                pdot = fmaf(acc[ch][4 * i4 + 3] / denom, w4.w, pdot);
+                pdot = fmaf(acc[ch][4 * i4 + 0], w4.x, pdot);
+                pdot = fmaf(acc[ch][4 * i4 + 1], w4.y, pdot);
+                pdot = fmaf(acc[ch][4 * i4 + 2], w4.z, pdot);
+                pdot = fmaf(acc[ch][4 * i4 + 3], w4.w, pdot);
             }
         }
         pdot = group_sum<G>(pdot) + __ldg(gb + sI);
