@@ -196,6 +196,64 @@ def stage_profile(model, batch, device, iters, pk):
                         "kernel_weighted_roofline_frac": round(t_roof / (sum(ms) * 1e-3), 3)}
 
 
+def kv_launch_roofline(model, batch, device, pk, iters=20):
+    """The dominant kernel's largest launch on its own: the kv projection (M = batch*N token rows,
+    N = 2C, K = C; operands + output exceed L2), `iters` launches back to back between two CUDA
+    events on the launch stream.  The per-stage times of `stage_profile` bracket every launch with
+    event records, which keeps the next launch from being queued behind the running one."""
+    from vtpack_b200 import _lib
+    lib = _lib.lib()
+    C, N = model.embed_dim, (model.img_size // model.patch_size) ** 2 + 1
+    M = batch * N
+    gen = torch.Generator(device).manual_seed(9)
+    x = torch.randn(M, C, device=device, generator=gen).bfloat16()
+    w = (torch.randn(2 * C, C, device=device, generator=gen) * 0.05).bfloat16()
+    b = torch.zeros(2 * C, device=device)
+    y = torch.empty(M, 2 * C, device=device, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream(device)
+
+    def launch():
+        _lib.check(lib.vtp_linear(x.data_ptr(), C, w.data_ptr(), b.data_ptr(), None, 0, y.data_ptr(), 2 * C, 1, M, None,
+                                  2 * C, C, 0, stream.cuda_stream))
+    for _ in range(5):
+        launch()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    e0.record(stream)
+    for _ in range(iters):
+        launch()
+    e1.record(stream)
+    torch.cuda.synchronize(device)
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    flops = 2.0 * M * 2 * C * C
+    ach = flops / (us * 1e-6) / 1e12
+    return {"kernel": "linear_tc_kernel, kv projection launch (M=batch*N token rows, N=2C, K=C)", "bound": "tensor",
+            "achieved": round(ach, 1), "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+            "frac": round(ach / pk["bf16_tflops_sustained"], 3), "traffic": int(NCU_TRAFFIC_BYTES_PER_ROW * M),
+            "algorithmic_bytes": (M * C + 2 * C * C + M * 2 * C) * 2, "launch_us": round(us, 2),
+            "timing": f"{iters} launches back to back between two CUDA events; 152 MB per launch at batch 256 (> L2)"}
+
+
+def model_roofline(model, batch, counts, ms_per_step, pk, image_bytes):
+    """Sum over the launches of one forward of the time the roofline allows each of them (the larger of
+    flops / measured tensor peak and algorithmic bytes / measured copy bandwidth), against the measured step."""
+    C, HW = model.embed_dim, (model.img_size // model.patch_size) ** 2
+    N, H, e = HW + 1, 4 * model.embed_dim, 2
+    BN = batch * N
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops_sustained"] * 1e12
+
+    def gemm(M, Nn, K):
+        return max(2.0 * M * Nn * K / tf, (M * K + Nn * K + M * Nn) * e / hbm)
+    KP = 3 * model.patch_size ** 2
+    t = batch * 3 * model.img_size ** 2 * (image_bytes + e) / hbm + gemm(batch * HW, C, KP) + gemm(batch, 1000, C)
+    for i in range(len(model.blocks)):
+        L = float(counts[i].sum())
+        t += (BN + L) * C * e / hbm + gemm(L, C, C) + gemm(BN, 2 * C, C) + gemm(L, C, C) + gemm(L, H, C) + gemm(L, C, H)
+        t += max(4.0 * L * N * C / tf, (2 * L * C + BN * 2 * C) * e / hbm) + (2 * BN + 2 * L) * C * e / hbm
+    return {"roofline_ms": round(t * 1e3, 4), "measured_ms": round(ms_per_step, 4), "frac": round(t * 1e3 / ms_per_step, 3),
+            "note": "kernel-weighted: sum of per-launch roofline times of one forward / measured ms_per_step"}
+
+
 def launches_per_forward(model):
     """Kernels of this library in one forward: im2col, cls rows, patch-embed Linear, then per block
     pool, q, kv, attention, proj, fc1, fc2, unpool (LayerNorms are folded into the Linears and the
@@ -437,9 +495,13 @@ def main():
             "gpu_launches": args.steps * launches_per_forward(model),
             "clocks": clocks, "device_status": status, "peaks": pk_src,
         }
+        if dtype == torch.bfloat16 and not args.cuda_cores:
+            line["roofline"] = kv_launch_roofline(model, B, device, pk)
+            line["model_roofline"] = model_roofline(model, B, model.last_counts.cpu(), ms_total / args.steps, pk,
+                                                    img_dev.element_size())
         if not args.no_stage_profile and dtype == torch.bfloat16:
             rows, roof, extra = stage_profile(model, B, device, 10, pk)
-            line["roofline"] = roof
+            line["roofline"]["all_linear_launches_of_a_block"] = roof["all_linear_launches"]
             line["kernels"] = rows
             line["block"] = extra
         if world == 1 and not args.no_cpu_baseline:
