@@ -74,6 +74,7 @@ def model_fixture():
             cnt.append(blk.dge.states["batches"].numpy())
             top2 = g.topk(2, dim=-1).values
             margin.append((top2[..., 0] - top2[..., 1]).numpy())
+        comp = m.complexity(x)               # the reference's own MAC accounting of this forward
     np.savez_compressed(
         os.path.join(HERE, "model_tiny_fp32.npz"),
         input_sum=np.float64(x.double().sum().item()),
@@ -82,8 +83,11 @@ def model_fixture():
         grain_indices=np.stack(idx).astype(np.int8),
         batch_lengths=np.stack(cnt),
         gate_margin=np.stack(margin),
+        comp_static=np.float64(float(comp["static"])),
+        comp_dynamic=np.float64(float(comp["dynamic"])),
     )
-    print("model:", logits.shape, np.stack(cnt).tolist(), "min margin", float(np.stack(margin).min()))
+    print("model:", logits.shape, np.stack(cnt).tolist(), "min margin", float(np.stack(margin).min()),
+          "MACs static/dynamic", float(comp["static"]), float(comp["dynamic"]))
 
 
 if __name__ == "__main__":

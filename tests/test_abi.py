@@ -85,3 +85,23 @@ def test_cpu_tensors_rejected():
     from vtpack_b200.layers import grained_sample_compress
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         grained_sample_compress(torch.zeros(1, 17, 8), torch.zeros(2, 4, dtype=torch.int64), 4, 4, 1)
+
+
+def test_complexity_accounting_matches_reference_fixture():
+    """VisionTransformer.complexity() of the mirror, fed the per-image query counts of the golden
+    forward the way the fused kernels leave them, reproduces the MACs the reference's own
+    complexity() reported for that forward (deit_dge.py:233-249, dge.py:40-59)."""
+    import os
+    import numpy as np
+    import torch
+    from vtpack_b200.models.dge.deit_dge import deit_dge_s124_tiny_patch16_256
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "model_tiny_fp32.npz"))
+    m = deit_dge_s124_tiny_patch16_256().eval()
+    counts = torch.from_numpy(g["batch_lengths"]).int()
+    tokens = torch.empty(0).expand(2, 257, 0)
+    for i, blk in enumerate(m.blocks):
+        blk.dge.states.update({"batches_device": counts[i], "input": tokens, "gate": None, "size": (16, 16),
+                               "num_extra_tokens": 1})
+    comp = m.complexity(torch.empty(2, 3, 256, 256))
+    assert float(comp["static"]) == float(g["comp_static"])
+    assert float(comp["dynamic"]) == float(g["comp_dynamic"])

@@ -130,6 +130,11 @@ def test_model_fp32_golden(golden_dir):
     assert g["gate_margin"].min() > 1e-5        # no near-tie in the fixture: counts must match exactly
     assert np.array_equal(m.last_counts.cpu().numpy(), g["batch_lengths"])
     assert rel_err(logits, torch.from_numpy(g["logits"])) < 1e-4
+    # MAC accounting of the same forward, from the counts the kernels left on the device
+    comp = m.complexity(O.make_images(2, 256, seed=1))
+    assert comp["static"].is_cuda and comp["dynamic"].is_cuda
+    assert float(comp["static"]) == float(g["comp_static"])
+    assert float(comp["dynamic"]) == float(g["comp_dynamic"])
 
 
 @pytest.mark.parametrize("cuda_cores", [True, False])

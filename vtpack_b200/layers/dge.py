@@ -78,11 +78,17 @@ class DynamicGrainedEncoder(nn.Module):
             return {"static": None, "dynamic": None}
         B, N, C = self.states["input"].shape
         gate = self.states["gate"]
-        indices = gate.argmax(dim=-1, keepdim=True)
-        gate = torch.zeros_like(gate).scatter_(-1, indices, 1.0)
-        num_queries = gate * (self.splits[None, None, None, :] ** 2)
-        num_queries = num_queries.view(B, -1).double().sum(-1)
-        num_queries = num_queries + self.states["num_extra_tokens"]
+        if gate is None:
+            # fused forward: the kernels left the per-image query counts (extra tokens included) on
+            # the device, which is the sum the reference recomputes from the gate; nothing is copied
+            # to the host here
+            num_queries = self.states["batches_device"].double()
+        else:
+            indices = gate.argmax(dim=-1, keepdim=True)
+            gate = torch.zeros_like(gate).scatter_(-1, indices, 1.0)
+            num_queries = gate * (self.splits[None, None, None, :] ** 2)
+            num_queries = num_queries.view(B, -1).double().sum(-1)
+            num_queries = num_queries + self.states["num_extra_tokens"]
         num_inputs = num_queries.new_full([B], N, dtype=torch.double)
         dge_cp = self.router.complexity(num_inputs, num_queries)
         static_cp = self.complexity_handler(num_inputs, num_inputs) + dge_cp

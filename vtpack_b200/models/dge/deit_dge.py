@@ -228,7 +228,7 @@ class Block(nn.Module):
             forced_gate = forced_gate.to(device=x.device, dtype=torch.float32).contiguous()
         _lib.check(lib.vtp_dge_block_forward(ctypes.byref(s), ctypes.byref(w), ptr(x), ptr(out), ptr(forced_gate),
                                              ptr(counts), ptr(ws), nbytes, stream_ptr(x.device)))
-        self.dge.states.update({"batches_device": counts, "input": x, "size": (s.H, s.W),
+        self.dge.states.update({"batches_device": counts, "input": x, "gate": None, "size": (s.H, s.W),
                                 "num_extra_tokens": s.num_extra})
         return out
 
@@ -375,7 +375,28 @@ class VisionTransformer(nn.Module):
         _lib.check(lib.vtp_deit_dge_forward(ctypes.byref(s), ctypes.byref(m), blocks, ptr(x), ptr(logits),
                                             ptr(counts), ptr(ws), nbytes, stream_ptr(x.device)))
         self.last_counts = counts
+        # what get_complexity() of each block's encoder needs (dge.py:40-59): shapes only, and the
+        # per-image query counts, which stay on the device
+        tokens = torch.empty(0, device=x.device).expand(B, G * G + 1, 0)
+        for i, blk in enumerate(self.blocks):
+            blk.dge.states.update({"batches_device": counts[i], "input": tokens, "gate": None, "size": (G, G),
+                                   "num_extra_tokens": 1})
         return logits
+
+    def complexity(self, x):
+        """Static and dynamic MACs per image of the last forward, averaged over the batch
+        (``deit_dge.py:233-249``, same formulae term by term); 0-d tensors on the device."""
+        N = x.shape[1] * x.shape[2]
+        comp = N * self.num_features * 3  # patch embed
+        comp += self.num_features * self.num_classes  # classifier
+        comp_static, comp_dynamic = [], []
+        for blk in self.blocks:
+            c = blk.dge.get_complexity()
+            comp_static.append(c["static"])
+            comp_dynamic.append(c["dynamic"])
+        comp_static = (sum(comp_static) + comp).mean()
+        comp_dynamic = (sum(comp_dynamic) + comp).mean()
+        return {"static": comp_static, "dynamic": comp_dynamic}
 
 
 def _graph_forward(model, x, logits_out):
