@@ -28,7 +28,9 @@ from torch import nn
 
 from . import dge_oracle
 
-REFERENCE_ROOT = os.environ.get("VTPACK_REFERENCE_ROOT", "/root/reference")
+# a checkout of the reference: $VTPACK_REFERENCE_ROOT, else a directory "reference" beside this repository
+REFERENCE_ROOT = os.environ.get("VTPACK_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 def reference_available() -> bool:

@@ -65,27 +65,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
-// Same bounded wait for warps that are not on the critical path (an epilogue waiting for the next
-// accumulator): sleeps between polls, so that many waiting warps do not take issue slots away
-// from the single threads that feed the TMA unit and the tensor core.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  int* status, int code, unsigned sleep_ns) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (int spin = 0;; ++spin) {
-        __nanosleep(sleep_ns);
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63) == 63) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
-                *abort_flag = 1;
-                if (status) atomicOr(status, code);
-                return false;
-            }
-        }
-    }
-}
-
 // ----------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
