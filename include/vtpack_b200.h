@@ -222,6 +222,12 @@ typedef struct {
     const void* q_wf; const float* q_s; const float* q_c;
     const void* kv_wf; const float* kv_s; const float* kv_c;
     const void* fc1_wf; const float* fc1_s; const float* fc1_c;
+    /* PVT+DGE blocks (shape sr_ratio > 1; vtpack/models/dge/pvt_dge.py:59-63,81-85): keys and values
+     * come from the normed tokens reduced by a stride-sr convolution and a LayerNorm.
+     * sr_w = attn.sr.weight as a matrix [C, sr*sr*C] in the model dtype with columns ordered
+     * (dy, dx, c_in), i.e. weight.permute(0, 2, 3, 1).reshape(C, -1); sr_b = attn.sr.bias;
+     * sr_norm_* = attn.norm (its epsilon is the shape's sr_eps, 1e-5 in the reference). */
+    const void* sr_w; const float* sr_b; const float* sr_norm_w; const float* sr_norm_b;
 } vtp_block_weights;
 
 /* Shapes shared by the block and model entry points. */
@@ -235,6 +241,9 @@ typedef struct {
     int splits[8];   /* sub-patches per region side, e.g. 4,2,1 */
     float eps;       /* LayerNorm epsilon */
     unsigned flags;  /* VTP_FLAG_CUDA_CORES */
+    int sr_ratio;    /* 0 or 1: keys = tokens (DeiT).  > 1: PVT spatial reduction, needs num_extra = 0,
+                        H and W multiples of it; the block then has H*W/sr^2 keys per image */
+    float sr_eps;    /* epsilon of the LayerNorm after the reduction */
 } vtp_dge_shape;
 
 /* Scratch bytes vtp_dge_block_forward needs for this shape (16-byte aligned slices). */

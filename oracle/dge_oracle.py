@@ -180,8 +180,15 @@ def router_forward(x_grid: torch.Tensor, gate_w: torch.Tensor, gate_b: torch.Ten
 def dge_block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], num_heads: int,
                       split_sizes: Sequence[int], eps: float = 1e-6,
                       forced_gate: Optional[torch.Tensor] = None,
-                      trace: Optional[dict] = None) -> torch.Tensor:
-    """Eval forward of one DeiT+DGE block.
+                      trace: Optional[dict] = None, grid: Optional[Tuple[int, int]] = None,
+                      sr_ratio: int = 1, sr_eps: float = 1e-5) -> torch.Tensor:
+    """Eval forward of one DeiT+DGE block, or of one PVT+DGE block when ``grid`` / ``sr_ratio``
+    are given.
+
+    PVT+DGE (``vtpack/models/dge/pvt_dge.py:140-146`` and ``Attention.forward`` ``:77-111``):
+    the same block on an explicit H x W grid (stages 1-3 carry no extra token), whose keys
+    and values come from the normed tokens reduced by a stride-``sr_ratio`` convolution
+    (``attn.sr``) and a LayerNorm (``attn.norm``, PyTorch's default eps 1e-5, ``:62-63``).
 
     Follows ``Block.forward`` (``vtpack/models/dge/deit_dge.py:123-130``),
     ``DynamicGrainedEncoder.compress/decompress`` (``vtpack/layers/dge.py:61-112``),
@@ -191,7 +198,10 @@ def dge_block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], num_heads: in
     ``forced_gate`` replaces the router output (teacher forcing).
     """
     B, N, C = x.shape
-    H = W = int(math.sqrt(N))
+    if grid is None:
+        H = W = int(math.sqrt(N))
+    else:
+        H, W = grid
     num_extra = N - H * W
     region = max(split_sizes)
     splits = torch.tensor(list(split_sizes), dtype=torch.int64)
@@ -212,8 +222,16 @@ def dge_block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], num_heads: in
     xn = F.layer_norm(x, (C,), w["norm1.weight"], w["norm1.bias"], eps)
     qn = F.layer_norm(comp, (C,), w["norm1.weight"], w["norm1.bias"], eps)
     q = F.linear(qn, w["attn.q.weight"], w.get("attn.q.bias")).reshape(-1, num_heads, d).permute(1, 0, 2)
-    kv = F.linear(xn, w["attn.kv.weight"], w.get("attn.kv.bias"))
-    kv = kv.reshape(B, N, 2, num_heads, d).permute(2, 3, 0, 1, 4)
+    if sr_ratio > 1:
+        # pvt_dge.py:81-85: the reshape needs N == H*W (no extra token in a reduced stage)
+        xr = xn.permute(0, 2, 1).reshape(B, C, H, W)
+        xr = F.conv2d(xr, w["attn.sr.weight"], w["attn.sr.bias"], stride=sr_ratio)
+        xr = xr.reshape(B, C, -1).permute(0, 2, 1)
+        keys_in = F.layer_norm(xr, (C,), w["attn.norm.weight"], w["attn.norm.bias"], sr_eps)
+    else:
+        keys_in = xn
+    kv = F.linear(keys_in, w["attn.kv.weight"], w.get("attn.kv.bias"))
+    kv = kv.reshape(B, keys_in.shape[1], 2, num_heads, d).permute(2, 3, 0, 1, 4)
     o = batched_sparse_attention_forward(q.contiguous(), kv[0].contiguous(), kv[1].contiguous(),
                                          batches, scale)
     o = o.transpose(0, 1).reshape(-1, C)
@@ -341,6 +359,40 @@ def make_state_dict(embed_dim: int, depth: int, num_heads: int, img_size: int = 
     sd["head.weight"] = tn(num_classes, C)
     sd["head.bias"] = torch.zeros(num_classes)
     return sd
+
+
+def make_pvt_block_weights(dim: int, mlp_ratio: int, sr_ratio: int, split_sizes: Sequence[int] = (4, 2, 1),
+                           seed: int = 0, std: float = 0.02) -> Dict[str, torch.Tensor]:
+    """Random-init weights of one PVT+DGE block under the reference's state_dict keys
+    (``pvt_dge.py:46-63,116-132``): matrices and the reduction convolution trunc-normal(std) in a
+    fixed order from one CPU generator, LayerNorm weights 1, every bias 0."""
+    g = torch.Generator().manual_seed(seed)
+
+    def tn(*shape):
+        t = torch.empty(*shape)
+        torch.nn.init.trunc_normal_(t, std=std, a=-2 * std, b=2 * std, generator=g)
+        return t
+
+    C = dim
+    w = {
+        "norm1.weight": torch.ones(C), "norm1.bias": torch.zeros(C),
+        "attn.q.weight": tn(C, C), "attn.q.bias": torch.zeros(C),
+        "attn.kv.weight": tn(2 * C, C), "attn.kv.bias": torch.zeros(2 * C),
+        "attn.proj.weight": tn(C, C), "attn.proj.bias": torch.zeros(C),
+    }
+    if sr_ratio > 1:
+        w["attn.sr.weight"] = tn(C, C, sr_ratio, sr_ratio)
+        w["attn.sr.bias"] = torch.zeros(C)
+        w["attn.norm.weight"] = torch.ones(C)
+        w["attn.norm.bias"] = torch.zeros(C)
+    w.update({
+        "norm2.weight": torch.ones(C), "norm2.bias": torch.zeros(C),
+        "mlp.fc1.weight": tn(mlp_ratio * C, C), "mlp.fc1.bias": torch.zeros(mlp_ratio * C),
+        "mlp.fc2.weight": tn(C, mlp_ratio * C), "mlp.fc2.bias": torch.zeros(C),
+        "dge.splits": torch.tensor(list(split_sizes)),
+        "dge.router.gate.weight": tn(len(split_sizes), C), "dge.router.gate.bias": torch.zeros(len(split_sizes)),
+    })
+    return w
 
 
 def make_images(batch: int, img_size: int = 256, seed: int = 1) -> torch.Tensor:

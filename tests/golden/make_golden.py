@@ -12,6 +12,9 @@ Fixtures
   model_tiny_fp32.npz   full DeiT-Ti+DGE (12 blocks), fp32, B=2, images seed 1,
                         free-running router: logits, per-layer grain indices
                         and per-image query counts.
+  pvt_block_fp32.npz    one PVT+DGE block (pvt_dge.py), fp32, B=2, 32x32 grid, no extra
+                        token, dim 64, 1 head, mlp ratio 8, spatial reduction 4 (64 keys);
+                        weights seed 3, tokens seed 4, free-running router.
 Inputs are regenerated from the seeds by the tests; each fixture carries a
 float64 sum of its inputs so RNG drift is detected rather than misread as a
 parity failure.
@@ -90,6 +93,35 @@ def model_fixture():
           "MACs static/dynamic", float(comp["static"]), float(comp["dynamic"]))
 
 
+def pvt_block_fixture():
+    import importlib
+    from functools import partial
+    ref_shim.install()
+    pvt = importlib.import_module("vtpack.models.dge.pvt_dge")
+    C, heads, H, sr, mr = 64, 1, 32, 4, 8
+    w = O.make_pvt_block_weights(C, mr, sr, seed=3)
+    blk = pvt.Block(C, heads, mlp_ratio=mr, qkv_bias=True, norm_layer=partial(torch.nn.LayerNorm, eps=1e-6),
+                    sr_ratio=sr, split_sizes=[4, 2, 1])
+    blk.load_state_dict(w, strict=True)
+    blk.eval()
+    x = O.make_tokens(2, H * H, C, seed=4)
+    with torch.no_grad():
+        out = blk(x, H, H)
+    st = blk.dge.states
+    top2 = st["gate"].topk(2, dim=-1).values
+    np.savez_compressed(
+        os.path.join(HERE, "pvt_block_fp32.npz"),
+        input_sum=np.float64(x.double().sum().item()),
+        weight_sum=np.float64(sum(v.double().sum().item() for v in w.values())),
+        grain_indices=st["gate"].argmax(-1).numpy().astype(np.int8),
+        batch_lengths=st["batches"].numpy(),
+        gate_margin=(top2[..., 0] - top2[..., 1]).numpy(),
+        out=out.numpy(),
+    )
+    print("pvt block:", out.shape, st["batches"].tolist(), "min margin", float((top2[..., 0] - top2[..., 1]).min()))
+
+
 if __name__ == "__main__":
     layer_fixture()
     model_fixture()
+    pvt_block_fixture()

@@ -252,3 +252,50 @@ def test_full_size_properties():
     b = blk(x, dense=True)
     assert rel_err(a.float(), b.float()) < 2e-2
     assert _lib.device_status() == 0
+
+
+def _pvt_block(C, heads, mr, sr, w, dtype):
+    from functools import partial
+    from vtpack_b200.models.dge.pvt_dge import Block
+    blk = Block(C, heads, mlp_ratio=mr, qkv_bias=True, norm_layer=partial(torch.nn.LayerNorm, eps=1e-6),
+                sr_ratio=sr, split_sizes=[4, 2, 1])
+    blk.load_state_dict(w, strict=True)
+    return blk.eval().to(device=DEV, dtype=dtype)
+
+
+def test_pvt_block_fp32_golden(golden_dir):
+    """PVT+DGE block (spatial reduction 4, 64 keys per image) against the reference's own output."""
+    from vtpack_b200 import _lib
+    g = np.load(os.path.join(golden_dir, "pvt_block_fp32.npz"))
+    w = O.make_pvt_block_weights(64, 8, 4, seed=3)
+    blk = _pvt_block(64, 1, 8, 4, w, torch.float32)
+    out = blk(O.make_tokens(2, 32 * 32, 64, seed=4).to(DEV), 32, 32)
+    assert g["gate_margin"].min() > 1e-5
+    assert blk.dge.states["batches_device"].tolist() == g["batch_lengths"].tolist()
+    assert rel_err(out, torch.from_numpy(g["out"])) < 1e-4
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("C,heads,H,sr,mr,extra", [(64, 1, 64, 8, 8, 0), (128, 2, 32, 4, 8, 0), (320, 5, 16, 2, 4, 0),
+                                                   (512, 8, 8, 1, 4, 1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pvt_block_stages(C, heads, H, sr, mr, extra, dtype):
+    """The four stage shapes of PVT+DGE at 256 px (grids 64..8, reductions 8..1, the last with a cls
+    token), gates teacher-forced: fp32 within 1e-4 of the oracle; bf16 against the fp32 oracle on
+    bf16-rounded weights and inputs."""
+    from vtpack_b200 import _lib
+    B = 4
+    w = O.make_pvt_block_weights(C, mr, sr, seed=7)
+    x = O.make_tokens(B, H * H + extra, C, seed=8)
+    if dtype == torch.bfloat16:
+        w = O.round_bf16(w)
+        x = x.bfloat16().float()
+    gate = O.make_gate_logits(B, H // 4, H // 4, 3, seed=9)
+    tr = {}
+    ref = O.dge_block_forward(x, w, heads, (4, 2, 1), forced_gate=gate, trace=tr, grid=(H, H), sr_ratio=sr)
+    blk = _pvt_block(C, heads, mr, sr, w, dtype)
+    out = blk(x.to(DEV).to(dtype), H, H, forced_gate=gate)
+    assert _lib.device_status() == 0
+    assert blk.dge.states["batches_device"].tolist() == tr["batches"].tolist()
+    err = rel_err(out.float(), ref)
+    assert err < (1e-4 if dtype == torch.float32 else 2e-2), err

@@ -171,3 +171,40 @@ def test_reference_modules_match_restatement():
     with torch.no_grad():
         ref = m(x)
     assert torch.equal(O.deit_dge_forward(x, sd, 2, 3, (4, 2, 1)), ref)
+
+
+def test_pvt_block_golden(golden_dir):
+    """The PVT+DGE block of the oracle against what the reference's pvt_dge.Block returned."""
+    g = _load(golden_dir, "pvt_block_fp32.npz")
+    w = O.make_pvt_block_weights(64, 8, 4, seed=3)
+    x = O.make_tokens(2, 32 * 32, 64, seed=4)
+    assert math.isclose(x.double().sum().item(), float(g["input_sum"]), rel_tol=0, abs_tol=1e-9)
+    assert math.isclose(sum(v.double().sum().item() for v in w.values()), float(g["weight_sum"]),
+                        rel_tol=0, abs_tol=1e-9)
+    tr = {}
+    out = O.dge_block_forward(x, w, 1, (4, 2, 1), trace=tr, grid=(32, 32), sr_ratio=4)
+    assert np.array_equal(tr["indices"].numpy().astype(np.int8), g["grain_indices"])
+    assert tr["batches"].tolist() == g["batch_lengths"].tolist()
+    assert torch.equal(out, torch.from_numpy(g["out"]))
+
+
+@needs_ref
+@pytest.mark.parametrize("C,heads,H,sr,mr,extra", [(64, 1, 32, 8, 8, 0), (128, 2, 16, 4, 8, 0), (320, 5, 8, 2, 4, 0),
+                                                   (512, 8, 8, 1, 4, 1)])
+def test_pvt_block_matches_reference(C, heads, H, sr, mr, extra):
+    """Every stage shape of the reference's PVT+DGE (last stage: no reduction, cls token in front)."""
+    import importlib
+    from functools import partial
+    ref_shim.install()
+    pvt = importlib.import_module("vtpack.models.dge.pvt_dge")
+    w = O.make_pvt_block_weights(C, mr, sr, seed=5)
+    blk = pvt.Block(C, heads, mlp_ratio=mr, qkv_bias=True, norm_layer=partial(torch.nn.LayerNorm, eps=1e-6),
+                    sr_ratio=sr, split_sizes=[4, 2, 1]).eval()
+    blk.load_state_dict(w, strict=True)
+    x = O.make_tokens(2, H * H + extra, C, seed=6)
+    with torch.no_grad():
+        ref = blk(x, H, H)
+    tr = {}
+    out = O.dge_block_forward(x, w, heads, (4, 2, 1), trace=tr, grid=(H, H), sr_ratio=sr)
+    assert tr["batches"].tolist() == blk.dge.states["batches"].tolist()
+    assert torch.equal(out, ref)

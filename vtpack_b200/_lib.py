@@ -19,13 +19,15 @@ class BlockWeights(C.Structure):
     _fields_ = [(n, c_void_p) for n in (
         "norm1_w", "norm1_b", "q_w", "q_b", "kv_w", "kv_b", "proj_w", "proj_b",
         "norm2_w", "norm2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b", "gate_w", "gate_b",
-        "q_wf", "q_s", "q_c", "kv_wf", "kv_s", "kv_c", "fc1_wf", "fc1_s", "fc1_c")]
+        "q_wf", "q_s", "q_c", "kv_wf", "kv_s", "kv_c", "fc1_wf", "fc1_s", "fc1_c",
+        "sr_w", "sr_b", "sr_norm_w", "sr_norm_b")]
 
 
 class DgeShape(C.Structure):
     _fields_ = [("dtype", c_int), ("B", c_int), ("H", c_int), ("W", c_int), ("num_extra", c_int),
                 ("C", c_int), ("heads", c_int), ("hidden", c_int), ("region", c_int),
-                ("n_splits", c_int), ("splits", c_int * 8), ("eps", c_float), ("flags", c_uint)]
+                ("n_splits", c_int), ("splits", c_int * 8), ("eps", c_float), ("flags", c_uint),
+                ("sr_ratio", c_int), ("sr_eps", c_float)]
 
 
 class ModelWeights(C.Structure):

@@ -11,6 +11,8 @@
 
 namespace vtp {
 
+int token_im2col(const void* x, int dtype, int B, int H, int W, int C, int sr, void* cols, cudaStream_t st);  // patch_embed.cu
+
 struct Carver {
     char* base;
     long long off = 0;
@@ -27,8 +29,14 @@ struct BlockScratch {
     float* logits[2];                                              // next block's (written by this block's unpool)
     float2 *stats_x[2], *stats_q, *stats_acc;
     void *comp, *xn, *qn, *qp, *kv, *ao, *q1, *hid;
+    void *sr_cols, *sr_out, *sr_norm;       // spatial reduction (PVT blocks): im2col rows, reduced tokens, their LayerNorm
     long long bytes;
 };
+
+// keys per image: the tokens, or the grid reduced by sr_ratio in each direction
+static int keys_per_image(const vtp_dge_shape& s) {
+    return s.sr_ratio > 1 ? (s.H / s.sr_ratio) * (s.W / s.sr_ratio) : s.num_extra + s.H * s.W;
+}
 
 static BlockScratch carve_block(const vtp_dge_shape& s, void* ws) {
     const long long e = (long long)elem_size(s.dtype);
@@ -58,6 +66,13 @@ static BlockScratch carve_block(const vtp_dge_shape& s, void* ws) {
     b.ao = c.take(rows * s.C * e);
     b.q1 = c.take(rows * s.C * e);
     b.hid = c.take(rows * s.hidden * e);
+    b.sr_cols = b.sr_out = b.sr_norm = nullptr;
+    if (s.sr_ratio > 1) {
+        const long long krows = (long long)s.B * keys_per_image(s);
+        b.sr_cols = c.take(rows * s.C * e);             // [B*keys, sr*sr*C] = as many elements as the tokens
+        b.sr_out = c.take(krows * s.C * e);
+        b.sr_norm = c.take(krows * s.C * e);
+    }
     b.bytes = c.off;
     return b;
 }
@@ -72,6 +87,12 @@ static int check_shape(const vtp_dge_shape* s) {
                 "block: grid %dx%d not divisible by region %d", s->H, s->W, s->region);
     VTP_REQUIRE(s->n_splits >= 1 && s->n_splits <= 8, VTP_ERR_SHAPE, "block: n_splits %d", s->n_splits);
     VTP_REQUIRE((long long)s->B * (s->num_extra + s->H * s->W) < (1ll << 30), VTP_ERR_SHAPE, "block: too many tokens");
+    if (s->sr_ratio > 1) {
+        // the reference reshapes the tokens to [B, C, H, W] before the reduction (pvt_dge.py:82)
+        VTP_REQUIRE(s->num_extra == 0, VTP_ERR_SHAPE, "block: spatial reduction needs a grid without extra tokens");
+        VTP_REQUIRE(s->H % s->sr_ratio == 0 && s->W % s->sr_ratio == 0, VTP_ERR_SHAPE,
+                    "block: grid %dx%d not divisible by the reduction ratio %d", s->H, s->W, s->sr_ratio);
+    }
     return VTP_OK;
 }
 
@@ -125,7 +146,11 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     // Region-parallel gate / pool / unpool when the region is 4x4 tokens, else one warp per patch.
     const bool by_region = region_ops_supported(g, s.dtype);
     // LayerNorm folded into the q / kv / fc1 GEMM epilogues (bf16 tensor-core path with prepared weights).
-    const bool fold = by_region && s.dtype == VTP_BF16 && !kflag && has_folded_weights(w);
+    const bool reduce = s.sr_ratio > 1;        // PVT block: keys from spatially reduced tokens (explicit LayerNorm rows)
+    VTP_REQUIRE(!reduce || (w.sr_w && w.sr_norm_w && w.sr_norm_b), VTP_ERR_NULL,
+                "block: spatial reduction needs the sr and sr_norm parameters");
+    const int n_keys = keys_per_image(s);
+    const bool fold = by_region && s.dtype == VTP_BF16 && !kflag && has_folded_weights(w) && !reduce;
     const int par = chain.parity & 1;
     int32_t* idx = b.idx[par];
     int32_t* counts = b.counts[par];
@@ -184,9 +209,22 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     if (fold) { lq.ln_mode = 1; lq.ln_stats = b.stats_q; lq.ln_s = w.q_s; }
     if ((rc = linear(lq, st)) || (rc = marks.mark(4))) return rc;
 
-    LinearArgs lkv;  // kv = LN(x) Wkv^T + b, rows stay [b, token, {k,v}, head, d]
-    lkv.a = fold ? x_in : b.xn; lkv.lda = C; lkv.w = fold ? w.kv_wf : w.kv_w; lkv.bias = fold ? w.kv_c : w.kv_b;
-    lkv.y = b.kv; lkv.ldy = 2 * C; lkv.dtype = s.dtype; lkv.m_max = rows; lkv.N = 2 * C; lkv.K = C; lkv.flags = kflag;
+    const void* keys_in = fold ? x_in : b.xn;
+    if (reduce) {
+        // x_ = norm(sr(LN1(x) as [B,C,H,W])): the stride-sr convolution as im2col rows times a matrix
+        const int krows = s.B * n_keys, KS = s.sr_ratio * s.sr_ratio * C;
+        if ((rc = token_im2col(b.xn, s.dtype, s.B, s.H, s.W, C, s.sr_ratio, b.sr_cols, st))) return rc;
+        LinearArgs lsr;
+        lsr.a = b.sr_cols; lsr.lda = KS; lsr.w = w.sr_w; lsr.bias = w.sr_b; lsr.y = b.sr_out; lsr.ldy = C;
+        lsr.dtype = s.dtype; lsr.m_max = krows; lsr.N = C; lsr.K = KS; lsr.flags = kflag;
+        if ((rc = linear(lsr, st))) return rc;
+        rc = vtp_layernorm(b.sr_out, s.dtype, krows, nullptr, C, C, w.sr_norm_w, w.sr_norm_b, s.sr_eps, b.sr_norm, st);
+        if (rc) return rc;
+        keys_in = b.sr_norm;
+    }
+    LinearArgs lkv;  // kv = LN(x) Wkv^T + b, rows stay [b, key, {k,v}, head, d]
+    lkv.a = keys_in; lkv.lda = C; lkv.w = fold ? w.kv_wf : w.kv_w; lkv.bias = fold ? w.kv_c : w.kv_b;
+    lkv.y = b.kv; lkv.ldy = 2 * C; lkv.dtype = s.dtype; lkv.m_max = s.B * n_keys; lkv.N = 2 * C; lkv.K = C; lkv.flags = kflag;
     if (fold) { lkv.ln_mode = 1; lkv.ln_stats = stats_x; lkv.ln_s = w.kv_s; }
     if ((rc = linear(lkv, st)) || (rc = marks.mark(5))) return rc;
 
@@ -194,9 +232,9 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     const long long e = (long long)elem_size(s.dtype);
     at.q = b.qp; at.q_rs = C; at.q_hs = d;
     at.k = b.kv; at.v = static_cast<const char*>(b.kv) + (long long)C * e;
-    at.kv_bs = (long long)N * 2 * C; at.kv_rs = 2 * C; at.kv_hs = d;
+    at.kv_bs = (long long)n_keys * 2 * C; at.kv_rs = 2 * C; at.kv_hs = d;
     at.out = b.ao; at.o_rs = C; at.o_hs = d;
-    at.dtype = s.dtype; at.B = s.B; at.n_keys = N; at.heads = s.heads; at.head_dim = d;
+    at.dtype = s.dtype; at.B = s.B; at.n_keys = n_keys; at.heads = s.heads; at.head_dim = d;
     at.offsets = b.offsets; at.l_max = rows; at.max_q = N; at.scale = 1.0f / sqrtf((float)d); at.flags = kflag;
     if ((rc = attention(at, st)) || (rc = marks.mark(6))) return rc;
 

@@ -57,6 +57,44 @@ __global__ void cls_row_kernel(const T* __restrict__ cls, const T* __restrict__ 
         x[(size_t)b * row_stride + c] = from_f32<T>(to_f32(cls[c]) + to_f32(pos[c]));
 }
 
+// Rows of the stride-sr reduction convolution of a PVT block as a GEMM operand: row (b, oy, ox) is
+// the sr x sr window of tokens, column (dy, dx, c).  A window row (fixed dy) is sr consecutive
+// tokens = sr*C contiguous elements on both sides; one thread moves 16 bytes.
+// Replaces the permute / reshape in front of attn.sr (vtpack/models/dge/pvt_dge.py:82-83).
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_im2col_kernel(const T* __restrict__ x, long long total_vec, int H, int W, int C, int sr, T* __restrict__ cols) {
+    constexpr int VN = Vec<T>::N;
+    const int run = sr * C / VN;                  // 16-byte vectors per window row
+    const int Wo = W / sr, Ho = H / sr;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total_vec;
+         v += (long long)gridDim.x * blockDim.x) {
+        const int i = (int)(v % run);
+        long long r = v / run;                    // (b, oy, ox, dy) with dy fastest
+        const int dy = (int)(r % sr); r /= sr;
+        const int ox = (int)(r % Wo); r /= Wo;
+        const int oy = (int)(r % Ho);
+        const long long b = r / Ho;
+        const long long tok = (b * H + (long long)oy * sr + dy) * W + (long long)ox * sr;
+        Vec<T> t;
+        t.load(x + tok * C + (long long)i * VN);
+        t.store(cols + ((((b * Ho + oy) * Wo + ox) * sr + dy) * (long long)run + i) * VN);
+    }
+}
+
+int token_im2col(const void* x, int dtype, int B, int H, int W, int C, int sr, void* cols, cudaStream_t st) {
+    const int vn = dtype == VTP_BF16 ? 8 : 4;
+    VTP_REQUIRE(C % vn == 0, VTP_ERR_SHAPE, "spatial reduction: C=%d must be a multiple of %d", C, vn);
+    const long long total = (long long)B * H * W * C / vn;
+    if (total == 0) return VTP_OK;
+    const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == VTP_BF16)
+        token_im2col_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, total, H, W, C, sr, (bf16*)cols);
+    else
+        token_im2col_kernel<float><<<grid, 256, 0, st>>>((const float*)x, total, H, W, C, sr, (float*)cols);
+    return check_launch("spatial reduction im2col");
+}
+
 }  // namespace vtp
 
 using namespace vtp;

@@ -140,7 +140,13 @@ def _pack_block(blk, dtype) -> _lib.BlockWeights:
             fc2_w=mat(m.fc2.weight), fc2_b=vec(m.fc2.bias),
             gate_w=vec(blk.dge.router.gate.weight), gate_b=vec(blk.dge.router.gate.bias),
         )
-        if dtype == torch.bfloat16 and blk.fold_layernorm:
+        sr = getattr(a, "sr", None)
+        if sr is not None:
+            # PVT spatial reduction: conv weight [C, C, sr, sr] -> matrix [C, sr*sr*C], columns (dy, dx, c_in)
+            t["sr_w"] = mat(sr.weight.permute(0, 2, 3, 1).reshape(sr.weight.shape[0], -1))
+            t["sr_b"] = vec(sr.bias) if sr.bias is not None else zeros(a.dim, sr.weight)
+            t["sr_norm_w"], t["sr_norm_b"] = vec(a.norm.weight), vec(a.norm.bias)
+        if dtype == torch.bfloat16 and blk.fold_layernorm and sr is None:
             # LayerNorm folded into the Linear that follows it (weight preparation, once)
             for name, lin_w, lin_b, gw, gb in (("q", t["q_w"], t["q_b"], t["norm1_w"], t["norm1_b"]),
                                                ("kv", t["kv_w"], t["kv_b"], t["norm1_w"], t["norm1_b"]),
