@@ -374,6 +374,53 @@ def layer_sweep(args):
                       "model": "DeiT-S layer, 16x16 grid, 16 regions"}), flush=True)
 
 
+def pvt_sweep(args):
+    """The four stage shapes of PVT+DGE (small) at 256 px, one block each, bf16, free-running
+    random-init gate: microseconds per block on the GPU, the FLOPs the block does and, beside it,
+    the CPU oracle on a bounded sample (4 images)."""
+    from functools import partial
+    from oracle import dge_oracle as O
+    from vtpack_b200 import _lib
+    from vtpack_b200.models.dge.pvt_dge import Block
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B = args.batch
+    torch.set_num_threads(os.cpu_count() or 1)
+    rows = []
+    for C, heads, H, sr, mr, extra in ((64, 1, 64, 8, 8, 0), (128, 2, 32, 4, 8, 0), (320, 5, 16, 2, 4, 0),
+                                       (512, 8, 8, 1, 4, 1)):
+        w = O.make_pvt_block_weights(C, mr, sr, seed=7)
+        blk = Block(C, heads, mlp_ratio=mr, qkv_bias=True, norm_layer=partial(torch.nn.LayerNorm, eps=1e-6),
+                    sr_ratio=sr, split_sizes=[4, 2, 1])
+        blk.load_state_dict(w, strict=True)
+        blk = blk.eval().to(device=dev, dtype=torch.bfloat16)
+        N = H * H + extra
+        x = torch.randn(B, N, C, device=dev, generator=torch.Generator(dev).manual_seed(3)).bfloat16()
+        for _ in range(3):
+            blk(x, H, H)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            blk(x, H, H)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / 20 * 1e3
+        L = float(blk.dge.states["batches_device"].float().sum())
+        nk = N if sr == 1 else (H // sr) ** 2
+        flops = 2.0 * (L * C * C * 2 + B * nk * C * 2 * C + (B * N * C * C if sr > 1 else 0) + 2 * L * nk * C
+                       + 2 * L * C * mr * C)
+        xc = O.make_tokens(4, N, C, seed=8)
+        t0 = time.perf_counter()
+        O.dge_block_forward(xc, w, heads, (4, 2, 1), grid=(H, H), sr_ratio=sr)
+        cpu_us = (time.perf_counter() - t0) * 1e6 / 4 * B
+        rows.append({"stage": f"C={C} heads={heads} grid={H}x{H} sr={sr}", "queries_per_image": round(L / B, 1),
+                     "keys": nk, "block_us": round(us, 1), "tflops": round(flops / us / 1e6, 1),
+                     "cpu_oracle_us_scaled_to_batch": round(cpu_us)})
+    assert _lib.device_status() == 0
+    print(json.dumps({"pvt_sweep": rows, "batch": B, "dtype": "bf16"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -394,9 +441,14 @@ def main():
                     help="run a small case of one kernel family (for ncu) and exit")
     ap.add_argument("--layer-sweep", action="store_true",
                     help="time one DGE layer over gate skew against the dense block and exit")
+    ap.add_argument("--pvt-sweep", action="store_true",
+                    help="time one PVT+DGE block per stage shape (256 px) and exit")
     args = ap.parse_args()
     if args.profile:
         profile_case(args.profile)
+        return
+    if args.pvt_sweep:
+        pvt_sweep(args)
         return
     if args.layer_sweep:
         layer_sweep(args)
