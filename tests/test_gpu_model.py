@@ -111,10 +111,10 @@ def test_layer_bf16_vs_fp32_oracle(cuda_cores, fold):
     assert rel_err(out.float(), ref) < 1.5e-2
 
 
-def _model(kind, sd, dtype, depth=12, flags=0):
+def _model(kind, sd, dtype, depth=12, flags=0, img_size=256):
     from vtpack_b200.models.dge import deit_dge
     cfg = O.MODEL_CONFIGS[kind]
-    m = deit_dge.VisionTransformer(img_size=256, patch_size=16, embed_dim=cfg["embed_dim"], depth=depth,
+    m = deit_dge.VisionTransformer(img_size=img_size, patch_size=16, embed_dim=cfg["embed_dim"], depth=depth,
                                    num_heads=cfg["num_heads"], mlp_ratio=4, qkv_bias=True, split_sizes=[4, 2, 1])
     m.load_state_dict(sd, strict=True)
     m.flags = flags
@@ -181,6 +181,32 @@ def test_model_bf16_top1_agreement_1024_images():
     assert err < 2e-2
     assert bool(same[clear].all())
     assert float(same.float().mean()) > 0.85
+
+
+@pytest.mark.parametrize("dtype,depth,tol", [(torch.float32, 4, 1e-4), (torch.bfloat16, 12, 2e-2)])
+def test_model_512px(dtype, depth, tol):
+    """BASELINE config 5 shape through the whole-model entry point at reduced batch and width:
+    512 x 512 images (32 x 32 grid + cls = 1025 tokens, 64 regions per image, 1025 keys = four
+    256-key chunks + one tail key), free-running router.  fp32: logits within 1e-4 relative of
+    the oracle wherever the per-layer query counts agree (they must, unless a gate is a near-tie);
+    bf16: logits within 2e-2 max-abs of the fp32 oracle on bf16-rounded weights."""
+    from vtpack_b200 import _lib
+    sd = O.make_state_dict(192, depth, 3, img_size=512, seed=30)
+    if dtype == torch.bfloat16:
+        sd = O.round_bf16(sd)
+    img = O.make_images(3, 512, seed=34)          # smallest top-2 gate margin of the fp32 run: 2.8e-4
+    tr = []
+    ref = O.deit_dge_forward(img, sd, depth, 3, (4, 2, 1), trace=tr)
+    m = _model("tiny", sd, dtype, depth=depth, img_size=512)
+    logits = m(img.to(DEV)).cpu()
+    assert _lib.device_status() == 0
+    counts_ref = torch.stack([t["batches"] for t in tr])
+    assert int(counts_ref.min()) >= 65 and int(counts_ref.max()) <= 1025
+    if dtype == torch.float32:
+        assert torch.equal(m.last_counts.cpu().long(), counts_ref)
+        assert rel_err(logits, ref) < tol
+    else:
+        assert float((logits - ref).abs().max()) < tol
 
 
 def test_layer_512px_bf16_skewed():
