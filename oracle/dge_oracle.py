@@ -301,6 +301,92 @@ def deit_dge_forward(images: torch.Tensor, sd: Dict[str, torch.Tensor], depth: i
     return F.linear(x[:, 0], sd["head.weight"], sd["head.bias"])
 
 
+PVT_CONFIGS = {
+    # pvt_dge.py:375-392: the 256 px factories (tiny: depths 2,2,2,2; small: 3,4,6,3)
+    "tiny": dict(embed_dims=(64, 128, 320, 512), num_heads=(1, 2, 5, 8), mlp_ratios=(8, 8, 4, 4),
+                 depths=(2, 2, 2, 2), sr_ratios=(8, 4, 2, 1), patch_size=4),
+    "small": dict(embed_dims=(64, 128, 320, 512), num_heads=(1, 2, 5, 8), mlp_ratios=(8, 8, 4, 4),
+                  depths=(3, 4, 6, 3), sr_ratios=(8, 4, 2, 1), patch_size=4),
+}
+
+
+def pvt_dge_forward(images: torch.Tensor, sd: Dict[str, torch.Tensor], cfg: dict,
+                    split_sizes: Sequence[int] = (4, 2, 1), eps: float = 1e-6,
+                    trace: Optional[List[dict]] = None) -> torch.Tensor:
+    """Eval forward of PVT+DGE, images ``[B,3,S,S] -> logits [B,classes]``.
+
+    Follows ``PyramidVisionTransformer.forward_features/forward``
+    (``vtpack/models/dge/pvt_dge.py:295-337``) at the training resolution (no position-embedding
+    interpolation, ``:287-288``): per stage a patch-embedding convolution (kernel = stride = 4,
+    then 2) followed by a LayerNorm with PyTorch's default eps 1e-5 (``PatchEmbed``, ``:149-179``),
+    the position embedding, the stage's DGE blocks, and the token grid handed to the next stage
+    as ``[B,C,H,W]``; the last stage gets the cls token in front; final LayerNorm, cls row, head.
+    """
+    B = images.shape[0]
+    x = images
+    n_stages = len(cfg["embed_dims"])
+    for i in range(n_stages):
+        p = cfg["patch_size"] if i == 0 else 2
+        pre = f"patch_embed{i + 1}."
+        x = F.conv2d(x, sd[pre + "proj.weight"], sd[pre + "proj.bias"], stride=p)
+        H, W = x.shape[2], x.shape[3]
+        x = x.flatten(2).transpose(1, 2)
+        x = F.layer_norm(x, (x.shape[-1],), sd[pre + "norm.weight"], sd[pre + "norm.bias"], 1e-5)
+        if i == n_stages - 1:
+            x = torch.cat((sd["cls_token"].expand(B, -1, -1), x), dim=1)
+        x = x + sd[f"pos_embed{i + 1}"]
+        for j in range(cfg["depths"][i]):
+            t = {} if trace is not None else None
+            pfx = f"block{i + 1}.{j}."
+            w = {k[len(pfx):]: v for k, v in sd.items() if k.startswith(pfx)}
+            x = dge_block_forward(x, w, cfg["num_heads"][i], split_sizes, eps, trace=t, grid=(H, W),
+                                  sr_ratio=cfg["sr_ratios"][i])
+            if trace is not None:
+                trace.append(t)
+        if i != n_stages - 1:
+            x = x.reshape(B, H, W, -1).permute(0, 3, 1, 2).contiguous()
+    x = F.layer_norm(x, (x.shape[-1],), sd["norm.weight"], sd["norm.bias"], eps)
+    return F.linear(x[:, 0], sd["head.weight"], sd["head.bias"])
+
+
+def make_pvt_state_dict(cfg: dict, img_size: int = 256, num_classes: int = 1000,
+                        split_sizes: Sequence[int] = (4, 2, 1), seed: int = 0, std: float = 0.02) -> Dict[str, torch.Tensor]:
+    """Random-init weights of PVT+DGE under the reference's state_dict keys (``pvt_dge.py:196-224``):
+    matrices, convolutions, position embeddings and the cls token trunc-normal(std) in a fixed order
+    from CPU generators, LayerNorm weights 1, every bias (the gates' included) 0."""
+    g = torch.Generator().manual_seed(seed)
+
+    def tn(*shape):
+        t = torch.empty(*shape)
+        torch.nn.init.trunc_normal_(t, std=std, a=-2 * std, b=2 * std, generator=g)
+        return t
+
+    sd = {}
+    dims = cfg["embed_dims"]
+    n_stages = len(dims)
+    for i in range(n_stages):
+        C = dims[i]
+        p = cfg["patch_size"] if i == 0 else 2
+        grid = img_size // (cfg["patch_size"] * 2 ** i)
+        pre = f"patch_embed{i + 1}."
+        sd[pre + "proj.weight"] = tn(C, 3 if i == 0 else dims[i - 1], p, p)
+        sd[pre + "proj.bias"] = torch.zeros(C)
+        sd[pre + "norm.weight"] = torch.ones(C)
+        sd[pre + "norm.bias"] = torch.zeros(C)
+        sd[f"pos_embed{i + 1}"] = tn(1, grid * grid + (1 if i == n_stages - 1 else 0), C)
+        for j in range(cfg["depths"][i]):
+            w = make_pvt_block_weights(C, cfg["mlp_ratios"][i], cfg["sr_ratios"][i], split_sizes,
+                                       seed=seed * 1000 + 17 * i + j + 1, std=std)
+            for k, v in w.items():
+                sd[f"block{i + 1}.{j}.{k}"] = v
+    sd["norm.weight"] = torch.ones(dims[-1])
+    sd["norm.bias"] = torch.zeros(dims[-1])
+    sd["cls_token"] = tn(1, 1, dims[-1])
+    sd["head.weight"] = tn(num_classes, dims[-1])
+    sd["head.bias"] = torch.zeros(num_classes)
+    return sd
+
+
 # --------------------------------------------------------------------------
 # Seeded synthetic weights / inputs shared by tests, golden fixtures and bench
 # --------------------------------------------------------------------------

@@ -15,6 +15,9 @@ Fixtures
   pvt_block_fp32.npz    one PVT+DGE block (pvt_dge.py), fp32, B=2, 32x32 grid, no extra
                         token, dim 64, 1 head, mlp ratio 8, spatial reduction 4 (64 keys);
                         weights seed 3, tokens seed 4, free-running router.
+  pvt_model_fp32.npz    full PVT+DGE tiny (pvt_dge_s124_tiny_256: 4 stages, 8 blocks), fp32, B=2,
+                        weights seed 0, images seed 8, free-running router: logits and the
+                        per-block per-image query counts.
 Inputs are regenerated from the seeds by the tests; each fixture carries a
 float64 sum of its inputs so RNG drift is detected rather than misread as a
 parity failure.
@@ -121,7 +124,37 @@ def pvt_block_fixture():
     print("pvt block:", out.shape, st["batches"].tolist(), "min margin", float((top2[..., 0] - top2[..., 1]).min()))
 
 
+def pvt_model_fixture():
+    import importlib
+    ref_shim.install()
+    pvt = importlib.import_module("vtpack.models.dge.pvt_dge")
+    cfg = O.PVT_CONFIGS["tiny"]
+    sd = O.make_pvt_state_dict(cfg, seed=0)
+    m = pvt.pvt_dge_s124_tiny_256()
+    m.load_state_dict(sd, strict=True)
+    m.eval()
+    x = O.make_images(2, 256, seed=8)
+    with torch.no_grad():
+        logits = m(x)
+    cnt, margin = [], []
+    for i in range(4):
+        for blk in getattr(m, f"block{i + 1}"):
+            cnt.append(blk.dge.states["batches"].numpy())
+            top2 = blk.dge.states["gate"].topk(2, dim=-1).values
+            margin.append(float((top2[..., 0] - top2[..., 1]).min()))
+    np.savez_compressed(
+        os.path.join(HERE, "pvt_model_fp32.npz"),
+        input_sum=np.float64(x.double().sum().item()),
+        weight_sum=np.float64(sum(v.double().sum().item() for v in sd.values())),
+        logits=logits.numpy(),
+        batch_lengths=np.stack(cnt),
+        gate_margin=np.array(margin),
+    )
+    print("pvt model:", logits.shape, np.stack(cnt).tolist(), "min margin", min(margin))
+
+
 if __name__ == "__main__":
     layer_fixture()
     model_fixture()
     pvt_block_fixture()
+    pvt_model_fixture()

@@ -208,3 +208,18 @@ def test_pvt_block_matches_reference(C, heads, H, sr, mr, extra):
     out = O.dge_block_forward(x, w, heads, (4, 2, 1), trace=tr, grid=(H, H), sr_ratio=sr)
     assert tr["batches"].tolist() == blk.dge.states["batches"].tolist()
     assert torch.equal(out, ref)
+
+
+def test_pvt_model_golden(golden_dir):
+    """The PVT+DGE model of the oracle against what the reference's pvt_dge_s124_tiny_256 returned."""
+    g = _load(golden_dir, "pvt_model_fp32.npz")
+    cfg = O.PVT_CONFIGS["tiny"]
+    sd = O.make_pvt_state_dict(cfg, seed=0)
+    x = O.make_images(2, 256, seed=8)
+    assert math.isclose(x.double().sum().item(), float(g["input_sum"]), rel_tol=0, abs_tol=1e-9)
+    assert math.isclose(sum(v.double().sum().item() for v in sd.values()), float(g["weight_sum"]),
+                        rel_tol=0, abs_tol=1e-9)
+    tr = []
+    logits = O.pvt_dge_forward(x, sd, cfg, trace=tr)
+    assert [t["batches"].tolist() for t in tr] == g["batch_lengths"].tolist()
+    assert torch.equal(logits, torch.from_numpy(g["logits"]))
