@@ -125,20 +125,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     // offsets, q, k and v below do.
     griddep_launch();
     griddep_wait();
-    // tile_prefix[b] = number of 128-query tiles of the images in front of b (serial scan by
-    // warp 0 in 32-image steps; B is a few hundred)
+    // tile_prefix[b] = number of 128-query tiles of the images in front of b.  All threads fetch the
+    // per-image tile counts at once (one global-load latency), then warp 0 scans them in shared memory.
+    for (int b = threadIdx.x; b < B; b += blockDim.x)
+        tile_prefix[b] = (offsets[b + 1] - offsets[b] + QT - 1) / QT;
+    __syncthreads();
     if (warp == 0) {
         int run = 0;
         for (int b0 = 0; b0 < B; b0 += 32) {
             const int b = b0 + lane;
-            int tiles = 0;
-            if (b < B) tiles = (offsets[b + 1] - offsets[b] + QT - 1) / QT;
+            const int tiles = b < B ? tile_prefix[b] : 0;
             int incl = tiles;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int nb = __shfl_up_sync(0xffffffffu, incl, o);
                 if (lane >= o) incl += nb;
             }
+            __syncwarp();
             if (b < B) tile_prefix[b] = run + incl - tiles;
             run += __shfl_sync(0xffffffffu, incl, 31);
         }

@@ -48,10 +48,10 @@ class DynamicRouter(nn.Module):
         r = self.region_size
         logits = torch.empty(B, H // r, W // r, len(self.split_sizes), dtype=torch.float32, device=x.device)
         idx = torch.empty(B, H // r, W // r, dtype=torch.int32, device=x.device)
+        gw, gb = self.gate.weight.detach().float().contiguous(), self.gate.bias.detach().float().contiguous()
         _lib.check(_lib.lib().vtp_router_gate(
-            ptr(x), dtype_code(x.dtype), B, H, W, C, 0, r, ptr(self.gate.weight.detach().float().contiguous()),
-            ptr(self.gate.bias.detach().float().contiguous()), len(self.split_sizes), ptr(logits), ptr(idx),
-            stream_ptr(x.device)))
+            ptr(x), dtype_code(x.dtype), B, H, W, C, 0, r, ptr(gw), ptr(gb), len(self.split_sizes), ptr(logits),
+            ptr(idx), stream_ptr(x.device)))
         self.last_indices = idx
         return logits
 
@@ -107,11 +107,11 @@ class DynamicGrainedEncoder(nn.Module):
         S = self.splits.numel()
         gate = torch.empty(B, H // r, W // r, S, dtype=torch.float32, device=x.device)
         indices = torch.empty(B, H // r, W // r, dtype=torch.int32, device=x.device)
+        gate_w = self.router.gate.weight.detach().float().contiguous()
+        gate_b = self.router.gate.bias.detach().float().contiguous()
         _lib.check(_lib.lib().vtp_router_gate(
-            ptr(x), dtype_code(x.dtype), B, H, W, C, num_extra_tokens, r,
-            ptr(self.router.gate.weight.detach().float().contiguous()),
-            ptr(self.router.gate.bias.detach().float().contiguous()), S, ptr(gate), ptr(indices),
-            stream_ptr(x.device)))
+            ptr(x), dtype_code(x.dtype), B, H, W, C, num_extra_tokens, r, ptr(gate_w), ptr(gate_b), S, ptr(gate),
+            ptr(indices), stream_ptr(x.device)))
         patches, batches = grained_sample_index_to_patch(indices, self.splits, r, num_extra_tokens)
         comp = grained_sample_compress(x, patches, H, W, num_extra_tokens)
         self.states.update({

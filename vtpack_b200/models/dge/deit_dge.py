@@ -46,9 +46,10 @@ def _linear(x, lin: nn.Linear, residual=None, gelu=False, flags=0):
 def _layernorm(x, ln: nn.LayerNorm):
     x2 = x.reshape(-1, x.shape[-1]).contiguous()
     y = torch.empty_like(x2)
+    # both fp32 copies must be alive together: a temporary freed between the two would hand its memory to the other
+    w, b = ln.weight.detach().float().contiguous(), ln.bias.detach().float().contiguous()
     _lib.check(_lib.lib().vtp_layernorm(
-        ptr(x2), dtype_code(x2.dtype), x2.shape[0], None, x2.shape[1], x2.shape[1],
-        ptr(ln.weight.detach().float().contiguous()), ptr(ln.bias.detach().float().contiguous()),
+        ptr(x2), dtype_code(x2.dtype), x2.shape[0], None, x2.shape[1], x2.shape[1], ptr(w), ptr(b),
         float(ln.eps), ptr(y), stream_ptr(x.device)))
     return y.reshape(x.shape)
 
