@@ -417,8 +417,32 @@ def pvt_sweep(args):
         rows.append({"stage": f"C={C} heads={heads} grid={H}x{H} sr={sr}", "queries_per_image": round(L / B, 1),
                      "keys": nk, "block_us": round(us, 1), "tflops": round(flops / us / 1e6, 1),
                      "cpu_oracle_us_scaled_to_batch": round(cpu_us)})
+    # the whole PVT+DGE tiny model (4 stages, 8 blocks), kernel-by-kernel launches
+    from vtpack_b200.models.dge.pvt_dge import pvt_dge_s124_tiny_256
+    cfg = O.PVT_CONFIGS["tiny"]
+    sd = O.make_pvt_state_dict(cfg, seed=0)
+    m = pvt_dge_s124_tiny_256()
+    m.load_state_dict(sd, strict=True)
+    m = m.eval().to(device=dev, dtype=torch.bfloat16)
+    img = torch.randn(B, 3, 256, 256, device=dev, generator=torch.Generator(dev).manual_seed(4))
+    for _ in range(3):
+        m(img)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        m(img)
+    e1.record()
+    torch.cuda.synchronize()
+    model_ms = e0.elapsed_time(e1) / 10
+    xc = O.make_images(4, 256, seed=5)
+    t0 = time.perf_counter()
+    O.pvt_dge_forward(xc, sd, cfg)
+    cpu_rate = 4 / (time.perf_counter() - t0)
     assert _lib.device_status() == 0
-    print(json.dumps({"pvt_sweep": rows, "batch": B, "dtype": "bf16"}), flush=True)
+    print(json.dumps({"pvt_sweep": rows, "batch": B, "dtype": "bf16",
+                      "pvt_tiny_model": {"ms_per_forward": round(model_ms, 3), "images_per_s": round(B / model_ms * 1e3),
+                                         "cpu_oracle_images_per_s": round(cpu_rate, 1)}}), flush=True)
 
 
 def main():

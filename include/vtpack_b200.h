@@ -203,6 +203,24 @@ int vtp_patch_im2col(const void* images, int image_dtype, int B, int S, int P, i
                      const void* cls_token, const void* pos_embed, int C, void* x,
                      void* stream);
 
+/*
+ * Stride-`ratio` window gather on a token grid: x [B, H*W, C] -> cols [B*(H/ratio)*(W/ratio), ratio*ratio*C],
+ * column (dy, dx, c).  With vtp_linear it is a convolution of kernel = stride = ratio whose weight
+ * [C_out, C_in, ratio, ratio] was reordered once to [C_out, (dy, dx, c_in)]: the spatial reduction of a
+ * PVT block (vtpack/models/dge/pvt_dge.py:82-83) and the patch embedding between PVT stages
+ * (PatchEmbed, pvt_dge.py:149-179; there the tokens stand for the [B, C, H, W] map of pvt_dge.py:315).
+ */
+int vtp_token_im2col(const void* x, int dtype, int B, int H, int W, int C, int ratio, void* cols, void* stream);
+
+/*
+ * out[orow(r), :] = x[r % x_mod, :] + addend[r % a_mod + a_off, :] for r < rows, with
+ * orow(r) = (r / out_grp) * out_stride + out_off + r % out_grp.  The position-embedding add of a stage
+ * (x_mod = rows, a_mod = tokens per image) and, with x_mod = a_mod = out_grp = 1, the cls rows that go in
+ * front of each image's tokens (pvt_dge.py:306-313; deit_dge.py:271-275).
+ */
+int vtp_add_rows(const void* x, int x_mod, const void* addend, int a_mod, int a_off, void* out, int out_grp,
+                 int out_stride, int out_off, int dtype, long long rows, int C, void* stream);
+
 /* Pointers to one block's parameters (device memory).  Matrices are in the model dtype,
  * vectors fp32.  Keys are the reference's state_dict names below blocks.{i}. */
 typedef struct {

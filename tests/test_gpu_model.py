@@ -325,3 +325,32 @@ def test_pvt_block_stages(C, heads, H, sr, mr, extra, dtype):
     assert blk.dge.states["batches_device"].tolist() == tr["batches"].tolist()
     err = rel_err(out.float(), ref)
     assert err < (1e-4 if dtype == torch.float32 else 2e-2), err
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pvt_model(golden_dir, dtype):
+    """PVT+DGE tiny (4 stages, 8 blocks, patch 4: 4096 -> 64 tokens) through the mirror model: fp32
+    against the reference's own logits and query counts; bf16 against the fp32 oracle on bf16-rounded
+    weights (logits within 2e-2 max-abs)."""
+    from vtpack_b200 import _lib
+    from vtpack_b200.models.dge.pvt_dge import pvt_dge_s124_tiny_256
+    g = np.load(os.path.join(golden_dir, "pvt_model_fp32.npz"))
+    cfg = O.PVT_CONFIGS["tiny"]
+    sd = O.make_pvt_state_dict(cfg, seed=0)
+    img = O.make_images(2, 256, seed=8)
+    if dtype == torch.bfloat16:
+        sd = O.round_bf16(sd)
+        ref = O.pvt_dge_forward(img, sd, cfg)
+    else:
+        ref = torch.from_numpy(g["logits"])
+    m = pvt_dge_s124_tiny_256()
+    m.load_state_dict(sd, strict=True)
+    m = m.eval().to(device=DEV, dtype=dtype)
+    logits = m(img.to(DEV)).cpu()
+    assert _lib.device_status() == 0
+    if dtype == torch.float32:
+        assert g["gate_margin"].min() > 1e-5
+        assert [c.tolist() for c in m.last_counts] == g["batch_lengths"].tolist()
+        assert rel_err(logits, ref) < 1e-4
+    else:
+        assert float((logits - ref).abs().max()) < 2e-2

@@ -55,6 +55,9 @@ PROTOTYPES = {
                                c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "vtp_layernorm": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_float,
                               c_void_p, c_void_p]),
+    "vtp_token_im2col": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "vtp_add_rows": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_ll,
+                             c_int, c_void_p]),
     "vtp_linear": (c_int, [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_ll, c_int,
                            c_int, c_void_p, c_int, c_int, c_uint, c_void_p]),
     "vtp_fold_layernorm": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

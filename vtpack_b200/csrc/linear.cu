@@ -17,7 +17,10 @@ int linear_validate(const LinearArgs& p) {
 
 int linear(const LinearArgs& p, cudaStream_t st) {
     if (int rc = linear_validate(p)) return rc;
-    if (p.dtype == VTP_BF16 && !(p.flags & VTP_FLAG_CUDA_CORES)) return linear_tcgen05(p, st);
+    // the tensor-core kernel takes K in 64-element TMA boxes; a narrower reduction (PVT's 4x4x3 patch
+    // embedding, K = 48) is small enough for the CUDA-core kernel
+    const bool tc_shape = p.K % 64 == 0 || p.ln_mode != 0 || p.emit_stats;
+    if (p.dtype == VTP_BF16 && !(p.flags & VTP_FLAG_CUDA_CORES) && tc_shape) return linear_tcgen05(p, st);
     VTP_REQUIRE(p.ln_mode == 0 && !p.emit_stats, VTP_ERR_UNSUPPORTED,
                 "linear (CUDA cores): folded LayerNorm is a feature of the tcgen05 kernel");
     return linear_cuda_cores(p, st);

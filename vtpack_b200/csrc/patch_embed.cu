@@ -22,6 +22,29 @@ __device__ __forceinline__ void load8(const bf16* p, float* f) {
     v.to_float(f);
 }
 
+// Patches narrower than 8 pixels (PVT's first stage: 4 x 4): one thread moves 4 adjacent pixels.
+template <typename I, typename T>
+__global__ void __launch_bounds__(256)
+im2col4_kernel(const I* __restrict__ img, long long total4, int S, int P, T* __restrict__ cols) {
+    const int G = S / P;
+    const int KP = 3 * P * P;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total4;
+         e += (long long)gridDim.x * blockDim.x) {
+        const long long pix = e * 4;
+        const int ix = (int)(pix % S);
+        const int iy = (int)((pix / S) % S);
+        const int c = (int)((pix / ((long long)S * S)) % 3);
+        const long long b = pix / ((long long)3 * S * S);
+        float f[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = to_f32(img[pix + i]);
+        const int gy = iy / P, py = iy % P, gx = ix / P, px = ix % P;
+        T* dst = cols + ((b * G + gy) * G + gx) * KP + c * P * P + py * P + px;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = from_f32<T>(f[i]);
+    }
+}
+
 template <typename I, typename T>
 __global__ void __launch_bounds__(256)
 im2col_kernel(const I* __restrict__ img, long long total8, int S, int P, T* __restrict__ cols) {
@@ -95,19 +118,91 @@ int token_im2col(const void* x, int dtype, int B, int H, int W, int C, int sr, v
     return check_launch("spatial reduction im2col");
 }
 
+// out[orow(r)] = x[r % x_mod] + addend[r % a_mod + a_off], orow(r) = (r / out_grp) * out_stride + out_off + r % out_grp:
+// the position-embedding add of a token stage, and (x_mod = a_mod = out_grp = 1) the cls rows put in front of it.
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_rows_kernel(const T* __restrict__ x, int x_mod, const T* __restrict__ addend, int a_mod, int a_off,
+                T* __restrict__ out, int out_grp, int out_stride, int out_off, long long total_vec, int C) {
+    constexpr int VN = Vec<T>::N;
+    const int cv = C / VN;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total_vec;
+         v += (long long)gridDim.x * blockDim.x) {
+        const long long r = v / cv;
+        const int i = (int)(v % cv) * VN;
+        Vec<T> a, p;
+        float fa[VN], fp[VN];
+        a.load(x + (r % x_mod) * C + i);
+        p.load(addend + (r % a_mod + a_off) * C + i);
+        a.to_float(fa);
+        p.to_float(fp);
+#pragma unroll
+        for (int k = 0; k < VN; ++k) fa[k] += fp[k];
+        a.from_float(fa);
+        a.store(out + ((r / out_grp) * out_stride + out_off + r % out_grp) * C + i);
+    }
+}
+
 }  // namespace vtp
 
 using namespace vtp;
+
+extern "C" int vtp_token_im2col(const void* x, int dtype, int B, int H, int W, int C, int ratio, void* cols,
+                                void* stream) {
+    VTP_REQUIRE(x && cols, VTP_ERR_NULL, "token im2col: null pointer");
+    VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "token im2col: dtype %d", dtype);
+    VTP_REQUIRE(B > 0 && H > 0 && W > 0 && C > 0 && ratio > 0 && H % ratio == 0 && W % ratio == 0, VTP_ERR_SHAPE,
+                "token im2col: grid %dx%d / ratio %d", H, W, ratio);
+    VTP_REQUIRE(aligned16(x) && aligned16(cols), VTP_ERR_ALIGN, "token im2col: unaligned pointer");
+    return token_im2col(x, dtype, B, H, W, C, ratio, cols, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vtp_add_rows(const void* x, int x_mod, const void* addend, int a_mod, int a_off, void* out, int out_grp,
+                            int out_stride, int out_off, int dtype, long long rows, int C, void* stream) {
+    VTP_REQUIRE(x && addend && out, VTP_ERR_NULL, "add rows: null pointer");
+    VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "add rows: dtype %d", dtype);
+    const int vn = dtype == VTP_BF16 ? 8 : 4;
+    VTP_REQUIRE(rows >= 0 && C > 0 && C % vn == 0 && x_mod > 0 && a_mod > 0 && a_off >= 0 && out_grp > 0 &&
+                    out_stride >= out_grp && out_off >= 0,
+                VTP_ERR_SHAPE, "add rows: bad shape");
+    VTP_REQUIRE(aligned16(x) && aligned16(addend) && aligned16(out), VTP_ERR_ALIGN, "add rows: unaligned pointer");
+    const long long total = rows * (C / vn);
+    if (total == 0) return VTP_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = (int)((total + 255) / 256 < (long long)sm_count() * 16 ? (total + 255) / 256 : (long long)sm_count() * 16);
+    if (dtype == VTP_BF16)
+        add_rows_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, x_mod, (const bf16*)addend, a_mod, a_off, (bf16*)out,
+                                                   out_grp, out_stride, out_off, total, C);
+    else
+        add_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)x, x_mod, (const float*)addend, a_mod, a_off,
+                                                    (float*)out, out_grp, out_stride, out_off, total, C);
+    return check_launch("add rows");
+}
 
 extern "C" int vtp_patch_im2col(const void* images, int image_dtype, int B, int S, int P, int dtype, void* cols,
                                 const void* cls_token, const void* pos_embed, int C, void* x, void* stream) {
     VTP_REQUIRE(images && cols, VTP_ERR_NULL, "im2col: null pointer");
     VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "im2col: dtype %d", dtype);
     VTP_REQUIRE(image_dtype == VTP_F32 || image_dtype == VTP_BF16, VTP_ERR_DTYPE, "im2col: image dtype %d", image_dtype);
-    VTP_REQUIRE(B > 0 && S > 0 && P > 0 && S % P == 0 && P % 8 == 0, VTP_ERR_SHAPE,
-                "im2col: image %d / patch %d (patch must be a multiple of 8)", S, P);
+    VTP_REQUIRE(B > 0 && S > 0 && P > 0 && S % P == 0 && P % 4 == 0, VTP_ERR_SHAPE,
+                "im2col: image %d / patch %d (patch must be a multiple of 4)", S, P);
     VTP_REQUIRE(aligned16(images) && aligned16(cols), VTP_ERR_ALIGN, "im2col: unaligned pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (P % 8 != 0) {
+        VTP_REQUIRE(!x, VTP_ERR_UNSUPPORTED, "im2col: the cls row is written for patches that are multiples of 8 only");
+        const long long total4 = (long long)B * 3 * S * S / 4;
+        const int g4 = (int)((total4 + 255) / 256 < (long long)sm_count() * 16 ? (total4 + 255) / 256
+                                                                                : (long long)sm_count() * 16);
+        if (image_dtype == VTP_F32 && dtype == VTP_F32)
+            im2col4_kernel<float, float><<<g4, 256, 0, st>>>((const float*)images, total4, S, P, (float*)cols);
+        else if (image_dtype == VTP_F32)
+            im2col4_kernel<float, bf16><<<g4, 256, 0, st>>>((const float*)images, total4, S, P, (bf16*)cols);
+        else if (dtype == VTP_F32)
+            im2col4_kernel<bf16, float><<<g4, 256, 0, st>>>((const bf16*)images, total4, S, P, (float*)cols);
+        else
+            im2col4_kernel<bf16, bf16><<<g4, 256, 0, st>>>((const bf16*)images, total4, S, P, (bf16*)cols);
+        return check_launch("im2col");
+    }
     const long long total8 = (long long)B * 3 * S * S / 8;
     const int grid = (int)((total8 + 255) / 256 < (long long)sm_count() * 16 ? (total8 + 255) / 256
                                                                              : (long long)sm_count() * 16);

@@ -2,20 +2,24 @@
 same class names, constructor arguments and state_dict keys, with ``Block.forward(x, H, W)`` as
 one call into the CUDA library.  Keys and values come from the normed tokens reduced by the
 stride-``sr_ratio`` convolution ``attn.sr`` and the LayerNorm ``attn.norm``; everything else is
-the DeiT+DGE block.  Only the block is mirrored here; the pyramid wrapper around it (patch
-embeddings between stages, position embeddings, head) is not.
+the DeiT+DGE block.  ``PyramidVisionTransformer`` (``pvt_dge.py:182-337``) sequences the stages
+through the library's entry points: patch embedding = im2col + Linear + LayerNorm, position
+embedding / cls rows = ``vtp_add_rows``, blocks, and between stages the token rows themselves
+stand for the ``[B, C, H, W]`` map (``vtp_token_im2col`` gathers the 2 x 2 windows from them).
 """
 import ctypes
+from functools import partial
 
 import torch
 import torch.nn as nn
 
 from ... import _lib
 from ...layers import DynamicGrainedEncoder
-from ...runtime import ptr, require_cuda, scratch, stream_ptr
+from ...runtime import dtype_code, ptr, require_cuda, scratch, stream_ptr
 from .deit_dge import Mlp, _WeightPack, _pack_block, _shape_struct
 
-__all__ = ["Mlp", "Attention", "Block"]
+__all__ = ["Mlp", "Attention", "Block", "PatchEmbed", "PyramidVisionTransformer",
+           "pvt_dge_s124_tiny_256", "pvt_dge_s124_small_256", "pvt_dge_s124_medium_256", "pvt_dge_s124_large_256"]
 
 
 class Attention(nn.Module):
@@ -101,3 +105,168 @@ class Block(nn.Module):
         self.dge.states.update({"batches_device": counts, "input": x, "gate": None, "size": (H, W),
                                 "num_extra_tokens": N - H * W})
         return out
+
+
+class PatchEmbed(nn.Module):
+    """Image (or previous stage's map) to patch embedding: convolution with kernel = stride =
+    patch_size, then LayerNorm (``pvt_dge.py:149-179``)."""
+
+    def __init__(self, img_size=224, patch_size=16, in_chans=3, embed_dim=768):
+        super().__init__()
+        self.img_size = (img_size, img_size)
+        self.patch_size = (patch_size, patch_size)
+        self.H, self.W = img_size // patch_size, img_size // patch_size
+        self.num_patches = self.H * self.W
+        self.proj = nn.Conv2d(in_chans, embed_dim, kernel_size=patch_size, stride=patch_size)
+        self.norm = nn.LayerNorm(embed_dim)
+
+    def complexity(self, num_inputs, num_queries):
+        comp = num_inputs * self.proj.in_channels * self.proj.out_channels
+        comp += num_inputs / (self.patch_size[0] * self.patch_size[1]) * self.proj.out_channels  # norm
+        return comp
+
+
+def _matmul_rows(cols, weight, bias, flags=0, out_dtype=None):
+    """cols [M, K] x weight [N, K]^T + bias through vtp_linear."""
+    M, K = cols.shape
+    N = weight.shape[0]
+    y = torch.empty(M, N, dtype=out_dtype or cols.dtype, device=cols.device)
+    b = None if bias is None else bias.detach().float().contiguous()
+    _lib.check(_lib.lib().vtp_linear(ptr(cols), K, ptr(weight), ptr(b), None, 0, ptr(y), N, dtype_code(cols.dtype), M,
+                                     None, N, K, flags, stream_ptr(cols.device)))
+    return y
+
+
+def _norm_rows(x, rows, C, row_stride, ln, eps=None):
+    y = torch.empty(rows, C, dtype=x.dtype, device=x.device)
+    # both fp32 copies must be alive together: a temporary freed between the two would hand its memory to the other
+    w, b = ln.weight.detach().float().contiguous(), ln.bias.detach().float().contiguous()
+    _lib.check(_lib.lib().vtp_layernorm(ptr(x), dtype_code(x.dtype), rows, None, C, row_stride, ptr(w), ptr(b),
+                                        float(ln.eps if eps is None else eps), ptr(y), stream_ptr(x.device)))
+    return y
+
+
+class PyramidVisionTransformer(nn.Module):
+
+    def __init__(self, img_size=224, patch_size=16, in_chans=3, num_classes=1000, embed_dims=[64, 128, 256, 512],
+                 num_heads=[1, 2, 4, 8], mlp_ratios=[4, 4, 4, 4], qkv_bias=False, qk_scale=None, drop_rate=0.,
+                 attn_drop_rate=0., drop_path_rate=0., norm_layer=nn.LayerNorm,
+                 depths=[3, 4, 6, 3], sr_ratios=[8, 4, 2, 1], num_stages=4,
+                 split_sizes=[[2, 1], [2, 1], [2, 1], [2, 1]]):
+        super().__init__()
+        assert in_chans == 3, "the image im2col kernel is written for 3 channels"
+        self.embed_dims = embed_dims
+        self.num_classes = num_classes
+        self.depths = depths
+        self.num_stages = num_stages
+        self.img_size = img_size
+        for i in range(num_stages):
+            patch_embed = PatchEmbed(img_size=img_size if i == 0 else img_size // (2 ** (i + 1)),
+                                     patch_size=patch_size if i == 0 else 2,
+                                     in_chans=in_chans if i == 0 else embed_dims[i - 1], embed_dim=embed_dims[i])
+            num_patches = patch_embed.num_patches if i != num_stages - 1 else patch_embed.num_patches + 1
+            pos_embed = nn.Parameter(torch.zeros(1, num_patches, embed_dims[i]))
+            block = nn.ModuleList([Block(
+                dim=embed_dims[i], num_heads=num_heads[i], mlp_ratio=mlp_ratios[i], qkv_bias=qkv_bias,
+                qk_scale=qk_scale, drop=drop_rate, attn_drop=attn_drop_rate, norm_layer=norm_layer,
+                sr_ratio=sr_ratios[i], split_sizes=split_sizes[i]) for _ in range(depths[i])])
+            setattr(self, f"patch_embed{i + 1}", patch_embed)
+            setattr(self, f"pos_embed{i + 1}", pos_embed)
+            setattr(self, f"pos_drop{i + 1}", nn.Dropout(p=drop_rate))
+            setattr(self, f"block{i + 1}", block)
+        self.norm = norm_layer(embed_dims[3]) if num_classes > 0 else nn.Identity()
+        self.cls_token = nn.Parameter(torch.zeros(1, 1, embed_dims[3]))
+        self.head = nn.Linear(embed_dims[3], num_classes) if num_classes > 0 else nn.Identity()
+        for i in range(num_stages):
+            nn.init.trunc_normal_(getattr(self, f"pos_embed{i + 1}"), std=.02)
+        nn.init.trunc_normal_(self.cls_token, std=.02)
+        for m in self.modules():
+            if isinstance(m, nn.Linear):
+                nn.init.trunc_normal_(m.weight, std=.02)
+                if m.bias is not None:
+                    nn.init.constant_(m.bias, 0)
+            elif isinstance(m, nn.LayerNorm):
+                nn.init.constant_(m.bias, 0)
+                nn.init.constant_(m.weight, 1.0)
+            elif isinstance(m, DynamicGrainedEncoder):
+                m.router.init_parameters()
+        self.last_counts = None
+
+    def forward(self, x):
+        """images [B,3,S,S] on the device -> logits fp32 [B,num_classes] (``pvt_dge.py:295-337``,
+        classification path at the training resolution)."""
+        if self.training:
+            raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
+        if self.num_classes <= 0:
+            raise NotImplementedError("the feature-pyramid outputs (num_classes = 0) are not mirrored")
+        require_cuda(x)
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            x = x.float()
+        x = x.contiguous()
+        B, _, S, _ = x.shape
+        dtype = self.cls_token.dtype
+        lib, st = _lib.lib(), stream_ptr(x.device)
+        counts = []
+        tokens, H, W = None, 0, 0
+        for i in range(self.num_stages):
+            pe = getattr(self, f"patch_embed{i + 1}")
+            pos = getattr(self, f"pos_embed{i + 1}").detach()[0].contiguous()
+            C = self.embed_dims[i]
+            P = pe.patch_size[0]
+            if i == 0:
+                if pe.H * P != S:
+                    raise NotImplementedError("position-embedding interpolation (other input sizes) is not mirrored")
+                H = W = S // P
+                cols = torch.empty(B * H * W, 3 * P * P, dtype=dtype, device=x.device)
+                _lib.check(lib.vtp_patch_im2col(ptr(x), dtype_code(x.dtype), B, S, P, dtype_code(dtype), ptr(cols),
+                                                None, None, C, None, st))
+                wm = pe.proj.weight.detach().reshape(C, -1).to(dtype).contiguous()
+            else:
+                cols = torch.empty(B * (H // P) * (W // P), P * P * tokens.shape[-1], dtype=dtype, device=x.device)
+                _lib.check(lib.vtp_token_im2col(ptr(tokens), dtype_code(dtype), B, H, W, tokens.shape[-1], P, ptr(cols), st))
+                H, W = H // P, W // P
+                wm = pe.proj.weight.detach().permute(0, 2, 3, 1).reshape(C, -1).to(dtype).contiguous()
+            y = _matmul_rows(cols, wm, pe.proj.bias)
+            y = _norm_rows(y, y.shape[0], C, C, pe.norm)
+            HW = H * W
+            last = i == self.num_stages - 1
+            tokens = torch.empty(B, HW + (1 if last else 0), C, dtype=dtype, device=x.device)
+            _lib.check(lib.vtp_add_rows(ptr(y), B * HW, ptr(pos), HW, 1 if last else 0, ptr(tokens), HW,
+                                        HW + (1 if last else 0), 1 if last else 0, dtype_code(dtype), B * HW, C, st))
+            if last:
+                cls = self.cls_token.detach().reshape(1, C).contiguous()
+                _lib.check(lib.vtp_add_rows(ptr(cls), 1, ptr(pos), 1, 0, ptr(tokens), 1, HW + 1, 0, dtype_code(dtype),
+                                            B, C, st))
+            for blk in getattr(self, f"block{i + 1}"):
+                tokens = blk(tokens, H, W)
+                counts.append(blk.dge.states["batches_device"])
+        N = tokens.shape[1]
+        C = tokens.shape[2]
+        cls_n = _norm_rows(tokens, B, C, N * C, self.norm)
+        logits = _matmul_rows(cls_n, self.head.weight.detach().to(dtype).contiguous(), self.head.bias,
+                              flags=_lib.FLAG_OUT_F32, out_dtype=torch.float32)
+        self.last_counts = counts
+        return logits
+
+
+def _pvt(depths, **kwargs):
+    return PyramidVisionTransformer(
+        img_size=256, patch_size=4, embed_dims=[64, 128, 320, 512], num_heads=[1, 2, 5, 8], mlp_ratios=[8, 8, 4, 4],
+        qkv_bias=True, norm_layer=partial(nn.LayerNorm, eps=1e-6), depths=depths, sr_ratios=[8, 4, 2, 1],
+        split_sizes=[[4, 2, 1], [4, 2, 1], [4, 2, 1], [4, 2, 1]], **kwargs)
+
+
+def pvt_dge_s124_tiny_256(pretrained=False, **kwargs):
+    return _pvt([2, 2, 2, 2], **kwargs)
+
+
+def pvt_dge_s124_small_256(pretrained=False, **kwargs):
+    return _pvt([3, 4, 6, 3], **kwargs)
+
+
+def pvt_dge_s124_medium_256(pretrained=False, **kwargs):
+    return _pvt([3, 4, 18, 3], **kwargs)
+
+
+def pvt_dge_s124_large_256(pretrained=False, **kwargs):
+    return _pvt([3, 8, 27, 3], **kwargs)
