@@ -237,3 +237,51 @@ def test_attention_strided_views(vl):
     got = layers.batched_sparse_attention(qv, kvp[0], kvp[1], torch.tensor(lens), d ** -0.5)
     assert rel_err(got, ref) < 1e-5
     assert got.transpose(0, 1).reshape(-1, h * d).is_contiguous()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,H,W,C,ratio", [(2, 8, 8, 64, 2), (3, 16, 8, 128, 4), (1, 32, 32, 64, 8), (2, 4, 4, 320, 2)])
+def test_token_im2col_is_a_strided_convolution(vl, dtype, B, H, W, C, ratio):
+    """vtp_token_im2col + a matrix product against F.conv2d(kernel = stride = ratio) on the same
+    tokens seen as a [B,C,H,W] map (the weight reordered to columns (dy, dx, c_in)); the gather itself
+    is checked bit for bit."""
+    _lib, _ = vl
+    from vtpack_b200.runtime import dtype_code, ptr, stream_ptr
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(B, H * W, C, generator=g).to(dtype).to(DEV)
+    cols = torch.empty(B * (H // ratio) * (W // ratio), ratio * ratio * C, dtype=dtype, device=DEV)
+    _lib.check(_lib.lib().vtp_token_im2col(ptr(x), dtype_code(dtype), B, H, W, C, ratio, ptr(cols), stream_ptr(x.device)))
+    ref = x.reshape(B, H // ratio, ratio, W // ratio, ratio, C).permute(0, 1, 3, 2, 4, 5).reshape(cols.shape)
+    assert torch.equal(cols, ref)
+    w = torch.randn(C, C, ratio, ratio, generator=g) * 0.05
+    conv = F.conv2d(x.float().cpu().permute(0, 2, 1).reshape(B, C, H, W), w, stride=ratio).flatten(2).transpose(1, 2)
+    got = cols.float().cpu() @ w.permute(0, 2, 3, 1).reshape(C, -1).t()
+    assert rel_err(got.reshape(conv.shape), conv) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_rows_position_embedding_and_cls_rows(vl, dtype):
+    """vtp_add_rows as the model uses it: tokens + position embedding written behind a cls slot, then
+    the cls rows themselves; compared with the same sums done by PyTorch in the same dtype order."""
+    _lib, _ = vl
+    from vtpack_b200.runtime import dtype_code, ptr, stream_ptr
+    B, HW, C = 3, 64, 192
+    g = torch.Generator().manual_seed(2)
+    y = torch.randn(B * HW, C, generator=g).to(dtype).to(DEV)
+    pos = torch.randn(HW + 1, C, generator=g).to(dtype).to(DEV)
+    cls = torch.randn(1, C, generator=g).to(dtype).to(DEV)
+    out = torch.zeros(B, HW + 1, C, dtype=dtype, device=DEV)
+    lib, st = _lib.lib(), stream_ptr(y.device)
+    _lib.check(lib.vtp_add_rows(ptr(y), B * HW, ptr(pos), HW, 1, ptr(out), HW, HW + 1, 1, dtype_code(dtype), B * HW, C, st))
+    _lib.check(lib.vtp_add_rows(ptr(cls), 1, ptr(pos), 1, 0, ptr(out), 1, HW + 1, 0, dtype_code(dtype), B, C, st))
+    ref = torch.cat(((cls.float() + pos[0:1].float()).expand(B, 1, C),
+                     y.float().reshape(B, HW, C) + pos[1:].float()[None]), dim=1).to(dtype)
+    assert torch.equal(out, ref)
+
+
+def test_linear_bf16_narrow_reduction_uses_cuda_cores(vl):
+    """K = 48 (PVT's 4 x 4 x 3 patch embedding) is not a multiple of the tensor-core kernel's 64-element
+    K box: vtp_linear must still answer, through the CUDA-core kernel."""
+    _lib, _ = vl
+    got, ref = _linear_case(500, 64, 48, torch.bfloat16, False, False, 0)
+    assert rel_err(got.float(), ref) < 8e-3

@@ -301,6 +301,26 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 tmem_ld_32x16(tacc + qsub * 16, r);
 #pragma unroll 1
                 for (int sl = 0; sl < NSLAB; ++sl, ++slab_no) {
+                    // the additive part of this slab's 16 columns (bias, or bias + ln_b * s for a folded
+                    // LayerNorm), fetched from shared memory while the accumulator columns are on their way
+                    float cadd[16];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float4* bs = reinterpret_cast<const float4*>(bias_s + sl * 64 + (qsub * 2 + j) * 8);
+                        const float4 b0 = bs[0];
+                        const float4 b1 = bs[1];
+                        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                        if (EPI & EPI_LN) {
+                            const float4 s0 = bs[BN / 4];
+                            const float4 s1 = bs[BN / 4 + 1];
+                            const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) cadd[8 * j + i] = fmaf(ln_b, ss[i], bb[i]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) cadd[8 * j + i] = bb[i];
+                        }
+                    }
                     tmem_ld_wait();
                     float v[16];
 #pragma unroll
@@ -324,19 +344,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         float* vj = v + 8 * j;
                         const int chunk = qsub * 2 + j;                          // 16-byte chunk within the 128-byte row
                         uint4* cell = reinterpret_cast<uint4*>(srow + ((chunk ^ (row & 7)) << 4));
-                        const float4* bs = reinterpret_cast<const float4*>(bias_s + sl * 64 + chunk * 8);
-                        const float4 b0 = bs[0];
-                        const float4 b1 = bs[1];
-                        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
                         if (EPI & EPI_LN) {
-                            const float4 s0 = bs[BN / 4];
-                            const float4 s1 = bs[BN / 4 + 1];
-                            const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) vj[i] = fmaf(ln_a, vj[i], fmaf(ln_b, ss[i], bb[i]));
+                            for (int i = 0; i < 8; ++i) vj[i] = fmaf(ln_a, vj[i], cadd[8 * j + i]);
                         } else {
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) vj[i] += bb[i];
+                            for (int i = 0; i < 8; ++i) vj[i] += cadd[8 * j + i];
                         }
                         if (EPI & EPI_GELU) gelu8(vj);
                         if (res) {
