@@ -19,6 +19,8 @@
 //                        last columns are in registers.  Tiles that touch the last valid row,
 //                        row-remapped outputs and fp32 outputs store straight from registers.
 // The two accumulators let the MMA of tile i+1 overlap the epilogue of tile i.
+// The tiles left for the last, partial round of the grid are cut into two to four column strips
+// (their own W boxes, a narrower MMA), one per CTA, so that round costs a fraction of a tile.
 // The number of valid rows is read from device memory: tiles beyond it do not exist, rows
 // beyond it are never stored.
 //
@@ -110,6 +112,7 @@ constexpr int EPI_GELU = 1, EPI_LN = 2, EPI_EMIT = 4;
 template <int BN, int STAGES, typename OutT, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                 const __grid_constant__ CUtensorMap tmap_w2, const __grid_constant__ CUtensorMap tmap_w3,
                  const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_r,
                  int use_tma_store, const float* __restrict__ bias, const bf16* __restrict__ res, long long ldr,
                  OutT* __restrict__ y, long long ldy, int m_max, const int32_t* __restrict__ m_dev, int N,
@@ -166,6 +169,41 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // no tiles for this CTA, or an earlier CTA gave up on a wait (the launch is void): skip the work
     const bool void_launch = status && *reinterpret_cast<volatile int*>(status) != 0;
     const int total = void_launch ? 0 : ((M + TBM - 1) / TBM) * n_tiles;
+    // Tail splitting.  A CTA takes tiles blockIdx.x, + gridDim.x, ...; the R tiles left for the last,
+    // partial round are cut into `parts` column strips of BN / parts columns, one strip per CTA, so that
+    // the round costs a fraction of a tile instead of a whole one with most SMs idle.  Strips use their
+    // own W boxes (tmap_w2 / tmap_w3) and a narrower MMA; kernels that keep per-tile row statistics
+    // (EPI_EMIT) do not split.
+    const int full_items = (total / (int)gridDim.x) * (int)gridDim.x;
+    int parts = 1;
+    {
+        const int R = total - full_items, G = (int)gridDim.x;
+        if (!(EPI & EPI_EMIT) && R > 0) {
+            if (BN == 256) parts = (R * 4 <= G) ? 4 : (R * 2 <= G ? 2 : 1);
+            else if (BN == 192) parts = (R * 3 <= G) ? 3 : 1;
+            else parts = (R * 2 <= G) ? 2 : 1;
+        }
+    }
+    // j-th work item of this CTA: rows m0.., columns ct0 .. ct0 + width of the output
+    struct Item { int m0, nt, ct0, width; };
+    auto item_at = [&](int j, Item& it) -> bool {
+        const int idx = (int)blockIdx.x + j * (int)gridDim.x;
+        int tile, sub = 0, p = 1;
+        if (idx < full_items) {
+            tile = idx;
+        } else {
+            const int u = idx - full_items;
+            if (u >= (total - full_items) * parts) return false;
+            tile = full_items + u / parts;
+            sub = u % parts;
+            p = parts;
+        }
+        it.m0 = (tile / n_tiles) * TBM;
+        it.nt = tile % n_tiles;
+        it.width = BN / p;
+        it.ct0 = it.nt * BN + sub * it.width;
+        return true;
+    };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -174,17 +212,19 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             prefetch_tmap(&tmap_w);
             int it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-                const int m0 = (t / n_tiles) * TBM;
-                const int n0 = (t % n_tiles) * BN;
+            Item wi;
+            for (int j = 0; ok && item_at(j, wi); ++j) {
+                // the W box that is as tall as the item is wide
+                const CUtensorMap* wm = wi.width == BN ? &tmap_w : ((BN == 256 && wi.width == 64) ? &tmap_w3 : &tmap_w2);
+                const uint32_t bytes = S::A_BYTES + (uint32_t)wi.width * TBK * 2;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, status, STATUS_GEMM_PRODUCER);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&full[s], S::A_BYTES + S::B_BYTES);
-                    tma_load_2d(smem_a + s * S::A_BYTES, &tmap_a, &full[s], kb * TBK, m0);
-                    tma_load_2d(smem_b + s * S::B_BYTES, &tmap_w, &full[s], kb * TBK, n0);
+                    mbar_arrive_expect_tx(&full[s], bytes);
+                    tma_load_2d(smem_a + s * S::A_BYTES, &tmap_a, &full[s], kb * TBK, wi.m0);
+                    tma_load_2d(smem_b + s * S::B_BYTES, wm, &full[s], kb * TBK, wi.ct0);
                 }
             }
         }
@@ -192,10 +232,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else if (warp == 1) {
         if (lane == 0) {
             // -------------------------------------------------------------- MMA issuer
-            constexpr uint32_t idesc = idesc_bf16_f32(TBM, BN, 0, 0);
             int it = 0, lt = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++lt) {
+            Item wi;
+            for (int j = 0; ok && item_at(j, wi); ++j, ++lt) {
+                const uint32_t idesc = idesc_bf16_f32(TBM, wi.width, 0, 0);
                 const int buf = lt & 1;
                 const uint32_t aph = (lt >> 1) & 1;
                 ok = mbar_wait(&acc_empty[buf], aph ^ 1, abort_flag, status, STATUS_GEMM_MMA);
@@ -227,13 +268,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int qsub = (warp - 2) >> 2;             // which of the four warps of that quarter
         const bool elected = threadIdx.x == 64;       // issues the TMA stores / residual loads
         const int row = quarter * 32 + lane;          // tile row = TMEM lane
-        constexpr int NSLAB = BN / 64;
         int lt = 0, slab_no = 0;
         int res_issued = -1;                          // elected thread: last slab whose residual load was issued
         bool ok = true;
-        for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++lt) {
-            const int m0 = (t / n_tiles) * TBM;
-            const int nt0 = (t % n_tiles) * BN;
+        Item wi;
+        for (int j = 0; ok && item_at(j, wi); ++j, ++lt) {
+            const int m0 = wi.m0;
+            const int nt0 = wi.ct0;                   // first output column of the item
+            const int NSLAB = wi.width / 64;          // 64-column slabs in it
             const int buf = lt & 1;
             const uint32_t aph = (lt >> 1) & 1;
             const bool tma_path = use_tma_store && m0 + TBM <= M;
@@ -241,7 +283,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 // this tile's bias slice -> shared memory (one value per thread), so the column
                 // loop reads it as a broadcast instead of through the global-load path
                 const int te = threadIdx.x - 64;
-                if (te < BN) {
+                if (te < wi.width) {
                     bias_s[te] = (bias && nt0 + te < N) ? __ldg(bias + nt0 + te) : 0.f;
                     if (EPI & EPI_LN) bias_s[BN + te] = (nt0 + te < N) ? __ldg(ln.s + nt0 + te) : 0.f;
                 }
@@ -285,9 +327,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             if (EPI & EPI_LN) {
                 // warm L1 with the row statistics the next tile of this CTA will start with
-                const int tn = t + gridDim.x;
-                const int mn = (tn / n_tiles) * TBM + row;
-                if (tn < total && mn < M) {
+                Item nxt;
+                const int mn = item_at(j + 1, nxt) ? nxt.m0 + row : M;
+                if (mn < M) {
                     const float2* nxt = ln.stats + (size_t)mn * (ln.mode == 2 ? STAT_SLOTS : 1);
                     asm volatile("prefetch.global.L1 [%0];" ::"l"(nxt));
                 }
@@ -376,20 +418,21 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         bulk_commit_group();
                         if (res) {
                             // prefetch the residual of the next slab into the buffer that just became free
-                            int nsl = sl + 1, nt = t;
-                            if (nsl == NSLAB) { nsl = 0; nt = t + gridDim.x; }
-                            const int nm0 = (nt / n_tiles) * TBM;
-                            if (nt < total && nm0 + TBM <= M) {
+                            Item nxt = wi;
+                            int nsl = sl + 1;
+                            bool more = true;
+                            if (nsl == NSLAB) { nsl = 0; more = item_at(j + 1, nxt); }
+                            if (more && nxt.m0 + TBM <= M) {
                                 const int nb = (slab_no + 1) & 1;
                                 mbar_arrive_expect_tx(&res_full[nb], TBM * 128);
-                                tma_load_2d(smem_out + nb * (TBM * 128), &tmap_r, &res_full[nb],
-                                            (nt % n_tiles) * BN + nsl * 64, nm0);
+                                tma_load_2d(smem_out + nb * (TBM * 128), &tmap_r, &res_full[nb], nxt.ct0 + nsl * 64,
+                                            nxt.m0);
                                 res_issued = slab_no + 1;
                             }
                         }
                     }
                 }
-                if (EPI & EPI_EMIT) ln.emit[(size_t)(m0 + row) * STAT_SLOTS + (t % n_tiles) * 4 + qsub] = make_float2(e1, e2);
+                if (EPI & EPI_EMIT) ln.emit[(size_t)(m0 + row) * STAT_SLOTS + wi.nt * 4 + qsub] = make_float2(e1, e2);
                 continue;
             }
             // ---- boundary tile / row-remapped / fp32 output: store straight from registers
@@ -452,7 +495,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     OutVec<OutT>::store8(y + orow * ldy + n, v);
                 }
             }
-            if ((EPI & EPI_EMIT) && row_ok) ln.emit[(size_t)m * STAT_SLOTS + (t % n_tiles) * 4 + qsub] = make_float2(e1, e2);
+            if ((EPI & EPI_EMIT) && row_ok) ln.emit[(size_t)m * STAT_SLOTS + wi.nt * 4 + qsub] = make_float2(e1, e2);
         }
         if (elected) bulk_wait_group0();      // every TMA store has landed before the CTA retires
     }
@@ -520,6 +563,16 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
         const unsigned box[2] = {TBK, BN};
         if (int rc = make_tmap_bf16(&tw, p.w, 2, dims, strides, box)) return rc;
     }
+    // W boxes for the column strips of split tail tiles: half (third for BN = 192) and quarter height
+    CUtensorMap tw2 = tw, tw3 = tw;
+    {
+        const unsigned long long dims[2] = {(unsigned long long)p.K, (unsigned long long)p.N};
+        const unsigned long long strides[1] = {(unsigned long long)p.K * 2ull};
+        const unsigned box2[2] = {TBK, BN == 256 ? 128u : 64u};
+        if (int rc = make_tmap_bf16(&tw2, p.w, 2, dims, strides, box2)) return rc;
+        const unsigned box3[2] = {TBK, 64u};
+        if (int rc = make_tmap_bf16(&tw3, p.w, 2, dims, strides, box3)) return rc;
+    }
     // Output map for the TMA-store epilogue (bf16 output, rows not remapped).
     const int use_tma_store = (sizeof(OutT) == 2 && p.out_grp == 0) ? 1 : 0;
     CUtensorMap ty = tw, tr = tw;
@@ -552,7 +605,7 @@ static int launch_tc(const LinearArgs& p, cudaStream_t st) {
     VTP_REQUIRE(!p.emit_stats || ceil_div(p.N, BN) * 4 <= STAT_SLOTS, VTP_ERR_SHAPE,
                 "linear (tcgen05): N=%d has too many column tiles for the row-statistics slots", p.N);
     const LnFold ln{p.ln_stats, p.ln_s, p.ln_mode, p.ln_dim, p.ln_eps, p.emit_stats, p.ln_slots};
-    const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), (size_t)S::TOTAL, st, ta, tw, ty, tr, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
+    const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), (size_t)S::TOTAL, st, ta, tw, tw2, tw3, ty, tr, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
                                       p.m_dev, p.N, p.K, p.flags, rm, ln, device_status_ptr());
     if (le != cudaSuccess) {
         cudaGetLastError();
