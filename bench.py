@@ -551,6 +551,23 @@ def main():
     e2e_value = world * B * args.steps / (float(e2e_ms.item()) * 1e-3)
     _ = t0
     clocks = sampler.stop() if sampler else None
+    # the same leg with the host images in the other element type (1 GPU only, to keep multi-GPU runs short):
+    # fp32 is what the reference's data loader hands over, bf16 is what this model rounds the pixels to anyway
+    e2e_other = None
+    if world == 1 and dtype == torch.bfloat16:
+        other_dt = torch.float32 if host_dt == torch.bfloat16 else torch.bfloat16
+        pipe2 = HostPipeline(model, B, 256, device, world=world, image_dtype=other_dt, use_graph=use_graph)
+        host2 = [synthetic.images(B, 256, seed=200 + 7 * i).to(other_dt).pin_memory() for i in range(2)]
+        batches2 = [host2[i & 1] for i in range(args.steps)]
+        pipe2.run(batches2[:3])
+        torch.cuda.synchronize(device)
+        e0.record()
+        pipe2.run(batches2)
+        e1.record()
+        torch.cuda.synchronize(device)
+        e2e_other = {"host_images": str(other_dt).replace("torch.", ""),
+                     "value": B * args.steps / (e0.elapsed_time(e1) * 1e-3), "unit": "images/s",
+                     "h2d_bytes_per_step": pipe2.h2d_bytes}
     status = _lib.device_status()
 
     if rank == 0:
@@ -571,6 +588,8 @@ def main():
             "gpu_launches": args.steps * launches_per_forward(model),
             "clocks": clocks, "device_status": status, "peaks": pk_src,
         }
+        if e2e_other:
+            line["e2e_other_host_dtype"] = e2e_other
         if dtype == torch.bfloat16 and not args.cuda_cores:
             line["roofline"] = kv_launch_roofline(model, B, device, pk)
             line["model_roofline"] = model_roofline(model, B, model.last_counts.cpu(), ms_total / args.steps, pk,
