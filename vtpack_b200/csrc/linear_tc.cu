@@ -13,11 +13,14 @@
 //   warps 2-17           epilogue: read the finished accumulator with tcgen05.ld (warp w may
 //                        touch TMEM lanes 32*(w%4)..+31 = tile rows; four warps share a lane
 //                        quarter and split the columns), apply bias / GELU / residual, then
-//                        write the tile 64 columns at a time into a swizzled staging buffer
-//                        that one thread hands to a TMA store (full 128-byte lines, no partial
-//                        sectors).  The accumulator goes back to the MMA warp as soon as its
+//                        write the tile 64 columns at a time into one of two swizzled staging
+//                        slabs (full 128-byte lines, no partial sectors) and signal it full
+//                        on an mbarrier: the warps never wait for each other inside a tile.  The accumulator goes back to the MMA warp as soon as its
 //                        last columns are in registers.  Tiles that touch the last valid row,
 //                        row-remapped outputs and fp32 outputs store straight from registers.
+//   warp 18  (one lane)  store thread: waits for a full slab, hands it to a TMA store, waits until
+//                        the store has read it, then marks it free again or, when there is a
+//                        residual, has the TMA load the residual of the slab after next into it.
 // The two accumulators let the MMA of tile i+1 overlap the epilogue of tile i.
 // The tiles left for the last, partial round of the grid are cut into two to four column strips
 // (their own W boxes, a narrower MMA), one per CTA, so that round costs a fraction of a tile.
@@ -43,7 +46,7 @@ using namespace sm100;
 constexpr int TBM = 128;   // tile rows = TMEM lanes
 constexpr int TBK = 64;    // 64 bf16 = one 128-byte swizzle row
 constexpr int EPI_THREADS = 512;  // 16 epilogue warps, four per TMEM lane quarter
-constexpr int TC_THREADS = 64 + EPI_THREADS;
+constexpr int TC_THREADS = 64 + EPI_THREADS + 32;   // + the store warp
 
 template <int BN, int STAGES>
 struct TcSmem {
@@ -133,7 +136,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint64_t* acc_full = empty + STAGES;       // [2]
     uint64_t* acc_empty = acc_full + 2;        // [2]
     uint64_t* res_full = acc_empty + 2;        // [2] residual slab landed in the staging buffer
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_full + 2);
+    uint64_t* slab_full = res_full + 2;        // [2] every epilogue warp has written its part of the staging slab
+    uint64_t* slab_free = slab_full + 2;       // [2] the TMA store has read the staging slab
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(slab_free + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -146,6 +151,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             mbar_init(&acc_full[b], 1);
             mbar_init(&acc_empty[b], EPI_THREADS / 32);
             mbar_init(&res_full[b], 1);
+            mbar_init(&slab_full[b], EPI_THREADS / 32);
+            mbar_init(&slab_free[b], 1);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -262,14 +269,47 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
         }
         __syncwarp();
+    } else if (warp == 2 + EPI_THREADS / 32) {
+        if (lane == 0 && use_tma_store) {
+            // -------------------------------------------------------------- store thread
+            // Walks the staged slabs in the epilogue's order: (item j, slab sl) of every item whose 128 rows
+            // are all valid (the items with the last, partial rows come last and store from registers).
+            struct Cursor { int j, sl; Item it; bool ok; };
+            auto first = [&]() { Cursor c; c.j = 0; c.sl = 0; c.ok = item_at(0, c.it) && c.it.m0 + TBM <= M; return c; };
+            auto advance = [&](Cursor& c) {
+                if (++c.sl == c.it.width / 64) { c.sl = 0; ++c.j; c.ok = item_at(c.j, c.it) && c.it.m0 + TBM <= M; }
+            };
+            auto load_residual = [&](const Cursor& c, int b) {
+                mbar_arrive_expect_tx(&res_full[b], TBM * 128);
+                tma_load_2d(smem_out + b * (TBM * 128), &tmap_r, &res_full[b], c.it.ct0 + c.sl * 64, c.it.m0);
+            };
+            Cursor cur = first(), ahead = cur;        // `ahead` runs two slabs in front (residual prefetch)
+            if (res) {
+                for (int b = 0; b < 2 && ahead.ok; ++b) { load_residual(ahead, b); advance(ahead); }
+            }
+            bool ok = true;
+            for (int slab_no = 0; cur.ok && ok; ++slab_no, advance(cur)) {
+                const int b = slab_no & 1;
+                ok = mbar_wait(&slab_full[b], (slab_no >> 1) & 1, abort_flag, status, STATUS_GEMM_EPILOGUE);
+                if (!ok) break;
+                tma_store_2d(&tmap_y, smem_out + b * (TBM * 128), cur.it.ct0 + cur.sl * 64, cur.it.m0);
+                bulk_commit_group();
+                bulk_wait_group_read0();              // the slab has been read: it can be written again
+                if (res) {
+                    if (ahead.ok) { load_residual(ahead, b); advance(ahead); }
+                } else {
+                    mbar_arrive(&slab_free[b]);
+                }
+            }
+            bulk_wait_group0();                       // every TMA store has landed before the CTA retires
+        }
+        __syncwarp();
     } else {
         // ------------------------------------------------------------------- epilogue
         const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
         const int qsub = (warp - 2) >> 2;             // which of the four warps of that quarter
-        const bool elected = threadIdx.x == 64;       // issues the TMA stores / residual loads
         const int row = quarter * 32 + lane;          // tile row = TMEM lane
         int lt = 0, slab_no = 0;
-        int res_issued = -1;                          // elected thread: last slab whose residual load was issued
         bool ok = true;
         Item wi;
         for (int j = 0; ok && item_at(j, wi); ++j, ++lt) {
@@ -282,17 +322,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (tma_path) {
                 // this tile's bias slice -> shared memory (one value per thread), so the column
                 // loop reads it as a broadcast instead of through the global-load path
+                named_barrier(1, EPI_THREADS);                       // nobody reads the previous slice any more
                 const int te = threadIdx.x - 64;
                 if (te < wi.width) {
                     bias_s[te] = (bias && nt0 + te < N) ? __ldg(bias + nt0 + te) : 0.f;
                     if (EPI & EPI_LN) bias_s[BN + te] = (nt0 + te < N) ? __ldg(ln.s + nt0 + te) : 0.f;
-                }
-                if (res && elected && res_issued < slab_no) {
-                    // first slab of a run of TMA tiles: nobody prefetched its residual
-                    bulk_wait_group_read0();
-                    mbar_arrive_expect_tx(&res_full[slab_no & 1], TBM * 128);
-                    tma_load_2d(smem_out + (slab_no & 1) * (TBM * 128), &tmap_r, &res_full[slab_no & 1], nt0, m0);
-                    res_issued = slab_no;
                 }
             }
             ok = mbar_wait(&acc_full[buf], aph, abort_flag, status, STATUS_GEMM_EPILOGUE);
@@ -377,10 +411,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     uint8_t* srow = smem_out + (slab_no & 1) * (TBM * 128) + row * 128;
                     if (res) {
+                        // the residual of this slab is in the staging slab (so the slab is free, too)
                         ok = mbar_wait(&res_full[slab_no & 1], (slab_no >> 1) & 1, abort_flag, status,
                                        STATUS_GEMM_EPILOGUE);
-                        if (!ok) break;
+                    } else if (slab_no >= 2) {
+                        // the store of the slab that used this staging slab last has read it
+                        ok = mbar_wait(&slab_free[slab_no & 1], ((slab_no >> 1) - 1) & 1, abort_flag, status,
+                                       STATUS_GEMM_EPILOGUE);
                     }
+                    if (!ok) break;
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         float* vj = v + 8 * j;
@@ -411,26 +450,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         *cell = ov.raw;
                     }
                     fence_proxy_async_smem();
-                    if (elected) bulk_wait_group_read0();      // the other slab buffer is free again
-                    named_barrier(1, EPI_THREADS);
-                    if (elected) {
-                        tma_store_2d(&tmap_y, smem_out + (slab_no & 1) * (TBM * 128), nt0 + sl * 64, m0);
-                        bulk_commit_group();
-                        if (res) {
-                            // prefetch the residual of the next slab into the buffer that just became free
-                            Item nxt = wi;
-                            int nsl = sl + 1;
-                            bool more = true;
-                            if (nsl == NSLAB) { nsl = 0; more = item_at(j + 1, nxt); }
-                            if (more && nxt.m0 + TBM <= M) {
-                                const int nb = (slab_no + 1) & 1;
-                                mbar_arrive_expect_tx(&res_full[nb], TBM * 128);
-                                tma_load_2d(smem_out + nb * (TBM * 128), &tmap_r, &res_full[nb], nxt.ct0 + nsl * 64,
-                                            nxt.m0);
-                                res_issued = slab_no + 1;
-                            }
-                        }
-                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&slab_full[slab_no & 1]);       // this warp's part of the slab is in place
                 }
                 if (EPI & EPI_EMIT) ln.emit[(size_t)(m0 + row) * STAT_SLOTS + wi.nt * 4 + qsub] = make_float2(e1, e2);
                 continue;
@@ -497,7 +518,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             if ((EPI & EPI_EMIT) && row_ok) ln.emit[(size_t)m * STAT_SLOTS + wi.nt * 4 + qsub] = make_float2(e1, e2);
         }
-        if (elected) bulk_wait_group0();      // every TMA store has landed before the CTA retires
     }
     if (*abort_flag) {
         // Unwinding after a wait gave up: give copies still in flight time to land before
