@@ -140,6 +140,43 @@ int vtp_unpool_add(const void* q, const void* comp, int dtype, int B, int N, int
                    int n_patches_max, const void* ref, void* out, void* stream);
 
 /*
+ * Gradients of the two movers (training path).  Each is the other mover with another scale:
+ *   vtp_pool_grad:   grad_x[b,tok,:] = grad_comp[p,:] / step(p)^2 for every token of patch p
+ *                    (backward of grained_sample_compress, vtpack/layers/grained_sample.py:26-38);
+ *   vtp_unpool_grad: grad_q[p,:] = sum over the tokens of patch p of grad_out[b,tok,:]
+ *                    (backward of grained_sample_decompress with respect to its packed input,
+ *                    grained_sample.py:61-72; the gradient with respect to ref_input is grad_out
+ *                    itself, :74-77).
+ * Shapes as in vtp_pool / vtp_unpool_add.  C may be any positive count for all four movers: rows of
+ * whole 16-byte chunks take the vector kernels (16-byte aligned pointers required), other widths
+ * (the one-channel gate tensor of vtpack/layers/dge.py:104-110) an element-wise kernel.
+ */
+int vtp_pool_grad(const void* grad_comp, int dtype, int B, int N, int C, int W, int num_extra,
+                  const int32_t* patches, const int32_t* n_patches_dev, int n_patches_max,
+                  void* grad_x, void* stream);
+int vtp_unpool_grad(const void* grad_out, int dtype, int B, int N, int C, int W, int num_extra,
+                    const int32_t* patches, const int32_t* n_patches_dev, int n_patches_max,
+                    void* grad_q, void* stream);
+
+/*
+ * Ragged batched matrix product of the training path.  For image i and head h
+ *   out_i = op(a_i) * op(b_i),  a_i = a[h, a_offsets[i] : a_offsets[i+1], :],  b_i likewise,
+ * op = transpose when the matching flag is non-zero; the out_i are stacked along the row axis: image i
+ * starts at row a_offsets[i] (a not transposed) or i*a_cols (a transposed).
+ *   a [heads, a_rows, a_cols], b [heads, b_rows, b_cols], out [heads, out_rows, out_cols], dense;
+ *   a_offsets / b_offsets device int32 [n_images+1]; max_a_len / max_b_len bound the per-image row
+ *   counts (they size the launch); when b is transposed every image must have out_cols rows of b.
+ * Replaces batched_sparse_gemm_forward (vtpack/layers/csrc/batched_sparse_gemm/
+ * batched_sparse_gemm.cu:150-196), the one native call behind batched_sparse_gemm and its backward
+ * (vtpack/layers/sparse_ops.py:11-57).
+ */
+int vtp_batched_sparse_gemm(const void* a, const void* b, void* out, int dtype, int heads, int n_images,
+                            long long a_rows, int a_cols, long long b_rows, int b_cols,
+                            const int32_t* a_offsets, const int32_t* b_offsets, int max_a_len,
+                            int max_b_len, int a_transposed, int b_transposed, long long out_rows,
+                            int out_cols, void* stream);
+
+/*
  * LayerNorm over the last axis.  Row r of the input starts at x + r*in_row_stride
  * elements; output rows are dense.  rows_dev (device int32) overrides rows_max when set.
  * Replaces nn.LayerNorm norm2 / norm (vtpack/models/dge/deit_dge.py:128, :277).

@@ -163,6 +163,55 @@ def batched_sparse_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.
     return out
 
 
+def batched_sparse_gemm_forward(a: torch.Tensor, b: torch.Tensor, a_lengths: torch.Tensor,
+                                b_lengths: torch.Tensor, is_a_transposed: bool,
+                                is_b_transposed: bool) -> torch.Tensor:
+    """Ragged batched product of the training path, ``a[h,La,ka]``, ``b[h,Lb,kb]``.
+
+    Follows ``vtpack/layers/csrc/batched_sparse_gemm/batched_sparse_gemm.cu:150-196``: image i owns
+    the next ``a_lengths[i]`` rows of ``a`` and ``b_lengths[i]`` rows of ``b``; each slice is
+    transposed when its flag is set, the per-image ``bmm`` results are concatenated along dim 1.
+    """
+    outs = []
+    sa = sb = 0
+    for la, lb in zip(a_lengths.tolist(), b_lengths.tolist()):
+        ai, bi = a[:, sa:sa + la], b[:, sb:sb + lb]
+        if is_a_transposed:
+            ai = ai.transpose(-1, -2)
+        if is_b_transposed:
+            bi = bi.transpose(-1, -2)
+        outs.append(torch.matmul(ai, bi))
+        sa += la
+        sb += lb
+    return torch.cat(outs, dim=1)
+
+
+def gumbel_softmax_fixed(noises):
+    """Stand-in for ``torch.nn.functional.gumbel_softmax`` that draws its Gumbel noise from the given
+    list (one tensor per call, in call order) instead of the random generator, so that a CPU run and
+    a CUDA run of a training-mode forward sample the same gates.  Hard straight-through form: the
+    forward value is the one-hot arg-max of softmax((logits + noise) / tau), the gradient that of the
+    softmax."""
+    it = iter(noises)
+
+    def gumbel_softmax(logits, tau=1, hard=False, eps=1e-10, dim=-1):
+        g = next(it).to(device=logits.device, dtype=logits.dtype)
+        y_soft = ((logits + g) / tau).softmax(dim)
+        if not hard:
+            return y_soft
+        index = y_soft.max(dim, keepdim=True)[1]
+        y_hard = torch.zeros_like(logits).scatter_(dim, index, 1.0)
+        return y_hard - y_soft.detach() + y_soft
+
+    return gumbel_softmax
+
+
+def make_gumbel_noise(shape, seed: int) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    u = torch.rand(*shape, generator=g).clamp_(1e-6, 1.0 - 1e-6)
+    return -torch.log(-torch.log(u))
+
+
 # --------------------------------------------------------------------------
 # Module-level restatements (weights passed as plain dicts of tensors)
 # --------------------------------------------------------------------------
@@ -506,3 +555,33 @@ def round_bf16(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
     bf16 device path is compared with fp32 math on these."""
     return {k: (v.to(torch.bfloat16).to(torch.float32) if v.is_floating_point() else v)
             for k, v in sd.items()}
+
+
+# --------------------------------------------------------------------------
+# Seeded inputs of the training-path fixtures (shared by the fixture generator and the tests)
+# --------------------------------------------------------------------------
+
+def randn_seeded(shape, seed: int) -> torch.Tensor:
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed))
+
+
+def train_ops_inputs(C: int):
+    """Tokens [2,257,C] (seed 1) and grain indices [2,4,4] (arg-max of the seed-2 gate logits)."""
+    x = randn_seeded((2, 257, C), 1)
+    gate = make_gate_logits(2, 4, 4, 3, seed=2)
+    return x, gate.argmax(dim=-1)
+
+
+TRAIN_BLOCK = dict(dim=64, heads=2, batch=2, noise_seed=21, grad_seed=22, weight_seed=5, token_seed=6)
+
+
+def train_block_weights() -> Dict[str, torch.Tensor]:
+    """Weights of the training-mode block fixture: trunc-normal matrices plus small random biases and
+    LayerNorm offsets, so that every gradient path carries signal."""
+    cfg = TRAIN_BLOCK
+    sd = block_weights(make_state_dict(cfg["dim"], 1, cfg["heads"], seed=cfg["weight_seed"]), 0)
+    g = torch.Generator().manual_seed(cfg["weight_seed"] + 100)
+    for k, v in sd.items():
+        if k.endswith("bias") and v.is_floating_point():
+            sd[k] = v + 0.02 * torch.randn(v.shape, generator=g)
+    return sd

@@ -7,8 +7,8 @@ The reference's native extension ``vtpack._C`` is CUDA-only and ``timm`` is
 not installed, so two stand-ins are placed in ``sys.modules`` before the
 reference is imported from its checkout:
 
-  * ``vtpack._C``: the four functions the eval path calls
-    (``vtpack/layers/csrc/vision.cpp:9-29``), backed by ``oracle/dge_oracle.py``;
+  * ``vtpack._C``: the four functions the eval path calls and the ragged product of the
+    training path (``vtpack/layers/csrc/vision.cpp:9-29``), backed by ``oracle/dge_oracle.py``;
   * ``timm.models.{layers,registry,vision_transformer}``: the handful of names
     ``vtpack/models/dge/deit_dge.py:9-11`` imports.  ``PatchEmbed`` is the
     conv(kernel = stride = patch) + flatten + transpose the reference's own
@@ -16,7 +16,9 @@ reference is imported from its checkout:
     because callers load a seeded state_dict afterwards.
 
 The reference's ``dge.py``, ``grained_sample.py``, ``sparse_ops.py``,
-``deit_dge.py`` and ``standard/deit.py`` then run unmodified.
+``deit_dge.py`` and ``standard/deit.py`` then run unmodified, in eval mode and (with
+stochastic depth off) in training mode, backward passes included: the reference's autograd
+functions call the same stand-ins.
 """
 import importlib
 import os
@@ -53,7 +55,7 @@ class _DropPath(nn.Module):
         self.p = p
 
     def forward(self, x):
-        assert not self.training, "stand-in supports eval only"
+        assert not self.training or self.p == 0.0, "stand-in has no stochastic depth"
         return x
 
 
@@ -97,8 +99,8 @@ def install():
     c.grained_sample_compress = dge_oracle.grained_sample_compress
     c.grained_sample_decompress = dge_oracle.grained_sample_decompress
     c.batched_sparse_attention_forward = dge_oracle.batched_sparse_attention_forward
-    for name in ("batched_sparse_gemm_forward", "batched_sparse_gemm_v2_forward",
-                 "grained_sample_index_to_patch_dense"):
+    c.batched_sparse_gemm_forward = dge_oracle.batched_sparse_gemm_forward
+    for name in ("batched_sparse_gemm_v2_forward", "grained_sample_index_to_patch_dense"):
         setattr(c, name, _not_on_eval_path)
     sys.modules["vtpack._C"] = c
     vtpack._C = c

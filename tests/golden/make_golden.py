@@ -18,6 +18,14 @@ Fixtures
   pvt_model_fp32.npz    full PVT+DGE tiny (pvt_dge_s124_tiny_256: 4 stages, 8 blocks), fp32, B=2,
                         weights seed 0, images seed 8, free-running router: logits and the
                         per-block per-image query counts.
+  train_ops_fp32.npz    gradients of the training path's native ops from the reference's own autograd
+                        functions: grained_sample_compress / _decompress (B=2, 16x16 grid + cls,
+                        C=32 and the one-channel case) and batched_sparse_gemm in the two flag
+                        combinations the model uses (forward values and both gradients).
+  train_block_fp32.npz  one DeiT+DGE block (dim 64, 2 heads) in training mode, fp32, B=2, with
+                        sparse_train on and off; Gumbel noise seed 21 injected through
+                        oracle.dge_oracle.gumbel_softmax_fixed; output, input gradient and
+                        parameter gradients for the loss sum(out * g), g seed 22.
 Inputs are regenerated from the seeds by the tests; each fixture carries a
 float64 sum of its inputs so RNG drift is detected rather than misread as a
 parity failure.
@@ -153,8 +161,87 @@ def pvt_model_fixture():
     print("pvt model:", logits.shape, np.stack(cnt).tolist(), "min margin", min(margin))
 
 
+def train_ops_fixture():
+    _, gs, _, _ = ref_shim.reference_modules()
+    import importlib
+    sparse_ops = importlib.import_module("vtpack.layers.sparse_ops")
+    out = {}
+    splits = torch.tensor([4, 2, 1])
+    for C in (32, 1):
+        x, indices = O.train_ops_inputs(C)
+        x.requires_grad_(True)
+        patches, lengths = gs.grained_sample_index_to_patch(indices, splits, 4, 1)
+        L = patches.shape[0]
+        comp = gs.grained_sample_compress(x, patches, 16, 16, 1)
+        g1 = O.randn_seeded((L, C), 11)
+        grad_x, = torch.autograd.grad(comp, x, g1.clone())
+        q = O.randn_seeded((L, C), 12).requires_grad_(True)
+        ref = x.detach().clone().requires_grad_(True)
+        tok = gs.grained_sample_decompress(q, patches, ref, 16, 16, 1, True)
+        g2 = O.randn_seeded((2, 257, C), 13)
+        grad_q, grad_ref = torch.autograd.grad(tok, (q, ref), g2.clone())
+        assert torch.equal(grad_ref, g2)
+        out.update({f"c{C}_comp": comp.detach().numpy(), f"c{C}_grad_x": grad_x.numpy(),
+                    f"c{C}_grad_q": grad_q.numpy(), f"c{C}_lengths": lengths.numpy()})
+    # ragged products: queries [h, L, d] x keys [h, B*N, d]^T, then probabilities x values
+    h, d, N = 2, 8, 12
+    la = torch.tensor([5, 17, 9])
+    lb = torch.full([3], N, dtype=torch.long)
+    L = int(la.sum())
+    qh = O.randn_seeded((h, L, d), 31).requires_grad_(True)
+    kh = O.randn_seeded((h, 3 * N, d), 32).requires_grad_(True)
+    vh = O.randn_seeded((h, 3 * N, d), 33).requires_grad_(True)
+    s = sparse_ops.batched_sparse_gemm(qh, kh, la, lb, False, True)
+    gs_ = O.randn_seeded((h, L, N), 34)
+    gq, gk = torch.autograd.grad(s, (qh, kh), gs_.clone())
+    p = O.randn_seeded((h, L, N), 35).requires_grad_(True)
+    o = sparse_ops.batched_sparse_gemm(p, vh, la, lb, False, False)
+    go = O.randn_seeded((h, L, d), 36)
+    gp, gv = torch.autograd.grad(o, (p, vh), go.clone())
+    out.update(gemm_s=s.detach().numpy(), gemm_gq=gq.numpy(), gemm_gk=gk.numpy(),
+               gemm_o=o.detach().numpy(), gemm_gp=gp.numpy(), gemm_gv=gv.numpy())
+    np.savez_compressed(os.path.join(HERE, "train_ops_fp32.npz"), **out)
+    print("train_ops_fp32.npz", {k: v.shape for k, v in out.items()})
+
+
+def train_block_fixture():
+    _, _, deit_dge, _ = ref_shim.reference_modules()
+    import torch.nn.functional as F
+    cfg = O.TRAIN_BLOCK
+    sd = O.train_block_weights()
+    out = {}
+    real = F.gumbel_softmax
+    for mode in ("sparse", "dense"):
+        blk = deit_dge.Block(cfg["dim"], cfg["heads"], mlp_ratio=4, qkv_bias=True,
+                             norm_layer=lambda d: torch.nn.LayerNorm(d, eps=1e-6), split_sizes=[4, 2, 1])
+        blk.load_state_dict(sd, strict=True)
+        blk.train()
+        blk.dge.sparse_train = mode == "sparse"
+        x = O.randn_seeded((cfg["batch"], 257, cfg["dim"]), cfg["token_seed"]).requires_grad_(True)
+        g = O.randn_seeded((cfg["batch"], 257, cfg["dim"]), cfg["grad_seed"])
+        F.gumbel_softmax = O.gumbel_softmax_fixed([O.make_gumbel_noise((cfg["batch"], 4, 4, 3), cfg["noise_seed"])])
+        try:
+            y = blk(x)
+            comp = blk.dge.get_complexity()
+            loss = (y * g).sum() + 1e-9 * comp["dynamic"].sum()
+            loss.backward()
+        finally:
+            F.gumbel_softmax = real
+        out[f"{mode}_out"] = y.detach().numpy()
+        out[f"{mode}_grad_x"] = x.grad.numpy()
+        out[f"{mode}_lengths"] = np.asarray(blk.dge.states["batches"])
+        out[f"{mode}_comp_dynamic"] = comp["dynamic"].detach().numpy()
+        for name, prm in blk.named_parameters():
+            if prm.grad is not None:
+                out[f"{mode}_grad.{name}"] = prm.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "train_block_fp32.npz"), **out)
+    print("train_block_fp32.npz", sorted(out)[:6], "...", len(out), "arrays")
+
+
 if __name__ == "__main__":
     layer_fixture()
     model_fixture()
     pvt_block_fixture()
     pvt_model_fixture()
+    train_ops_fixture()
+    train_block_fixture()

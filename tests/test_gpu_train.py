@@ -1,0 +1,205 @@
+"""GPU parity of the training path: gradients of the token movers, the ragged products, and a
+training-mode DeiT+DGE block, against what the reference's own autograd functions returned on the
+same seeded inputs (committed fixtures; tests/golden/make_golden.py)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from tests.gpu_util import O, rel_err
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL = 1e-4          # fp32, relative to the largest reference value
+
+
+@pytest.fixture(scope="module")
+def layers():
+    from vtpack_b200 import _lib, layers
+    _lib.lib()
+    return layers
+
+
+def _golden(golden_dir, name):
+    return {k: torch.from_numpy(v) for k, v in np.load(os.path.join(golden_dir, name)).items()}
+
+
+@pytest.mark.parametrize("C", [32, 1])
+def test_mover_gradients_match_reference(layers, golden_dir, C):
+    z = _golden(golden_dir, "train_ops_fp32.npz")
+    splits = torch.tensor([4, 2, 1])
+    x, indices = O.train_ops_inputs(C)
+    x = x.to(DEV).requires_grad_(True)
+    patches, lengths = layers.grained_sample_index_to_patch(indices.to(DEV), splits, 4, 1)
+    assert torch.equal(lengths, z[f"c{C}_lengths"])
+    L = patches.shape[0]
+    comp = layers.grained_sample_compress(x, patches, 16, 16, 1)
+    assert torch.equal(comp.detach().cpu(), z[f"c{C}_comp"])
+    grad_x, = torch.autograd.grad(comp, x, O.randn_seeded((L, C), 11).to(DEV))
+    assert torch.equal(grad_x.cpu(), z[f"c{C}_grad_x"])            # a power-of-two scale: exact
+    q = O.randn_seeded((L, C), 12).to(DEV).requires_grad_(True)
+    ref = x.detach().clone().requires_grad_(True)
+    tok = layers.grained_sample_decompress(q, patches, ref, 16, 16, 1, True)
+    g2 = O.randn_seeded((2, 257, C), 13).to(DEV)
+    grad_q, grad_ref = torch.autograd.grad(tok, (q, ref), g2)
+    assert torch.equal(grad_ref, g2)
+    assert rel_err(grad_q, z[f"c{C}_grad_q"]) < 1e-6
+    # without the reference term the reference tensor receives a zero gradient (grained_sample.py:76-77)
+    tok2 = layers.grained_sample_decompress(q, patches, ref, 16, 16, 1, False)
+    _, grad_ref2 = torch.autograd.grad(tok2, (q, ref), g2)
+    assert not grad_ref2.any()
+
+
+@pytest.mark.parametrize("B,G,C", [(3, 16, 384), (2, 32, 64)])
+def test_mover_gradients_bf16_and_adjoint(layers, B, G, C):
+    """Size-independent property: <pool(x), g> == <x, pool_grad(g)> and the same for the unpool (the
+    gradient kernels are the adjoints of the forward kernels); bf16 gradients round the fp32 ones."""
+    splits = torch.tensor([4, 2, 1])
+    gen = torch.Generator().manual_seed(B * G + C)
+    indices = torch.randint(0, 3, (B, G // 4, G // 4), generator=gen).to(DEV)
+    patches, _ = layers.grained_sample_index_to_patch(indices, splits, 4, 1)
+    L, N = patches.shape[0], G * G + 1
+    x = torch.randn(B, N, C, generator=gen).to(DEV).requires_grad_(True)
+    g = torch.randn(L, C, generator=gen).to(DEV)
+    comp = layers.grained_sample_compress(x, patches, G, G, 1)
+    gx, = torch.autograd.grad(comp, x, g)
+    lhs, rhs = (comp.detach().double() * g.double()).sum(), (x.detach().double() * gx.double()).sum()
+    assert abs(float(lhs - rhs)) < 1e-6 * max(1.0, abs(float(lhs)))
+    q = torch.randn(L, C, generator=gen).to(DEV).requires_grad_(True)
+    gt = torch.randn(B, N, C, generator=gen).to(DEV)
+    tok = layers.grained_sample_decompress(q, patches, x.detach(), G, G, 1, False)
+    gq, = torch.autograd.grad(tok, q, gt)
+    lhs, rhs = (tok.detach().double() * gt.double()).sum(), (q.detach().double() * gq.double()).sum()
+    assert abs(float(lhs - rhs)) < 1e-6 * max(1.0, abs(float(lhs)))
+    # bf16
+    xb = x.detach().bfloat16().requires_grad_(True)
+    gxb, = torch.autograd.grad(layers.grained_sample_compress(xb, patches, G, G, 1), xb, g.bfloat16())
+    gx_ref, = torch.autograd.grad(layers.grained_sample_compress(x, patches, G, G, 1), x, g.bfloat16().float())
+    assert torch.equal(gxb.float(), gx_ref)                             # exact: scale by 1, 1/4 or 1/16
+    qb = q.detach().bfloat16().requires_grad_(True)
+    tokb = layers.grained_sample_decompress(qb, patches, xb.detach(), G, G, 1, False)
+    gqb, = torch.autograd.grad(tokb, qb, gt.bfloat16())
+    tokf = layers.grained_sample_decompress(q, patches, x.detach(), G, G, 1, False)
+    gqf, = torch.autograd.grad(tokf, q, gt.bfloat16().float())
+    assert torch.equal(gqb, gqf.bfloat16())                             # fp32 sum, one rounding
+
+
+def test_ragged_products_match_reference(layers, golden_dir):
+    z = _golden(golden_dir, "train_ops_fp32.npz")
+    h, d, N = 2, 8, 12
+    la, lb = torch.tensor([5, 17, 9]), torch.full([3], N, dtype=torch.long)
+    L = int(la.sum())
+    q = O.randn_seeded((h, L, d), 31).to(DEV).requires_grad_(True)
+    k = O.randn_seeded((h, 3 * N, d), 32).to(DEV).requires_grad_(True)
+    v = O.randn_seeded((h, 3 * N, d), 33).to(DEV).requires_grad_(True)
+    p = O.randn_seeded((h, L, N), 35).to(DEV).requires_grad_(True)
+    s = layers.batched_sparse_gemm(q, k, la, lb, False, True)
+    o = layers.batched_sparse_gemm(p, v, la, lb, False, False)
+    gq, gk = torch.autograd.grad(s, (q, k), O.randn_seeded((h, L, N), 34).to(DEV))
+    gp, gv = torch.autograd.grad(o, (p, v), O.randn_seeded((h, L, d), 36).to(DEV))
+    for name, t in (("gemm_s", s), ("gemm_o", o), ("gemm_gq", gq), ("gemm_gk", gk), ("gemm_gp", gp), ("gemm_gv", gv)):
+        assert t.shape == z[name].shape, name
+        assert rel_err(t.detach(), z[name]) < 1e-5, name
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+def test_ragged_products_all_flag_combinations(layers, dtype, ta, tb):
+    """Every transpose combination, ragged lengths (an empty image included) and sizes that are not
+    multiples of the tile, against the CPU restatement in float64."""
+    h, B, ka = 3, 4, 70
+    la = torch.tensor([67, 0, 129, 5])
+    gen = torch.Generator().manual_seed(17 + 2 * ta + tb)
+    a = torch.randn(h, int(la.sum()), ka, generator=gen).to(dtype)
+    if ta:          # op(a_i) is [ka, la]: b_i needs la rows (or la columns when transposed)
+        lb = la if not tb else torch.full([B], 33, dtype=torch.long)
+        kb = 41 if not tb else None
+    else:           # op(a_i) is [la, ka]: b_i needs ka rows (or ka columns when transposed)
+        lb = torch.full([B], ka, dtype=torch.long) if not tb else torch.full([B], 33, dtype=torch.long)
+        kb = 41 if not tb else ka
+    if ta and tb:
+        pytest.skip("op(b_i) would need la columns in every image: not expressible with one column count")
+    b = torch.randn(h, int(lb.sum()), kb, generator=gen).to(dtype)
+    ref = O.batched_sparse_gemm_forward(a.double(), b.double(), la, lb, ta, tb)
+    out = layers.batched_sparse_gemm(a.to(DEV), b.to(DEV), la, lb, ta, tb)
+    assert out.shape == ref.shape and out.dtype == dtype
+    assert rel_err(out.float(), ref) < (1e-5 if dtype == torch.float32 else 8e-3)
+
+
+def _train_block(mode):
+    from vtpack_b200.models.dge import deit_dge
+    cfg = O.TRAIN_BLOCK
+    blk = deit_dge.Block(cfg["dim"], cfg["heads"], mlp_ratio=4, qkv_bias=True,
+                         norm_layer=lambda d: torch.nn.LayerNorm(d, eps=1e-6), split_sizes=[4, 2, 1])
+    blk.load_state_dict(O.train_block_weights(), strict=True)
+    blk.to(DEV).train()
+    blk.dge.sparse_train = mode == "sparse"
+    return blk, cfg
+
+
+@pytest.mark.parametrize("mode", ["sparse", "dense"])
+def test_training_block_matches_reference(golden_dir, mode):
+    """Forward value, input gradient, every parameter gradient and the complexity term of one
+    training-mode block, with the reference's Gumbel noise injected."""
+    z = _golden(golden_dir, "train_block_fp32.npz")
+    blk, cfg = _train_block(mode)
+    x = O.randn_seeded((cfg["batch"], 257, cfg["dim"]), cfg["token_seed"]).to(DEV).requires_grad_(True)
+    g = O.randn_seeded((cfg["batch"], 257, cfg["dim"]), cfg["grad_seed"]).to(DEV)
+    real = F.gumbel_softmax
+    F.gumbel_softmax = O.gumbel_softmax_fixed([O.make_gumbel_noise((cfg["batch"], 4, 4, 3), cfg["noise_seed"])])
+    try:
+        y = blk(x)
+        comp = blk.dge.get_complexity()
+        ((y * g).sum() + 1e-9 * comp["dynamic"].sum()).backward()
+    finally:
+        F.gumbel_softmax = real
+    assert torch.equal(torch.as_tensor(blk.dge.states["batches"]).cpu(), z[f"{mode}_lengths"])
+    assert rel_err(comp["dynamic"].detach(), z[f"{mode}_comp_dynamic"]) < 1e-12
+    assert rel_err(y.detach(), z[f"{mode}_out"]) < TOL
+    assert rel_err(x.grad, z[f"{mode}_grad_x"]) < TOL
+    checked = 0
+    for name, prm in blk.named_parameters():
+        key = f"{mode}_grad.{name}"
+        if key in z:
+            assert prm.grad is not None, name
+            assert rel_err(prm.grad, z[key]) < 5 * TOL, name
+            checked += 1
+    assert checked >= 17
+
+
+def test_training_model_step_and_eval_after():
+    """A DeiT-Ti+DGE model takes an SGD step in training mode (sparse_train on): gradients reach the
+    router and the patch embedding, and the fused eval forward afterwards runs on the updated
+    weights (its packed copies are rebuilt)."""
+    from vtpack_b200.models.dge import deit_dge
+    torch.manual_seed(0)
+    m = deit_dge.deit_dge_s124_tiny_patch16_256().to(DEV)
+    for blk in m.blocks:
+        blk.dge.sparse_train = True
+    images = O.make_images(4, 256, seed=3).to(DEV)
+    m.eval()
+    with torch.no_grad():
+        logits_before = m(images).clone()
+    m.train()
+    target = torch.tensor([1, 2, 3, 4], device=DEV)
+    opt = torch.optim.SGD(m.parameters(), lr=1e-2)
+    before = m.blocks[0].dge.router.gate.weight.detach().clone()
+    logits = m(images)
+    assert logits.shape == (4, 1000) and logits.requires_grad
+    budget = torch.stack([blk.dge.get_complexity()["dynamic"].mean() for blk in m.blocks]).sum()
+    loss = F.cross_entropy(logits, target) + 1e-10 * budget
+    loss.backward()
+    assert torch.isfinite(loss)
+    params = dict(m.named_parameters())
+    for name in ("patch_embed.proj.weight", "blocks.0.dge.router.gate.weight", "blocks.11.attn.kv.weight"):
+        grad = params[name].grad
+        assert grad is not None and torch.isfinite(grad).all() and grad.abs().max() > 0, name
+    opt.step()
+    assert not torch.equal(before, m.blocks[0].dge.router.gate.weight.detach())
+    m.eval()
+    with torch.no_grad():
+        logits_after = m(images)
+    assert torch.isfinite(logits_after).all() and not torch.equal(logits_after, logits_before)

@@ -223,3 +223,83 @@ def test_pvt_model_golden(golden_dir):
     logits = O.pvt_dge_forward(x, sd, cfg, trace=tr)
     assert [t["batches"].tolist() for t in tr] == g["batch_lengths"].tolist()
     assert torch.equal(logits, torch.from_numpy(g["logits"]))
+
+
+# ------------------------------------------------------------------ training path
+
+def test_train_ops_golden_known_answers(golden_dir):
+    """The gradients the reference's autograd functions returned (fixture) against closed forms: a
+    token receives 1/size^2 of its patch's gradient row; a packed row receives the sum over its
+    tokens; the ragged products against per-image torch autograd."""
+    z = _load(golden_dir, "train_ops_fp32.npz")
+    splits = torch.tensor([4, 2, 1])
+    for C in (32, 1):
+        x, indices = O.train_ops_inputs(C)
+        patches, lengths = O.grained_sample_index_to_patch(indices, splits, 4, 1)
+        assert np.array_equal(lengths.numpy(), z[f"c{C}_lengths"])
+        L = patches.shape[0]
+        assert torch.equal(O.grained_sample_compress(x, patches, 16, 16, 1), torch.from_numpy(z[f"c{C}_comp"]))
+        g1, g2 = O.randn_seeded((L, C), 11), O.randn_seeded((2, 257, C), 13)
+        grad_x = torch.zeros(2, 257, C)
+        grad_q = torch.zeros(L, C)
+        for p, (b, y, xx, step) in enumerate(patches.tolist()):
+            toks = [-y - 1] if y < 0 else [1 + (y + dy) * 16 + xx + dx for dy in range(step) for dx in range(step)]
+            for t in toks:
+                grad_x[b, t] = g1[p] / (step * step)
+                grad_q[p] += g2[b, t]
+        assert torch.allclose(grad_x, torch.from_numpy(z[f"c{C}_grad_x"]), rtol=0, atol=1e-7)
+        assert torch.allclose(grad_q, torch.from_numpy(z[f"c{C}_grad_q"]), rtol=1e-6, atol=1e-6)
+
+    h, d, N = 2, 8, 12
+    la, lb = torch.tensor([5, 17, 9]), torch.full([3], N, dtype=torch.long)
+    L = int(la.sum())
+    q = O.randn_seeded((h, L, d), 31).requires_grad_(True)
+    k = O.randn_seeded((h, 3 * N, d), 32).requires_grad_(True)
+    v = O.randn_seeded((h, 3 * N, d), 33).requires_grad_(True)
+    p = O.randn_seeded((h, L, N), 35).requires_grad_(True)
+    s = O.batched_sparse_gemm_forward(q, k, la, lb, False, True)       # plain torch ops: autograd applies
+    o = O.batched_sparse_gemm_forward(p, v, la, lb, False, False)
+    gq, gk = torch.autograd.grad(s, (q, k), O.randn_seeded((h, L, N), 34))
+    gp, gv = torch.autograd.grad(o, (p, v), O.randn_seeded((h, L, d), 36))
+    for name, t in (("gemm_s", s), ("gemm_o", o), ("gemm_gq", gq), ("gemm_gk", gk), ("gemm_gp", gp), ("gemm_gv", gv)):
+        assert torch.allclose(t.detach(), torch.from_numpy(z[name]), rtol=1e-5, atol=1e-6), name
+
+
+def test_gumbel_stand_in_matches_torch_form():
+    """The fixed-noise stand-in is F.gumbel_softmax with the noise made explicit: same forward value
+    (one-hot) and same gradient as torch's straight-through form for that noise."""
+    logits = O.randn_seeded((2, 4, 4, 3), 7).requires_grad_(True)
+    noise = O.make_gumbel_noise((2, 4, 4, 3), 8)
+    y = O.gumbel_softmax_fixed([noise])(logits, dim=-1, hard=True)
+    assert torch.equal(y.detach().sum(-1), torch.ones(2, 4, 4)) and set(y.detach().unique().tolist()) <= {0.0, 1.0}
+    assert torch.equal(y.detach().argmax(-1), (logits.detach() + noise).argmax(-1))
+    w = O.randn_seeded((2, 4, 4, 3), 9)
+    g, = torch.autograd.grad((y * w).sum(), logits)
+    logits2 = logits.detach().clone().requires_grad_(True)
+    g2, = torch.autograd.grad((((logits2 + noise).softmax(-1)) * w).sum(), logits2)
+    assert torch.allclose(g, g2, atol=1e-7)
+
+
+@needs_ref
+def test_train_block_fixture_matches_reference(golden_dir):
+    """The committed training-mode block fixture is what the reference's modules return here."""
+    import torch.nn.functional as F
+    _, _, deit_dge, _ = ref_shim.reference_modules()
+    z = _load(golden_dir, "train_block_fp32.npz")
+    cfg = O.TRAIN_BLOCK
+    blk = deit_dge.Block(cfg["dim"], cfg["heads"], mlp_ratio=4, qkv_bias=True,
+                         norm_layer=lambda d: torch.nn.LayerNorm(d, eps=1e-6), split_sizes=[4, 2, 1])
+    blk.load_state_dict(O.train_block_weights(), strict=True)
+    blk.train()
+    blk.dge.sparse_train = True
+    x = O.randn_seeded((cfg["batch"], 257, cfg["dim"]), cfg["token_seed"]).requires_grad_(True)
+    real = F.gumbel_softmax
+    F.gumbel_softmax = O.gumbel_softmax_fixed([O.make_gumbel_noise((cfg["batch"], 4, 4, 3), cfg["noise_seed"])])
+    try:
+        y = blk(x)
+        (y * O.randn_seeded((cfg["batch"], 257, cfg["dim"]), cfg["grad_seed"])).sum().backward()
+    finally:
+        F.gumbel_softmax = real
+    assert np.array_equal(np.asarray(blk.dge.states["batches"]), z["sparse_lengths"])
+    assert torch.allclose(y.detach(), torch.from_numpy(z["sparse_out"]), rtol=1e-5, atol=1e-6)
+    assert torch.allclose(x.grad, torch.from_numpy(z["sparse_grad_x"]), rtol=1e-4, atol=1e-6)

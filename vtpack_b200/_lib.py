@@ -53,6 +53,13 @@ PROTOTYPES = {
                          c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p]),
     "vtp_unpool_add": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "vtp_pool_grad": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                              c_void_p, c_void_p]),
+    "vtp_unpool_grad": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                c_void_p, c_void_p]),
+    "vtp_batched_sparse_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_int, c_ll,
+                                        c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_int,
+                                        c_void_p]),
     "vtp_layernorm": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_float,
                               c_void_p, c_void_p]),
     "vtp_token_im2col": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),

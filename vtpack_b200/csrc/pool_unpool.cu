@@ -64,7 +64,8 @@ __device__ __forceinline__ void load_vecs(float (&dst)[MAXCH][Vec<T>::N], const 
 }
 
 // ------------------------------------------------------------------------------- pool
-// comp[p] = mean of the patch's tokens (sum in (dy,dx) order, then divide);  optionally
+// comp[p] = mean of the patch's tokens (sum in (dy,dx) order, then divide; mean = 0 keeps the
+// sum, which is the gradient of the replicate-unpool with respect to its packed rows);  optionally
 // xn[b,tok] = LN(x[b,tok]) for every token read and qn[p] = LN(comp[p]).  Every token
 // belongs to exactly one patch, so x is read once.
 // Algorithmic bytes: (B*N + L)*C*e  (+ (B*N + L)*C*e when the LayerNorm outputs are on).
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(256)
 pool_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
             const int4* __restrict__ patches, const int32_t* __restrict__ n_dev, int n_max,
             T* __restrict__ comp, const float* __restrict__ lnw, const float* __restrict__ lnb,
-            float eps, T* __restrict__ xn, T* __restrict__ qn) {
+            float eps, T* __restrict__ xn, T* __restrict__ qn, int mean) {
     constexpr int VN = Vec<T>::N;
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -133,7 +134,7 @@ pool_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
                 }
             }
         }
-        const float denom = (float)(step * step);
+        const float denom = mean ? (float)(step * step) : 1.0f;   // 1: the plain sum (gradient of the unpool)
 #pragma unroll
         for (int ch = 0; ch < MAXCH; ++ch) {
             const int chunk = lane + 32 * ch;
@@ -150,13 +151,14 @@ pool_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
 }
 
 // ----------------------------------------------------------------------------- unpool
-// out[b,tok] = (q[p] - comp[p]) + ref[b,tok] for every token of patch p.
+// out[b,tok] = (q[p] - comp[p]) + ref[b,tok] for every token of patch p; inv_area = 1 scales the
+// replicated row by 1/step^2 (the gradient of the mean pooling with respect to its tokens).
 // Algorithmic bytes: (2*B*N + L)*C*e (+ L*C*e for comp).
 template <typename T, int MAXCH>
 __global__ void __launch_bounds__(256)
 unpool_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, int C, int W,
               int num_extra, const int4* __restrict__ patches, const int32_t* __restrict__ n_dev,
-              int n_max, const T* ref, T* out) {
+              int n_max, const T* ref, T* out, int inv_area) {
     constexpr int VN = Vec<T>::N;
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -186,6 +188,12 @@ unpool_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, int C,
                     cv.to_float(c);
 #pragma unroll
                     for (int i = 0; i < VN; ++i) d[ch][i] -= c[i];
+                }
+                if (inv_area) {
+                    // gradient of the mean pooling: every token of the patch receives 1/step^2 of the row
+                    const float sc = 1.0f / (float)(step * step);
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) d[ch][i] *= sc;
                 }
             }
         }
@@ -228,6 +236,68 @@ unpool_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, int C,
             }
         }
     }
+}
+
+// ------------------------------------------------- any channel count (one thread per element)
+// The vector kernels above need rows of whole 16-byte chunks.  Training also pools narrow
+// tensors (the per-token gate value, one channel: vtpack/layers/dge.py:104-110); those rows
+// take the element-wise form of the same arithmetic, one thread per (packed row, channel) as in
+// grained_sample.cu:31-69 and :107-144.
+template <typename T>
+__global__ void __launch_bounds__(256)
+pool_any_c_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
+                  const int4* __restrict__ patches, const int32_t* __restrict__ n_dev, int n_max,
+                  T* __restrict__ comp, int mean) {
+    int L = n_max;
+    if (n_dev) L = min(__ldg(n_dev), n_max);
+    const long long total = (long long)L * C;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (long long)gridDim.x * blockDim.x) {
+        const int p = (int)(e / C), c = (int)(e % C);
+        const int4 pt = __ldg(patches + p);
+        const bool extra = pt.y < 0;
+        const int step = extra ? 1 : pt.w;
+        const int tok0 = extra ? (-pt.y - 1) : (num_extra + pt.y * W + pt.z);
+        const size_t row0 = (size_t)pt.x * N + tok0;
+        float sum = 0.f;
+        for (int dy = 0; dy < step; ++dy)
+            for (int dx = 0; dx < step; ++dx) sum += to_f32(x[(row0 + (size_t)dy * W + dx) * C + c]);
+        if (mean) sum = sum / (float)(step * step);
+        comp[e] = from_f32<T>(sum);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+unpool_any_c_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, int C, int W, int num_extra,
+                    const int4* __restrict__ patches, const int32_t* __restrict__ n_dev, int n_max,
+                    const T* ref, T* out, int inv_area) {
+    int L = n_max;
+    if (n_dev) L = min(__ldg(n_dev), n_max);
+    const long long total = (long long)L * C;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (long long)gridDim.x * blockDim.x) {
+        const int p = (int)(e / C), c = (int)(e % C);
+        const int4 pt = __ldg(patches + p);
+        const bool extra = pt.y < 0;
+        const int step = extra ? 1 : pt.w;
+        const int tok0 = extra ? (-pt.y - 1) : (num_extra + pt.y * W + pt.z);
+        const size_t row0 = (size_t)pt.x * N + tok0;
+        float d = to_f32(q[e]);
+        if (comp) d -= to_f32(comp[e]);
+        if (inv_area) d *= 1.0f / (float)(step * step);
+        for (int dy = 0; dy < step; ++dy)
+            for (int dx = 0; dx < step; ++dx) {
+                const size_t o = (row0 + (size_t)dy * W + dx) * C + c;
+                out[o] = from_f32<T>(ref ? d + to_f32(ref[o]) : d);
+            }
+    }
+}
+
+static int elem_grid(long long elems) {
+    const long long want = (elems + 255) / 256;
+    const long long cap = (long long)sm_count() * 8;
+    return (int)(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
 // -------------------------------------------------------------------------- layernorm
@@ -273,7 +343,13 @@ static int row_grid(int rows) {
 template <typename T>
 static int launch_pool(const void* x, int N, int C, int W, int num_extra, const int32_t* patches,
                        const int32_t* n_dev, int n_max, void* comp, const float* lnw,
-                       const float* lnb, float eps, void* xn, void* qn, cudaStream_t st) {
+                       const float* lnb, float eps, void* xn, void* qn, int mean, cudaStream_t st) {
+    if (C % Vec<T>::N != 0) {
+        if (lnw) return fail(VTP_ERR_SHAPE, "pool: fused LayerNorm needs C=%d in whole 16-byte chunks", C);
+        pool_any_c_kernel<T><<<elem_grid((long long)n_max * C), 256, 0, st>>>(
+            (const T*)x, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp, mean);
+        return check_launch("pool");
+    }
     const int maxch = ceil_div(C / Vec<T>::N, 32);
     const int grid = row_grid(n_max);
     const bool ln = lnw != nullptr;
@@ -282,11 +358,11 @@ static int launch_pool(const void* x, int N, int C, int W, int num_extra, const 
         if (ln)                                                                                      \
             pool_kernel<T, M, true><<<grid, 256, 0, st>>>(                                           \
                 (const T*)x, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp, lnw,  \
-                lnb, eps, (T*)xn, (T*)qn);                                                           \
+                lnb, eps, (T*)xn, (T*)qn, mean);                                                     \
         else                                                                                         \
             pool_kernel<T, M, false><<<grid, 256, 0, st>>>(                                          \
                 (const T*)x, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp,       \
-                nullptr, nullptr, eps, nullptr, nullptr);                                            \
+                nullptr, nullptr, eps, nullptr, nullptr, mean);                                      \
     } while (0)
     if (maxch <= 1) VTP_POOL(1);
     else if (maxch == 2) VTP_POOL(2);
@@ -301,12 +377,19 @@ static int launch_pool(const void* x, int N, int C, int W, int num_extra, const 
 template <typename T>
 static int launch_unpool(const void* q, const void* comp, int N, int C, int W, int num_extra,
                          const int32_t* patches, const int32_t* n_dev, int n_max, const void* ref,
-                         void* out, cudaStream_t st) {
+                         void* out, int inv_area, cudaStream_t st) {
+    if (C % Vec<T>::N != 0) {
+        unpool_any_c_kernel<T><<<elem_grid((long long)n_max * C), 256, 0, st>>>(
+            (const T*)q, (const T*)comp, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (const T*)ref,
+            (T*)out, inv_area);
+        return check_launch("unpool_add");
+    }
     const int maxch = ceil_div(C / Vec<T>::N, 32);
     const int grid = row_grid(n_max);
 #define VTP_UNPOOL(M)                                                                           \
     unpool_kernel<T, M><<<grid, 256, 0, st>>>((const T*)q, (const T*)comp, N, C, W, num_extra,  \
-                                              (const int4*)patches, n_dev, n_max, (const T*)ref, (T*)out)
+                                              (const int4*)patches, n_dev, n_max, (const T*)ref,      \
+                                              (T*)out, inv_area)
     if (maxch <= 1) VTP_UNPOOL(1);
     else if (maxch == 2) VTP_UNPOOL(2);
     else if (maxch == 3) VTP_UNPOOL(3);
@@ -343,6 +426,19 @@ static int check_rows(const char* what, int dtype, int C, const void* a, const v
     return VTP_OK;
 }
 
+// pool / unpool rows: any C > 0; rows of whole 16-byte chunks take the vector kernels, which need
+// 16-byte aligned pointers
+static bool vector_rows(int dtype, int C) { return C % (16 / (int)elem_size(dtype)) == 0; }
+static int check_token_rows(const char* what, int dtype, int C, const void* a, const void* b, const void* c,
+                            const void* d) {
+    VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "%s: dtype %d", what, dtype);
+    VTP_REQUIRE(C > 0, VTP_ERR_SHAPE, "%s: C=%d", what, C);
+    if (vector_rows(dtype, C))
+        VTP_REQUIRE(aligned16(a) && aligned16(b) && aligned16(c) && aligned16(d), VTP_ERR_ALIGN,
+                    "%s: unaligned pointer", what);
+    return VTP_OK;
+}
+
 }  // namespace vtp
 
 using namespace vtp;
@@ -356,15 +452,15 @@ extern "C" int vtp_pool(const void* x, int dtype, int B, int N, int C, int W, in
     VTP_REQUIRE(ln_w || (!xn && !qn), VTP_ERR_NULL, "pool: xn/qn need LayerNorm weights");
     VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
                 "pool: bad shape");
-    if (int rc = check_rows("pool", dtype, C, x, comp)) return rc;
-    VTP_REQUIRE(aligned16(patches) && aligned16(xn) && aligned16(qn), VTP_ERR_ALIGN, "pool: unaligned pointer");
+    if (int rc = check_token_rows("pool", dtype, C, x, comp, xn, qn)) return rc;
+    VTP_REQUIRE(aligned16(patches), VTP_ERR_ALIGN, "pool: unaligned patch list");
     if (n_patches_max == 0) return VTP_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == VTP_F32)
         return launch_pool<float>(x, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, comp,
-                                  ln_w, ln_b, eps, xn, qn, st);
+                                  ln_w, ln_b, eps, xn, qn, 1, st);
     return launch_pool<bf16>(x, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, comp, ln_w,
-                             ln_b, eps, xn, qn, st);
+                             ln_b, eps, xn, qn, 1, st);
 }
 
 extern "C" int vtp_unpool_add(const void* q, const void* comp, int dtype, int B, int N, int C, int W,
@@ -373,16 +469,51 @@ extern "C" int vtp_unpool_add(const void* q, const void* comp, int dtype, int B,
     VTP_REQUIRE(q && patches && out, VTP_ERR_NULL, "unpool: null pointer");
     VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
                 "unpool: bad shape");
-    if (int rc = check_rows("unpool", dtype, C, q, out)) return rc;
-    VTP_REQUIRE(aligned16(patches) && aligned16(comp) && aligned16(ref), VTP_ERR_ALIGN,
-                "unpool: unaligned pointer");
+    if (int rc = check_token_rows("unpool", dtype, C, q, out, comp, ref)) return rc;
+    VTP_REQUIRE(aligned16(patches), VTP_ERR_ALIGN, "unpool: unaligned patch list");
     if (n_patches_max == 0) return VTP_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == VTP_F32)
         return launch_unpool<float>(q, comp, N, C, W, num_extra, patches, n_patches_dev, n_patches_max,
-                                    ref, out, st);
+                                    ref, out, 0, st);
     return launch_unpool<bf16>(q, comp, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, ref,
-                               out, st);
+                               out, 0, st);
+}
+
+// Gradients of the two movers; each is the other kernel with a different scale
+// (vtpack/layers/grained_sample.py:26-38 and :61-78).
+extern "C" int vtp_pool_grad(const void* grad_comp, int dtype, int B, int N, int C, int W, int num_extra,
+                             const int32_t* patches, const int32_t* n_patches_dev, int n_patches_max,
+                             void* grad_x, void* stream) {
+    VTP_REQUIRE(grad_comp && patches && grad_x, VTP_ERR_NULL, "pool_grad: null pointer");
+    VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
+                "pool_grad: bad shape");
+    if (int rc = check_token_rows("pool_grad", dtype, C, grad_comp, grad_x, nullptr, nullptr)) return rc;
+    VTP_REQUIRE(aligned16(patches), VTP_ERR_ALIGN, "pool_grad: unaligned patch list");
+    if (n_patches_max == 0) return VTP_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == VTP_F32)
+        return launch_unpool<float>(grad_comp, nullptr, N, C, W, num_extra, patches, n_patches_dev,
+                                    n_patches_max, nullptr, grad_x, 1, st);
+    return launch_unpool<bf16>(grad_comp, nullptr, N, C, W, num_extra, patches, n_patches_dev, n_patches_max,
+                               nullptr, grad_x, 1, st);
+}
+
+extern "C" int vtp_unpool_grad(const void* grad_out, int dtype, int B, int N, int C, int W, int num_extra,
+                               const int32_t* patches, const int32_t* n_patches_dev, int n_patches_max,
+                               void* grad_q, void* stream) {
+    VTP_REQUIRE(grad_out && patches && grad_q, VTP_ERR_NULL, "unpool_grad: null pointer");
+    VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
+                "unpool_grad: bad shape");
+    if (int rc = check_token_rows("unpool_grad", dtype, C, grad_out, grad_q, nullptr, nullptr)) return rc;
+    VTP_REQUIRE(aligned16(patches), VTP_ERR_ALIGN, "unpool_grad: unaligned patch list");
+    if (n_patches_max == 0) return VTP_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == VTP_F32)
+        return launch_pool<float>(grad_out, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, grad_q,
+                                  nullptr, nullptr, 0.f, nullptr, nullptr, 0, st);
+    return launch_pool<bf16>(grad_out, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, grad_q,
+                             nullptr, nullptr, 0.f, nullptr, nullptr, 0, st);
 }
 
 extern "C" int vtp_layernorm(const void* x, int dtype, int rows_max, const int32_t* rows_dev, int C,

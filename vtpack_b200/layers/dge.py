@@ -1,16 +1,26 @@
 """``DynamicGrainedEncoder`` / ``DynamicRouter`` with the reference's constructor,
 parameters (``splits``, ``router.gate.*``), ``states`` dict and methods
-(``vtpack/layers/dge.py:19-150``), for eval-mode inference on CUDA."""
+(``vtpack/layers/dge.py:19-150``) on CUDA.  Eval mode runs the fused gate kernel; training mode
+(Gumbel-softmax gate, ``dge.py:66-67``) keeps the router in autograd and moves tokens through the
+differentiable ``grained_sample_compress`` / ``grained_sample_decompress``, or through the dense
+all-grains form when ``sparse_train`` is off (``dge.py:69-73,92-96``)."""
 import ctypes
 import math
 from typing import List
 
 import torch
+import torch.nn.functional as F
 from torch import nn
 
 from .. import _lib
 from ..runtime import dtype_code, ptr, require_cuda, stream_ptr
-from .grained_sample import grained_sample_compress, grained_sample_decompress, grained_sample_index_to_patch
+from .grained_sample import (
+    grained_sample_compress,
+    grained_sample_compress_dense,
+    grained_sample_decompress,
+    grained_sample_decompress_dense,
+    grained_sample_index_to_patch,
+)
 
 
 class DynamicRouter(nn.Module):
@@ -41,7 +51,13 @@ class DynamicRouter(nn.Module):
         return comp
 
     def forward(self, x):
-        """x [B,H,W,C] -> gate logits fp32 [B,H/r,W/r,n_splits]."""
+        """x [B,H,W,C] -> gate logits [B,H/r,W/r,n_splits] (fp32 from the fused kernel in eval mode;
+        in training mode the region mean and the Linear stay in autograd, ``dge.py:145-150``)."""
+        if self.training:
+            B, H, W, C = x.shape
+            r = self.region_size
+            pooled = x.reshape(B, H // r, r, W // r, r, C).mean(dim=(2, 4))
+            return self.gate(pooled)
         require_cuda(x)
         x = x.contiguous()
         B, H, W, C = x.shape
@@ -84,8 +100,11 @@ class DynamicGrainedEncoder(nn.Module):
             # to the host here
             num_queries = self.states["batches_device"].double()
         else:
-            indices = gate.argmax(dim=-1, keepdim=True)
-            gate = torch.zeros_like(gate).scatter_(-1, indices, 1.0)
+            if not self.training:
+                indices = gate.argmax(dim=-1, keepdim=True)
+                gate = torch.zeros_like(gate).scatter_(-1, indices, 1.0)
+            # in training mode the gate is the hard Gumbel-softmax sample: already one-hot, and it keeps
+            # its straight-through gradient so a complexity loss can train the router
             num_queries = gate * (self.splits[None, None, None, :] ** 2)
             num_queries = num_queries.view(B, -1).double().sum(-1)
             num_queries = num_queries + self.states["num_extra_tokens"]
@@ -96,9 +115,9 @@ class DynamicGrainedEncoder(nn.Module):
         return {"static": static_cp, "dynamic": dynamic_cp}
 
     def compress(self, x, H, W):
-        """x [B,N,C] -> packed queries [L,C] (``dge.py:61-85``, eval branch)."""
+        """x [B,N,C] -> packed queries [L,C] (``dge.py:61-85``)."""
         if self.training:
-            raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
+            return self._compress_train(x, H, W)
         require_cuda(x)
         x = x.contiguous()
         B, N, C = x.shape
@@ -123,7 +142,7 @@ class DynamicGrainedEncoder(nn.Module):
     def decompress(self, x):
         """packed queries [L,C] -> tokens [B,N,C]: input + replicate(x - comp) (``dge.py:87-112``)."""
         if self.training:
-            raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
+            return self._decompress_train(x)
         st = self.states
         ref = st["input"]
         B, N, C = ref.shape
@@ -135,3 +154,45 @@ class DynamicGrainedEncoder(nn.Module):
             ptr(x), ptr(st["comp"]), dtype_code(x.dtype), B, N, C, W, st["num_extra_tokens"], ptr(p32), None,
             p32.shape[0], ptr(ref), ptr(out), stream_ptr(x.device)))
         return out
+
+    # ------------------------------------------------------------------ training mode
+    def _compress_train(self, x, H, W):
+        """``dge.py:61-85`` with ``self.training``: hard Gumbel-softmax gate (straight-through), then
+        either every grain of every region (dense) or the sampled grain only (``sparse_train``)."""
+        B, N, C = x.shape
+        num_extra_tokens = N - H * W
+        gate = self.router(x[:, num_extra_tokens:, :].reshape(B, H, W, C))
+        gate = F.gumbel_softmax(gate, dim=-1, hard=True)
+        if not self.sparse_train:
+            patches = None
+            comp, batches = grained_sample_compress_dense(x, self.splits, self.region_size, H, W, num_extra_tokens)
+        else:
+            indices = gate.argmax(dim=-1)
+            patches, batches = grained_sample_index_to_patch(indices, self.splits, self.region_size,
+                                                             num_extra_tokens)
+            comp = grained_sample_compress(x, patches, H, W, num_extra_tokens)
+        self.states.update({
+            "comp": comp, "input": x, "patches": patches, "batches": batches,
+            "gate": gate, "size": (H, W), "num_extra_tokens": num_extra_tokens,
+        })
+        return comp
+
+    def _decompress_train(self, x):
+        """``dge.py:87-112`` with ``self.training``: the gate value (1 in the forward pass, carrying the
+        straight-through gradient in the backward pass) multiplies the update of every query."""
+        st = self.states
+        x = x - st["comp"]
+        H, W = st["size"]
+        num_extra_tokens = st["num_extra_tokens"]
+        if not self.sparse_train:
+            return grained_sample_decompress_dense(x, st["gate"], st["input"], self.splits, self.region_size,
+                                                   H, W, num_extra_tokens, True)
+        B, N, C = st["input"].shape
+        r = self.region_size
+        gate = st["gate"].max(dim=-1, keepdim=True)[0]                       # [B,Hr,Wr,1]
+        Hr, Wr = gate.shape[1:3]
+        gate = gate.reshape(B, Hr, 1, Wr, 1, 1).expand(B, Hr, r, Wr, r, 1).reshape(B, H * W, 1)
+        if num_extra_tokens > 0:
+            gate = torch.cat([gate.new_ones([B, num_extra_tokens, 1]), gate], dim=1)
+        gate = grained_sample_compress(gate, st["patches"], H, W, num_extra_tokens)
+        return grained_sample_decompress(x * gate, st["patches"], st["input"], H, W, num_extra_tokens, True)

@@ -1,4 +1,4 @@
-"""DeiT + Dynamic Grained Encoder for eval-mode inference on B200.
+"""DeiT + Dynamic Grained Encoder on B200: fused eval-mode inference, op-by-op training mode.
 
 Same classes, constructor arguments, parameter names (state_dict keys) and factory
 names as ``vtpack/models/dge/deit_dge.py`` so checkpoints of the reference load
@@ -7,7 +7,10 @@ each (``vtp_dge_block_forward`` / ``vtp_deit_dge_forward``): every kernel is lau
 from C++ on the current stream and the variable number of queries never leaves the
 device.  ``Block.forward_unfused`` follows the reference's op-by-op sequence through
 the ``vtpack_b200.layers`` functions (it synchronises once per block, as the reference
-does).  Training mode is not implemented.
+does).  In training mode (``module.train()``) the blocks run the reference's training sequence
+(``deit_dge.py:79-98,123-130``): dense layers, LayerNorm, softmax and GELU through PyTorch's autograd
+as in the reference, token movement and the ragged attention products through this library's
+differentiable ``grained_sample_compress`` / ``grained_sample_decompress`` / ``batched_sparse_gemm``.
 """
 import ctypes
 import math
@@ -17,7 +20,7 @@ import torch
 import torch.nn as nn
 
 from ... import _lib
-from ...layers import DynamicGrainedEncoder, batched_sparse_attention
+from ...layers import DynamicGrainedEncoder, batched_sparse_attention, batched_sparse_gemm
 from ...runtime import dtype_code, ptr, require_cuda, scratch, stream_ptr
 
 __all__ = [
@@ -71,6 +74,9 @@ class Mlp(nn.Module):
         return comp
 
     def forward(self, x, residual=None):
+        if self.training:
+            y = self.drop(self.fc2(self.drop(self.act(self.fc1(x)))))           # deit_dge.py:38-44
+            return y if residual is None else residual + y
         return _linear(_linear(x, self.fc1, gelu=True), self.fc2, residual=residual)
 
 
@@ -98,14 +104,56 @@ class Attention(nn.Module):
 
     def forward(self, x, q, q_lengths, residual=None):
         """x [B,N,C] (normed tokens), q [L,C] (normed queries) -> [L,C]
-        (``deit_dge.py:70-98``, eval branch)."""
+        (``deit_dge.py:70-98``)."""
         B, N, C = x.shape
         h = self.num_heads
+        if self.training:
+            y = self._forward_train(x, q, q_lengths)
+            return y if residual is None else residual + y
         qh = _linear(q, self.q).reshape(-1, h, C // h).permute(1, 0, 2)
         kv = _linear(x.reshape(B * N, C), self.kv).reshape(B, N, 2, h, C // h).permute(2, 3, 0, 1, 4)
         o = batched_sparse_attention(qh, kv[0], kv[1], q_lengths, self.scale)
         o = o.transpose(0, 1).reshape(-1, C)
         return _linear(o, self.proj, residual=residual)
+
+    def _forward_train(self, x, q, q_lengths):
+        """Training branch of ``deit_dge.py:79-98``: a batched product when every image has the same
+        number of queries, else the two ragged products with the softmax between them."""
+        B, N, C = x.shape
+        h, d = self.num_heads, C // self.num_heads
+        q = self.q(q).reshape(-1, h, d).permute(1, 0, 2)
+        kv = self.kv(x).reshape(B, N, 2, h, d).permute(2, 3, 0, 1, 4)
+        k, v = kv[0], kv[1]
+        if int(q_lengths.max() - q_lengths.min()) == 0:
+            q = q.reshape(h, B, -1, d)
+            attn = (q @ k.transpose(-1, -2)) * self.scale
+            attn = self.attn_drop(attn.softmax(dim=-1, dtype=v.dtype))
+            o = (attn @ v).permute(1, 2, 0, 3).reshape(-1, C)
+        else:
+            kv_lengths = q_lengths.new_full([B], N)
+            k = k.reshape(h, -1, d)
+            v = v.reshape(h, -1, d)
+            attn = batched_sparse_gemm(q, k, q_lengths, kv_lengths, False, True) * self.scale
+            attn = self.attn_drop(attn.softmax(dim=-1, dtype=v.dtype))
+            o = batched_sparse_gemm(attn, v, q_lengths, kv_lengths, False, False)
+            o = o.transpose(0, 1).reshape(-1, C)
+        return self.proj_drop(self.proj(o))
+
+
+class DropPath(nn.Module):
+    """Stochastic depth: in training mode each row of the first axis keeps its residual branch with
+    probability 1 - p, scaled by 1 / (1 - p); identity otherwise."""
+
+    def __init__(self, p=0.):
+        super().__init__()
+        self.p = float(p)
+
+    def forward(self, x):
+        if not self.training or self.p == 0.:
+            return x
+        keep = 1.0 - self.p
+        mask = x.new_empty((x.shape[0],) + (1,) * (x.dim() - 1)).bernoulli_(keep)
+        return x * (mask / keep)
 
 
 class _WeightPack:
@@ -189,7 +237,7 @@ class Block(nn.Module):
         self.norm1 = norm_layer(dim)
         self.attn = Attention(dim, num_heads=num_heads, qkv_bias=qkv_bias, qk_scale=qk_scale,
                               attn_drop=attn_drop, proj_drop=drop)
-        self.drop_path = nn.Identity()          # stochastic depth is a training-only feature
+        self.drop_path = DropPath(drop_path) if drop_path > 0. else nn.Identity()   # training mode only
         self.norm2 = norm_layer(dim)
         mlp_hidden_dim = int(dim * mlp_ratio)
         self.mlp = Mlp(in_features=dim, hidden_features=mlp_hidden_dim, act_layer=act_layer, drop=drop)
@@ -215,9 +263,10 @@ class Block(nn.Module):
     def forward(self, x, forced_gate=None, dense=False):
         """One C-ABI call for the whole block (``deit_dge.py:123-130``).  ``forced_gate``
         (fp32 [B,Hr,Wr,n_splits]) replaces the router output; ``dense`` runs the dense
-        DeiT block built from the same weights instead."""
+        DeiT block built from the same weights instead.  In training mode: the reference's
+        differentiable sequence."""
         if self.training:
-            raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
+            return self._forward_train(x)
         require_cuda(x)
         x = x.contiguous()
         s = self.shape_struct(x)
@@ -239,6 +288,15 @@ class Block(nn.Module):
                                 "num_extra_tokens": s.num_extra})
         return out
 
+    def _forward_train(self, x):
+        """``deit_dge.py:123-130`` with ``self.training``."""
+        B, N, C = x.shape
+        H = W = int(math.sqrt(N))
+        q = self.dge.compress(x, H, W)
+        q = q + self.drop_path(self.attn(self.norm1(x), self.norm1(q), self.dge.states["batches"]))
+        q = q + self.drop_path(self.mlp(self.norm2(q)))
+        return self.dge.decompress(q)
+
     def forward_unfused(self, x):
         """The reference's sequence op by op through vtpack_b200.layers."""
         B, N, C = x.shape
@@ -259,6 +317,11 @@ class PatchEmbed(nn.Module):
         self.patch_size = patch_size
         self.num_patches = (img_size // patch_size) ** 2
         self.proj = nn.Conv2d(in_chans, embed_dim, kernel_size=patch_size, stride=patch_size)
+
+    def forward(self, x):
+        """Used by the training-mode forward only; eval mode runs the patch embedding inside the
+        model's fused C-ABI call."""
+        return self.proj(x).flatten(2).transpose(1, 2)
 
 
 class VisionTransformer(nn.Module):
@@ -282,11 +345,13 @@ class VisionTransformer(nn.Module):
         self.cls_token = nn.Parameter(torch.zeros(1, 1, embed_dim))
         self.dist_token = None
         self.pos_embed = nn.Parameter(torch.zeros(1, num_patches + self.num_tokens, embed_dim))
+        self.pos_drop = nn.Dropout(p=drop_rate)
+        dpr = [v.item() for v in torch.linspace(0, drop_path_rate, depth)]   # drop rate grows linearly with depth
         self.blocks = nn.Sequential(*[
             Block(dim=embed_dim, num_heads=num_heads, mlp_ratio=mlp_ratio, qkv_bias=qkv_bias, qk_scale=qk_scale,
-                  drop=drop_rate, attn_drop=attn_drop_rate, drop_path=0., norm_layer=norm_layer,
+                  drop=drop_rate, attn_drop=attn_drop_rate, drop_path=dpr[i], norm_layer=norm_layer,
                   act_layer=act_layer, split_sizes=split_sizes)
-            for _ in range(depth)])
+            for i in range(depth)])
         self.norm = norm_layer(embed_dim)
         self.pre_logits = nn.Identity()
         self.head = nn.Linear(self.num_features, num_classes)
@@ -358,9 +423,10 @@ class VisionTransformer(nn.Module):
     def forward(self, x, logits_out=None):
         """images [B,3,S,S] on the device (fp32, or bf16 to halve the host-to-device copy of
         a bf16 model: the kernel rounds fp32 pixels to bf16 anyway) -> logits fp32
-        [B,num_classes] (``deit_dge.py:267-299``) in one C-ABI call."""
+        [B,num_classes] (``deit_dge.py:267-299``) in one C-ABI call.  In training mode: the
+        differentiable op-by-op sequence in the parameters' dtype."""
         if self.training:
-            raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
+            return self._forward_train(x)
         require_cuda(x)
         if x.dtype not in (torch.float32, torch.bfloat16):
             x = x.float()
@@ -389,6 +455,15 @@ class VisionTransformer(nn.Module):
             blk.dge.states.update({"batches_device": counts[i], "input": tokens, "gate": None, "size": (G, G),
                                    "num_extra_tokens": 1})
         return logits
+
+    def _forward_train(self, x):
+        """``deit_dge.py:267-299`` with ``self.training`` (cls token, no distillation token)."""
+        x = self.patch_embed(x.to(self.compute_dtype()))
+        x = torch.cat((self.cls_token.expand(x.shape[0], -1, -1), x), dim=1)
+        x = self.pos_drop(x + self.pos_embed)
+        x = self.blocks(x)
+        x = self.norm(x)
+        return self.head(self.pre_logits(x[:, 0]))
 
     def complexity(self, x):
         """Static and dynamic MACs per image of the last forward, averaged over the batch
