@@ -96,7 +96,7 @@ def test_router_gate(vl, dtype, C):
     r = DynamicRouter(C, [4, 2, 1])
     torch.nn.init.trunc_normal_(r.gate.weight, std=0.02, generator=torch.Generator().manual_seed(6))
     ref = O.router_forward(x.float().reshape(B, G, G, C), r.gate.weight.detach(), r.gate.bias.detach(), 4)
-    got = r.to(DEV)(x.to(DEV).reshape(B, G, G, C))
+    got = r.to(DEV).eval()(x.to(DEV).reshape(B, G, G, C))     # eval mode: the fused gate kernel
     assert got.dtype == torch.float32
     assert torch.allclose(got.cpu(), ref, rtol=1e-4, atol=1e-5)
     top2 = ref.topk(2, -1).values

@@ -106,9 +106,10 @@ def test_ragged_products_match_reference(layers, golden_dir):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False)])
 def test_ragged_products_all_flag_combinations(layers, dtype, ta, tb):
-    """Every transpose combination, ragged lengths (an empty image included) and sizes that are not
+    """The transpose combinations the forward and backward passes use (both operands transposed
+    would need the same row count in every image on both sides), ragged lengths (an empty image included) and sizes that are not
     multiples of the tile, against the CPU restatement in float64."""
     h, B, ka = 3, 4, 70
     la = torch.tensor([67, 0, 129, 5])
@@ -120,8 +121,6 @@ def test_ragged_products_all_flag_combinations(layers, dtype, ta, tb):
     else:           # op(a_i) is [la, ka]: b_i needs ka rows (or ka columns when transposed)
         lb = torch.full([B], ka, dtype=torch.long) if not tb else torch.full([B], 33, dtype=torch.long)
         kb = 41 if not tb else ka
-    if ta and tb:
-        pytest.skip("op(b_i) would need la columns in every image: not expressible with one column count")
     b = torch.randn(h, int(lb.sum()), kb, generator=gen).to(dtype)
     ref = O.batched_sparse_gemm_forward(a.double(), b.double(), la, lb, ta, tb)
     out = layers.batched_sparse_gemm(a.to(DEV), b.to(DEV), la, lb, ta, tb)
@@ -167,7 +166,7 @@ def test_training_block_matches_reference(golden_dir, mode):
             assert prm.grad is not None, name
             assert rel_err(prm.grad, z[key]) < 5 * TOL, name
             checked += 1
-    assert checked >= 17
+    assert checked == 16          # two LayerNorms, five Linears and the gate: weight and bias each
 
 
 def test_training_model_step_and_eval_after():
