@@ -585,3 +585,7 @@ def train_block_weights() -> Dict[str, torch.Tensor]:
         if k.endswith("bias") and v.is_floating_point():
             sd[k] = v + 0.02 * torch.randn(v.shape, generator=g)
     return sd
+
+
+TRAIN_PVT_BLOCK = dict(dim=32, heads=1, grid=16, sr=2, mlp_ratio=8, batch=2, noise_seed=23, grad_seed=24,
+                       weight_seed=7, token_seed=8)

@@ -26,6 +26,9 @@ Fixtures
                         sparse_train on and off; Gumbel noise seed 21 injected through
                         oracle.dge_oracle.gumbel_softmax_fixed; output, input gradient and
                         parameter gradients for the loss sum(out * g), g seed 22.
+  train_pvt_block_fp32.npz  one PVT+DGE block (dim 32, 1 head, 16x16 grid, spatial reduction 2) in
+                        training mode with sparse_train on, fp32, B=2; Gumbel noise seed 23 injected;
+                        output, input gradient, parameter gradients for sum(out * g), g seed 24.
 Inputs are regenerated from the seeds by the tests; each fixture carries a
 float64 sum of its inputs so RNG drift is detected rather than misread as a
 parity failure.
@@ -238,6 +241,37 @@ def train_block_fixture():
     print("train_block_fp32.npz", sorted(out)[:6], "...", len(out), "arrays")
 
 
+def train_pvt_block_fixture():
+    import importlib
+    from functools import partial
+    import torch.nn.functional as F
+    ref_shim.install()
+    pvt = importlib.import_module("vtpack.models.dge.pvt_dge")
+    cfg = O.TRAIN_PVT_BLOCK
+    w = O.make_pvt_block_weights(cfg["dim"], cfg["mlp_ratio"], cfg["sr"], seed=cfg["weight_seed"])
+    blk = pvt.Block(cfg["dim"], cfg["heads"], mlp_ratio=cfg["mlp_ratio"], qkv_bias=True,
+                    norm_layer=partial(torch.nn.LayerNorm, eps=1e-6), sr_ratio=cfg["sr"], split_sizes=[4, 2, 1])
+    blk.load_state_dict(w, strict=True)
+    blk.train()
+    blk.dge.sparse_train = True
+    G = cfg["grid"]
+    x = O.randn_seeded((cfg["batch"], G * G, cfg["dim"]), cfg["token_seed"]).requires_grad_(True)
+    g = O.randn_seeded((cfg["batch"], G * G, cfg["dim"]), cfg["grad_seed"])
+    real = F.gumbel_softmax
+    F.gumbel_softmax = O.gumbel_softmax_fixed([O.make_gumbel_noise((cfg["batch"], G // 4, G // 4, 3), cfg["noise_seed"])])
+    try:
+        y = blk(x, G, G)
+        (y * g).sum().backward()
+    finally:
+        F.gumbel_softmax = real
+    out = {"out": y.detach().numpy(), "grad_x": x.grad.numpy(), "lengths": np.asarray(blk.dge.states["batches"])}
+    for name, prm in blk.named_parameters():
+        if prm.grad is not None:
+            out[f"grad.{name}"] = prm.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "train_pvt_block_fp32.npz"), **out)
+    print("train_pvt_block_fp32.npz", out["lengths"], len(out), "arrays")
+
+
 if __name__ == "__main__":
     layer_fixture()
     model_fixture()
@@ -245,3 +279,4 @@ if __name__ == "__main__":
     pvt_model_fixture()
     train_ops_fixture()
     train_block_fixture()
+    train_pvt_block_fixture()

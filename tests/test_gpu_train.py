@@ -202,3 +202,40 @@ def test_training_model_step_and_eval_after():
     with torch.no_grad():
         logits_after = m(images)
     assert torch.isfinite(logits_after).all() and not torch.equal(logits_after, logits_before)
+
+
+def test_training_pvt_block_matches_reference(golden_dir):
+    """A PVT+DGE block with spatial-reduction keys in training mode (sparse_train on): output,
+    input gradient and all parameter gradients against the reference's."""
+    from functools import partial
+    from vtpack_b200.models.dge import pvt_dge
+    z = _golden(golden_dir, "train_pvt_block_fp32.npz")
+    cfg = O.TRAIN_PVT_BLOCK
+    blk = pvt_dge.Block(cfg["dim"], cfg["heads"], mlp_ratio=cfg["mlp_ratio"], qkv_bias=True,
+                        norm_layer=partial(torch.nn.LayerNorm, eps=1e-6), sr_ratio=cfg["sr"], split_sizes=[4, 2, 1])
+    blk.load_state_dict(O.make_pvt_block_weights(cfg["dim"], cfg["mlp_ratio"], cfg["sr"], seed=cfg["weight_seed"]),
+                        strict=True)
+    blk.to(DEV).train()
+    blk.dge.sparse_train = True
+    G = cfg["grid"]
+    x = O.randn_seeded((cfg["batch"], G * G, cfg["dim"]), cfg["token_seed"]).to(DEV).requires_grad_(True)
+    g = O.randn_seeded((cfg["batch"], G * G, cfg["dim"]), cfg["grad_seed"]).to(DEV)
+    real = F.gumbel_softmax
+    F.gumbel_softmax = O.gumbel_softmax_fixed([O.make_gumbel_noise((cfg["batch"], G // 4, G // 4, 3), cfg["noise_seed"])])
+    prev = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False          # the reduction convolution in full fp32
+    try:
+        y = blk(x, G, G)
+        (y * g).sum().backward()
+    finally:
+        F.gumbel_softmax = real
+        torch.backends.cudnn.allow_tf32 = prev
+    assert torch.equal(blk.dge.states["batches"].cpu(), z["lengths"])
+    assert rel_err(y, z["out"]) < TOL
+    assert rel_err(x.grad, z["grad_x"]) < TOL
+    checked = 0
+    for name, prm in blk.named_parameters():
+        if f"grad.{name}" in z:
+            assert rel_err(prm.grad, z[f"grad.{name}"]) < 5 * TOL, name
+            checked += 1
+    assert checked == 20          # DeiT block's 16 plus the reduction convolution and its LayerNorm

@@ -1,4 +1,4 @@
-"""Eval-mode mirror of the reference's PVT+DGE block (``vtpack/models/dge/pvt_dge.py:19-146``): the
+"""Mirror of the reference's PVT+DGE block (``vtpack/models/dge/pvt_dge.py:19-146``): the
 same class names, constructor arguments and state_dict keys, with ``Block.forward(x, H, W)`` as
 one call into the CUDA library.  Keys and values come from the normed tokens reduced by the
 stride-``sr_ratio`` convolution ``attn.sr`` and the LayerNorm ``attn.norm``; everything else is
@@ -6,6 +6,9 @@ the DeiT+DGE block.  ``PyramidVisionTransformer`` (``pvt_dge.py:182-337``) seque
 through the library's entry points: patch embedding = im2col + Linear + LayerNorm, position
 embedding / cls rows = ``vtp_add_rows``, blocks, and between stages the token rows themselves
 stand for the ``[B, C, H, W]`` map (``vtp_token_im2col`` gathers the 2 x 2 windows from them).
+A block in training mode (``module.train()``) runs the reference's differentiable sequence
+(``pvt_dge.py:77-146``) like the DeiT+DGE mirror does: dense layers through PyTorch autograd, token
+movement and ragged attention products through this library's differentiable ops.
 """
 import ctypes
 from functools import partial
@@ -14,9 +17,9 @@ import torch
 import torch.nn as nn
 
 from ... import _lib
-from ...layers import DynamicGrainedEncoder
+from ...layers import DynamicGrainedEncoder, batched_sparse_attention, batched_sparse_gemm
 from ...runtime import dtype_code, ptr, require_cuda, scratch, stream_ptr
-from .deit_dge import Mlp, _WeightPack, _pack_block, _shape_struct
+from .deit_dge import DropPath, Mlp, _WeightPack, _pack_block, _shape_struct
 
 __all__ = ["Mlp", "Attention", "Block", "PatchEmbed", "PyramidVisionTransformer",
            "pvt_dge_s124_tiny_256", "pvt_dge_s124_small_256", "pvt_dge_s124_medium_256", "pvt_dge_s124_large_256"]
@@ -40,6 +43,36 @@ class Attention(nn.Module):
             self.sr = nn.Conv2d(dim, dim, kernel_size=sr_ratio, stride=sr_ratio)
             self.norm = nn.LayerNorm(dim)
 
+    def forward(self, x, q, H, W, q_lengths):
+        """x [B,N,C] normed tokens, q [L,C] normed queries -> [L,C] (``pvt_dge.py:77-114``), op by op
+        through the parameters' own modules; differentiable in training mode.  The eval-mode fast
+        path is ``Block.forward``, which never comes through here."""
+        B, N, C = x.shape
+        h, d = self.num_heads, C // self.num_heads
+        q = self.q(q).reshape(-1, h, d).permute(1, 0, 2)
+        if self.sr_ratio > 1:
+            x_ = x.permute(0, 2, 1).reshape(B, C, H, W)
+            x_ = self.norm(self.sr(x_).reshape(B, C, -1).permute(0, 2, 1))
+            kv = self.kv(x_)
+        else:
+            kv = self.kv(x)
+        kv = kv.reshape(B, -1, 2, h, d).permute(2, 3, 0, 1, 4)
+        k, v = kv[0], kv[1]
+        n_keys = kv.shape[3]
+        if not self.training:
+            o = batched_sparse_attention(q, k, v, q_lengths, self.scale).transpose(0, 1).reshape(-1, C)
+        elif int(q_lengths.max() - q_lengths.min()) == 0:
+            q = q.reshape(h, B, -1, d)
+            attn = self.attn_drop(((q @ k.transpose(-1, -2)) * self.scale).softmax(dim=-1, dtype=v.dtype))
+            o = (attn @ v).permute(1, 2, 0, 3).reshape(-1, C)
+        else:
+            kv_lengths = q_lengths.new_full([B], n_keys)
+            k, v = k.reshape(h, -1, d), v.reshape(h, -1, d)
+            attn = batched_sparse_gemm(q, k, q_lengths, kv_lengths, False, True) * self.scale
+            attn = self.attn_drop(attn.softmax(dim=-1, dtype=v.dtype))
+            o = batched_sparse_gemm(attn, v, q_lengths, kv_lengths, False, False).transpose(0, 1).reshape(-1, C)
+        return self.proj_drop(self.proj(o))
+
     def complexity(self, num_inputs, num_queries):
         num_channels = self.dim
         comp = num_queries * (num_channels ** 2)  # q embed
@@ -62,7 +95,7 @@ class Block(nn.Module):
         self.norm1 = norm_layer(dim)
         self.attn = Attention(dim, num_heads=num_heads, qkv_bias=qkv_bias, qk_scale=qk_scale,
                               attn_drop=attn_drop, proj_drop=drop, sr_ratio=sr_ratio)
-        self.drop_path = nn.Identity()
+        self.drop_path = DropPath(drop_path) if drop_path > 0. else nn.Identity()   # training mode only
         self.norm2 = norm_layer(dim)
         self.mlp = Mlp(in_features=dim, hidden_features=int(dim * mlp_ratio), act_layer=act_layer, drop=drop)
         self.dge = DynamicGrainedEncoder(in_channels=dim, split_sizes=split_sizes, complexity_handler=self.complexity)
@@ -80,9 +113,12 @@ class Block(nn.Module):
     def forward(self, x, H, W, forced_gate=None):
         """x [B, N, C] with N = H*W (+ extra tokens when sr_ratio == 1) -> [B, N, C]
         (``pvt_dge.py:140-146``), one C-ABI call.  ``forced_gate`` (fp32 [B,Hr,Wr,n_splits])
-        replaces the router output."""
+        replaces the router output.  In training mode: the reference's differentiable sequence."""
         if self.training:
-            raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
+            q = self.dge.compress(x, H, W)
+            q = q + self.drop_path(self.attn(self.norm1(x), self.norm1(q), H, W, self.dge.states["batches"]))
+            q = q + self.drop_path(self.mlp(self.norm2(q)))
+            return self.dge.decompress(q)
         require_cuda(x)
         x = x.contiguous()
         B, N, C = x.shape
@@ -196,7 +232,7 @@ class PyramidVisionTransformer(nn.Module):
         """images [B,3,S,S] on the device -> logits fp32 [B,num_classes] (``pvt_dge.py:295-337``,
         classification path at the training resolution)."""
         if self.training:
-            raise NotImplementedError("vtpack_b200 implements the eval-mode forward only")
+            raise NotImplementedError("training mode is mirrored for the blocks, not for the pyramid wrapper")
         if self.num_classes <= 0:
             raise NotImplementedError("the feature-pyramid outputs (num_classes = 0) are not mirrored")
         require_cuda(x)
