@@ -177,6 +177,26 @@ int vtp_batched_sparse_gemm(const void* a, const void* b, void* out, int dtype, 
                             int out_cols, void* stream);
 
 /*
+ * Bilinear-sampling attention of the deformable PVT (vtpack/models/standard/dpvt.py:92-115).
+ *   input [B,H,W,C] feature map; grid [B,G,P,2] sampling points in pixel coordinates (x, y);
+ *   a sample is the bilinear interpolation of the map at the point, zero outside the map.
+ *   mode 0 ("point"):   weight [B,G,P], out [B,G,C] = sum_p weight * sample;
+ *   mode 1 ("channel"): weight [B,G,C], out [B,G,P] = sum_c weight * sample.
+ * All tensors dense and of the one dtype.  The backward call writes grad_input [B,H,W,C] (cleared
+ * on the stream first, then accumulated with atomics), grad_grid [B,G,P,2] and grad_weight (shape of
+ * weight); it needs C <= 256.
+ * Replace bilinear_attention_{pointwise,channelwise}_{forward,backward}
+ * (vtpack/layers/csrc/bilinear_attention/bilinear_attention.cu:364-536, kernels :88-362).
+ */
+int vtp_bilinear_attention_forward(const void* input, const void* grid, const void* weight, void* out,
+                                   int dtype, int mode, int B, int H, int W, int C, int G, int P,
+                                   void* stream);
+int vtp_bilinear_attention_backward(const void* grad_out, const void* input, const void* grid,
+                                    const void* weight, void* grad_input, void* grad_grid,
+                                    void* grad_weight, int dtype, int mode, int B, int H, int W, int C,
+                                    int G, int P, void* stream);
+
+/*
  * LayerNorm over the last axis.  Row r of the input starts at x + r*in_row_stride
  * elements; output rows are dense.  rows_dev (device int32) overrides rows_max when set.
  * Replaces nn.LayerNorm norm2 / norm (vtpack/models/dge/deit_dge.py:128, :277).

@@ -8,7 +8,8 @@ not installed, so two stand-ins are placed in ``sys.modules`` before the
 reference is imported from its checkout:
 
   * ``vtpack._C``: the four functions the eval path calls and the ragged product of the
-    training path (``vtpack/layers/csrc/vision.cpp:9-29``), backed by ``oracle/dge_oracle.py``;
+    training path (``vtpack/layers/csrc/vision.cpp:9-29``), backed by ``oracle/dge_oracle.py``, and the
+    four bilinear-attention functions, backed by ``oracle/bilinear_oracle.py``;
   * ``timm.models.{layers,registry,vision_transformer}``: the handful of names
     ``vtpack/models/dge/deit_dge.py:9-11`` imports.  ``PatchEmbed`` is the
     conv(kernel = stride = patch) + flatten + transpose the reference's own
@@ -28,7 +29,7 @@ import types
 import torch
 from torch import nn
 
-from . import dge_oracle
+from . import bilinear_oracle, dge_oracle
 
 # a checkout of the reference: $VTPACK_REFERENCE_ROOT, else a directory "reference" beside this repository
 REFERENCE_ROOT = os.environ.get("VTPACK_REFERENCE_ROOT") or os.path.join(
@@ -100,6 +101,9 @@ def install():
     c.grained_sample_decompress = dge_oracle.grained_sample_decompress
     c.batched_sparse_attention_forward = dge_oracle.batched_sparse_attention_forward
     c.batched_sparse_gemm_forward = dge_oracle.batched_sparse_gemm_forward
+    for name in ("bilinear_attention_pointwise_forward", "bilinear_attention_pointwise_backward",
+                 "bilinear_attention_channelwise_forward", "bilinear_attention_channelwise_backward"):
+        setattr(c, name, getattr(bilinear_oracle, name))
     for name in ("batched_sparse_gemm_v2_forward", "grained_sample_index_to_patch_dense"):
         setattr(c, name, _not_on_eval_path)
     sys.modules["vtpack._C"] = c

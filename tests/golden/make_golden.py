@@ -29,6 +29,10 @@ Fixtures
   train_pvt_block_fp32.npz  one PVT+DGE block (dim 32, 1 head, 16x16 grid, spatial reduction 2) in
                         training mode with sparse_train on, fp32, B=2; Gumbel noise seed 23 injected;
                         output, input gradient, parameter gradients for sum(out * g), g seed 24.
+  bilinear_attention_fp32.npz  the reference's bilinear_attention autograd function
+                        (vtpack/layers/bilinear_attention.py) in both modes on B=2, 9x11 map, C=40,
+                        G=23 queries, P=5 points reaching two pixels outside the map: output and the
+                        three gradients.
 Inputs are regenerated from the seeds by the tests; each fixture carries a
 float64 sum of its inputs so RNG drift is detected rather than misread as a
 parity failure.
@@ -42,6 +46,7 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 
+from oracle import bilinear_oracle as BO  # noqa: E402
 from oracle import dge_oracle as O  # noqa: E402
 from oracle import ref_shim  # noqa: E402
 
@@ -272,6 +277,22 @@ def train_pvt_block_fixture():
     print("train_pvt_block_fp32.npz", out["lengths"], len(out), "arrays")
 
 
+def bilinear_fixture():
+    import importlib
+    ref_shim.install()
+    ba = importlib.import_module("vtpack.layers.bilinear_attention")
+    out = {}
+    for mode, seed in BO.GOLDEN_SEEDS.items():
+        inp, grid, weight, grad_out = BO.make_bilinear_inputs(seed=seed, mode=mode, **BO.GOLDEN_CASE)
+        inp.requires_grad_(True), grid.requires_grad_(True), weight.requires_grad_(True)
+        y = ba.bilinear_attention(inp, grid, weight, mode)
+        gi, gg, gw = torch.autograd.grad(y, (inp, grid, weight), grad_out)
+        out.update({f"{mode}_out": y.detach().numpy(), f"{mode}_grad_input": gi.numpy(),
+                    f"{mode}_grad_grid": gg.numpy(), f"{mode}_grad_weight": gw.numpy()})
+    np.savez_compressed(os.path.join(HERE, "bilinear_attention_fp32.npz"), **out)
+    print("bilinear_attention_fp32.npz", {k: v.shape for k, v in out.items()})
+
+
 if __name__ == "__main__":
     layer_fixture()
     model_fixture()
@@ -280,3 +301,4 @@ if __name__ == "__main__":
     train_ops_fixture()
     train_block_fixture()
     train_pvt_block_fixture()
+    bilinear_fixture()

@@ -303,3 +303,29 @@ def test_train_block_fixture_matches_reference(golden_dir):
     assert np.array_equal(np.asarray(blk.dge.states["batches"]), z["sparse_lengths"])
     assert torch.allclose(y.detach(), torch.from_numpy(z["sparse_out"]), rtol=1e-5, atol=1e-6)
     assert torch.allclose(x.grad, torch.from_numpy(z["sparse_grad_x"]), rtol=1e-4, atol=1e-6)
+
+
+# ------------------------------------------------------------------ bilinear-sampling attention
+
+@pytest.mark.parametrize("mode", ["point", "channel"])
+def test_bilinear_attention_golden_and_autograd(golden_dir, mode):
+    """The restated forward reproduces the fixture (made by the reference's autograd function over the
+    stand-in), and the restated backward formulas equal torch autograd of the forward in float64 —
+    two independent derivations of the three gradients."""
+    from oracle import bilinear_oracle as BO
+    z = _load(golden_dir, "bilinear_attention_fp32.npz")
+    fwd = getattr(BO, f"bilinear_attention_{mode}wise_forward")
+    bwd = getattr(BO, f"bilinear_attention_{mode}wise_backward")
+    inp, grid, weight, grad_out = BO.make_bilinear_inputs(seed=BO.GOLDEN_SEEDS[mode], mode=mode, **BO.GOLDEN_CASE)
+    assert torch.allclose(fwd(inp, grid, weight), torch.from_numpy(z[f"{mode}_out"]), rtol=1e-6, atol=1e-6)
+    gi, gg, gw = bwd(grad_out, inp, grid, weight)
+    for name, t in (("grad_input", gi), ("grad_grid", gg), ("grad_weight", gw)):
+        assert torch.allclose(t, torch.from_numpy(z[f"{mode}_{name}"]), rtol=1e-5, atol=1e-5), name
+    a, g, w = (t.double().requires_grad_(True) for t in (inp, grid, weight))
+    auto = torch.autograd.grad(fwd(a, g, w), (a, g, w), grad_out.double())
+    for t, ref in zip(bwd(grad_out.double(), a.detach(), g.detach(), w.detach()), auto):
+        assert torch.allclose(t, ref, rtol=1e-10, atol=1e-10)
+    # taps outside the map read zero: a point more than a pixel outside contributes nothing
+    far = grid.clone()
+    far[..., 0] = -1.5
+    assert not fwd(inp, far, weight).any()

@@ -60,6 +60,11 @@ PROTOTYPES = {
     "vtp_batched_sparse_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_int, c_ll,
                                         c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_int,
                                         c_void_p]),
+    "vtp_bilinear_attention_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                               c_int, c_int, c_int, c_int, c_void_p]),
+    "vtp_bilinear_attention_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_void_p]),
     "vtp_layernorm": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_float,
                               c_void_p, c_void_p]),
     "vtp_token_im2col": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),

@@ -1,0 +1,229 @@
+// Bilinear-sampling attention of the deformable PVT (vtpack/models/standard/dpvt.py:92-115):
+// every query position g of a feature map [B, H, W, C] looks at P sampling points given in pixel
+// coordinates (x, y), reads the map there by bilinear interpolation (zero outside the map) and
+//   "point"   mode: out[b,g,c] = sum_p weight[b,g,p] * sample(b, p, c)         weight [B,G,P]
+//   "channel" mode: out[b,g,p] = sum_c weight[b,g,c] * sample(b, p, c)         weight [B,G,C]
+// Replaces bilinear_attention_{pointwise,channelwise}_{forward,backward}
+// (vtpack/layers/csrc/bilinear_attention/bilinear_attention.cu:88-132, :134-232, :234-268, :270-362).
+//
+// The reference runs one thread per (b, g) that walks the channels serially, so neighbouring
+// threads read addresses C elements apart.  Here one warp owns a (b, g) instance and its lanes walk
+// the channels: every corner read, every atomic of the input gradient and every output row is a
+// run of consecutive addresses.  All four kernels are bound by those gathers (4 corner rows per
+// point), not by arithmetic.
+#include "common.cuh"
+
+namespace vtp {
+
+constexpr int BA_WARPS = 8;           // instances per 256-thread block
+constexpr int BA_MAXCH = 8;           // channel-mode backward keeps C / 32 weight gradients per lane
+
+struct Corner {
+    int x0, y0;
+    float w_lt, w_rt, w_lb, w_rb, tx, ty;
+    bool in_lt, in_rt, in_lb, in_rb;
+};
+
+__device__ __forceinline__ Corner corners_of(float x, float y, int H, int W) {
+    Corner c;
+    const float fx = floorf(x), fy = floorf(y);
+    c.x0 = (int)fx;
+    c.y0 = (int)fy;
+    c.tx = x - fx;
+    c.ty = y - fy;
+    c.w_lt = (1.f - c.tx) * (1.f - c.ty);
+    c.w_rt = c.tx * (1.f - c.ty);
+    c.w_lb = (1.f - c.tx) * c.ty;
+    c.w_rb = c.tx * c.ty;
+    const bool xl = c.x0 >= 0 && c.x0 < W, xr = c.x0 + 1 >= 0 && c.x0 + 1 < W;
+    const bool yt = c.y0 >= 0 && c.y0 < H, yb = c.y0 + 1 >= 0 && c.y0 + 1 < H;
+    c.in_lt = xl && yt; c.in_rt = xr && yt; c.in_lb = xl && yb; c.in_rb = xr && yb;
+    return c;
+}
+
+// a coordinate far outside the map (or not finite) touches no pixel; clamp it so the int casts stay defined
+__device__ __forceinline__ float sane(float v, int extent) {
+    return (v > -4.f && v < (float)extent + 4.f) ? v : -4.f;
+}
+
+template <typename T>
+struct Taps {
+    float lt, rt, lb, rb;
+    __device__ __forceinline__ void load(const T* __restrict__ img, const Corner& k, int W, int C, int c) {
+        const size_t o = ((size_t)k.y0 * W + k.x0) * C + c;   // only dereferenced where in-bounds
+        lt = k.in_lt ? to_f32(img[o]) : 0.f;
+        rt = k.in_rt ? to_f32(img[o + C]) : 0.f;
+        lb = k.in_lb ? to_f32(img[o + (size_t)W * C]) : 0.f;
+        rb = k.in_rb ? to_f32(img[o + (size_t)W * C + C]) : 0.f;
+    }
+    __device__ __forceinline__ float value(const Corner& k) const {
+        return k.w_lt * lt + k.w_rt * rt + k.w_lb * lb + k.w_rb * rb;
+    }
+};
+
+__device__ __forceinline__ void atomic_add(float* p, float v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add(bf16* p, float v) { atomicAdd(p, __float2bfloat16_rn(v)); }
+
+template <typename T>
+__device__ __forceinline__ void scatter(T* __restrict__ gimg, const Corner& k, int W, int C, int c, float v) {
+    const size_t o = ((size_t)k.y0 * W + k.x0) * C + c;
+    if (k.in_lt) atomic_add(gimg + o, v * k.w_lt);
+    if (k.in_rt) atomic_add(gimg + o + C, v * k.w_rt);
+    if (k.in_lb) atomic_add(gimg + o + (size_t)W * C, v * k.w_lb);
+    if (k.in_rb) atomic_add(gimg + o + (size_t)W * C + C, v * k.w_rb);
+}
+
+// ---------------------------------------------------------------------------- forward
+template <typename T, bool POINT>
+__global__ void __launch_bounds__(BA_WARPS * 32)
+bilinear_attention_fwd_kernel(const T* __restrict__ input, const T* __restrict__ grid, const T* __restrict__ weight,
+                              T* __restrict__ out, int B, int H, int W, int C, int G, int P) {
+    const int lane = threadIdx.x & 31;
+    const long long n_inst = (long long)B * G;
+    for (long long inst = (long long)blockIdx.x * BA_WARPS + (threadIdx.x >> 5); inst < n_inst;
+         inst += (long long)gridDim.x * BA_WARPS) {
+        const int b = (int)(inst / G);
+        const T* img = input + (size_t)b * H * W * C;
+        const T* pts = grid + (size_t)inst * P * 2;
+        if (POINT) {
+            const T* wt = weight + (size_t)inst * P;
+            for (int c = lane; c < C; c += 32) {
+                float acc = 0.f;
+                for (int p = 0; p < P; ++p) {
+                    const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), H, W);
+                    Taps<T> t;
+                    t.load(img, k, W, C, c);
+                    acc = fmaf(t.value(k), to_f32(wt[p]), acc);
+                }
+                out[(size_t)inst * C + c] = from_f32<T>(acc);
+            }
+        } else {
+            const T* wt = weight + (size_t)inst * C;
+            for (int p = 0; p < P; ++p) {
+                const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), H, W);
+                float acc = 0.f;
+                for (int c = lane; c < C; c += 32) {
+                    Taps<T> t;
+                    t.load(img, k, W, C, c);
+                    acc = fmaf(t.value(k), to_f32(wt[c]), acc);
+                }
+                acc = warp_sum(acc);
+                if (lane == 0) out[(size_t)inst * P + p] = from_f32<T>(acc);
+            }
+        }
+    }
+}
+
+// --------------------------------------------------------------------------- backward
+// grad_input must be zero on entry (the host wrapper clears it on the same stream).
+template <typename T, bool POINT>
+__global__ void __launch_bounds__(BA_WARPS * 32)
+bilinear_attention_bwd_kernel(const T* __restrict__ grad_out, const T* __restrict__ input, const T* __restrict__ grid,
+                              const T* __restrict__ weight, T* __restrict__ grad_input, T* __restrict__ grad_grid,
+                              T* __restrict__ grad_weight, int B, int H, int W, int C, int G, int P) {
+    const int lane = threadIdx.x & 31;
+    const long long n_inst = (long long)B * G;
+    for (long long inst = (long long)blockIdx.x * BA_WARPS + (threadIdx.x >> 5); inst < n_inst;
+         inst += (long long)gridDim.x * BA_WARPS) {
+        const int b = (int)(inst / G);
+        const T* img = input + (size_t)b * H * W * C;
+        T* gimg = grad_input + (size_t)b * H * W * C;
+        const T* pts = grid + (size_t)inst * P * 2;
+        float gw_c[BA_MAXCH];                              // channel mode: this lane's weight gradients
+#pragma unroll
+        for (int j = 0; j < BA_MAXCH; ++j) gw_c[j] = 0.f;
+        for (int p = 0; p < P; ++p) {
+            const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), H, W);
+            const float wp = POINT ? to_f32(weight[(size_t)inst * P + p]) : 0.f;
+            const float gp = POINT ? 0.f : to_f32(grad_out[(size_t)inst * P + p]);
+            float gix = 0.f, giy = 0.f, giw = 0.f;
+#pragma unroll
+            for (int j = 0; j < BA_MAXCH; ++j) {
+                const int c = lane + 32 * j;
+                if (c < C) {
+                    // g = d(loss) / d(sample(b, p, c))
+                    const float g = POINT ? to_f32(grad_out[(size_t)inst * C + c]) * wp
+                                          : gp * to_f32(weight[(size_t)inst * C + c]);
+                    scatter<T>(gimg, k, W, C, c, g);
+                    Taps<T> t;
+                    t.load(img, k, W, C, c);
+                    // d(sample)/dx and d(sample)/dy of the bilinear form
+                    gix += g * ((t.rt - t.lt) * (1.f - k.ty) + (t.rb - t.lb) * k.ty);
+                    giy += g * ((t.lb - t.lt) * (1.f - k.tx) + (t.rb - t.rt) * k.tx);
+                    if (POINT) giw += t.value(k) * to_f32(grad_out[(size_t)inst * C + c]);
+                    else gw_c[j] += t.value(k) * gp;
+                }
+            }
+            gix = warp_sum(gix);
+            giy = warp_sum(giy);
+            if (POINT) giw = warp_sum(giw);
+            if (lane == 0) {
+                grad_grid[((size_t)inst * P + p) * 2] = from_f32<T>(gix);
+                grad_grid[((size_t)inst * P + p) * 2 + 1] = from_f32<T>(giy);
+                if (POINT) grad_weight[(size_t)inst * P + p] = from_f32<T>(giw);
+            }
+        }
+        if (!POINT) {
+#pragma unroll
+            for (int j = 0; j < BA_MAXCH; ++j) {
+                const int c = lane + 32 * j;
+                if (c < C) grad_weight[(size_t)inst * C + c] = from_f32<T>(gw_c[j]);
+            }
+        }
+    }
+}
+
+static int ba_grid(long long instances) {
+    const long long want = (instances + BA_WARPS - 1) / BA_WARPS;
+    const long long cap = (long long)sm_count() * 16;
+    return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+static int ba_check(const char* what, int dtype, int mode, int B, int H, int W, int C, int G, int P) {
+    VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "%s: dtype %d", what, dtype);
+    VTP_REQUIRE(mode == 0 || mode == 1, VTP_ERR_SHAPE, "%s: mode %d (0 = point, 1 = channel)", what, mode);
+    VTP_REQUIRE(B > 0 && H > 0 && W > 0 && C > 0 && G > 0 && P > 0, VTP_ERR_SHAPE, "%s: bad shape", what);
+    return VTP_OK;
+}
+
+}  // namespace vtp
+
+using namespace vtp;
+
+extern "C" int vtp_bilinear_attention_forward(const void* input, const void* grid, const void* weight, void* out,
+                                              int dtype, int mode, int B, int H, int W, int C, int G, int P,
+                                              void* stream) {
+    VTP_REQUIRE(input && grid && weight && out, VTP_ERR_NULL, "bilinear_attention: null pointer");
+    if (int rc = ba_check("bilinear_attention", dtype, mode, B, H, W, C, G, P)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int blocks = ba_grid((long long)B * G);
+#define VTP_BA_FWD(T, PT)                                                                                    \
+    bilinear_attention_fwd_kernel<T, PT><<<blocks, BA_WARPS * 32, 0, st>>>(                                  \
+        (const T*)input, (const T*)grid, (const T*)weight, (T*)out, B, H, W, C, G, P)
+    if (dtype == VTP_F32) { if (mode == 0) VTP_BA_FWD(float, true); else VTP_BA_FWD(float, false); }
+    else { if (mode == 0) VTP_BA_FWD(bf16, true); else VTP_BA_FWD(bf16, false); }
+#undef VTP_BA_FWD
+    return check_launch("bilinear_attention_forward");
+}
+
+extern "C" int vtp_bilinear_attention_backward(const void* grad_out, const void* input, const void* grid,
+                                               const void* weight, void* grad_input, void* grad_grid,
+                                               void* grad_weight, int dtype, int mode, int B, int H, int W, int C,
+                                               int G, int P, void* stream) {
+    VTP_REQUIRE(grad_out && input && grid && weight && grad_input && grad_grid && grad_weight, VTP_ERR_NULL,
+                "bilinear_attention_backward: null pointer");
+    if (int rc = ba_check("bilinear_attention_backward", dtype, mode, B, H, W, C, G, P)) return rc;
+    VTP_REQUIRE(C <= 32 * BA_MAXCH, VTP_ERR_SHAPE, "bilinear_attention_backward: C=%d above %d", C, 32 * BA_MAXCH);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemsetAsync(grad_input, 0, (size_t)B * H * W * C * elem_size(dtype), st);
+    if (e != cudaSuccess) return fail((int)e, "bilinear_attention_backward: clearing grad_input: %s", cudaGetErrorString(e));
+    const int blocks = ba_grid((long long)B * G);
+#define VTP_BA_BWD(T, PT)                                                                                    \
+    bilinear_attention_bwd_kernel<T, PT><<<blocks, BA_WARPS * 32, 0, st>>>(                                  \
+        (const T*)grad_out, (const T*)input, (const T*)grid, (const T*)weight, (T*)grad_input, (T*)grad_grid, \
+        (T*)grad_weight, B, H, W, C, G, P)
+    if (dtype == VTP_F32) { if (mode == 0) VTP_BA_BWD(float, true); else VTP_BA_BWD(float, false); }
+    else { if (mode == 0) VTP_BA_BWD(bf16, true); else VTP_BA_BWD(bf16, false); }
+#undef VTP_BA_BWD
+    return check_launch("bilinear_attention_backward");
+}
