@@ -445,6 +445,94 @@ def pvt_sweep(args):
                                          "cpu_oracle_images_per_s": round(cpu_rate, 1)}}), flush=True)
 
 
+def _time_us(fn, iters=20, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def train_ops_sweep(args):
+    """The native ops of the training path and the bilinear-sampling ops at model shapes, bf16 unless
+    noted: microseconds per call (CUDA events, 20 calls back to back, operands larger than L2 or
+    rewritten every call), the algorithmic bytes or FLOPs of a call against the measured peaks, and
+    beside the ragged products the reference's formulation (one library bmm per image and a
+    concatenation, batched_sparse_gemm.cu:150-196) on the same GPU."""
+    from vtpack_b200 import _lib, layers
+    from vtpack_b200.runtime import dtype_code, ptr, stream_ptr
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pk, pk_kind = peaks()
+    gen = torch.Generator(dev).manual_seed(1)
+    B, G, C, heads = args.batch, 16, 384, 6
+    N, d = G * G + 1, C // heads
+    rows = []
+    # ---- token movers and their gradients (DeiT-S, batch 256, random grains)
+    indices = torch.randint(0, 3, (B, G // 4, G // 4), device=dev, generator=gen)
+    patches, lengths = layers.grained_sample_index_to_patch(indices, torch.tensor([4, 2, 1]), 4, 1)
+    L = patches.shape[0]
+    x = torch.randn(B, N, C, device=dev, generator=gen).bfloat16()
+    q = torch.randn(L, C, device=dev, generator=gen).bfloat16()
+    lib, st, p32 = _lib.lib(), stream_ptr(dev), patches._vtp_i32
+    gx, gq = torch.empty_like(x), torch.empty_like(q)
+    mover = lambda fn, src, dst: _lib.check(fn(ptr(src), dtype_code(src.dtype), B, N, C, G, 1, ptr(p32), None, L,   # noqa: E731
+                                               ptr(dst), st))
+    for name, fn, src, dst in (("pool_grad", lib.vtp_pool_grad, q, gx), ("unpool_grad", lib.vtp_unpool_grad, x, gq)):
+        us = _time_us(lambda: mover(fn, src, dst))
+        nbytes = (B * N + L) * C * 2
+        rows.append({"op": name, "shape": f"B={B} N={N} C={C} L={L}", "us": round(us, 1),
+                     "GB/s": round(nbytes / us / 1e3), "frac_of_hbm_peak": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)})
+    # ---- ragged products of the training-mode attention: S = Q K^T and O = P V
+    qh = torch.randn(heads, L, d, device=dev, generator=gen).bfloat16()
+    kh = torch.randn(heads, B * N, d, device=dev, generator=gen).bfloat16()
+    kv_len = torch.full([B], N, dtype=torch.long)
+    prob = torch.randn(heads, L, N, device=dev, generator=gen).bfloat16()
+    off = torch.zeros(B + 1, dtype=torch.long)
+    off[1:] = torch.cumsum(lengths, 0)
+    off = off.tolist()
+
+    def per_image(a, b, tb):
+        outs = []
+        for i in range(B):
+            bi = b[:, i * N:(i + 1) * N]
+            outs.append(torch.bmm(a[:, off[i]:off[i + 1]], bi.transpose(-1, -2) if tb else bi))
+        return torch.cat(outs, dim=1)
+
+    for name, a, tb in (("ragged Q K^T", qh, True), ("ragged P V", prob, False)):
+        us = _time_us(lambda: layers.batched_sparse_gemm(a, kh, lengths, kv_len, False, tb), iters=10)
+        us_loop = _time_us(lambda: per_image(a, kh, tb), iters=3, warm=1)
+        flops = 2.0 * heads * L * N * d
+        rows.append({"op": name, "shape": f"heads={heads} L={L} keys={N} d={d}", "us": round(us, 1),
+                     "tflops": round(flops / us / 1e6, 2), "per_image_bmm_loop_us": round(us_loop, 1)})
+    # ---- bilinear-sampling attention at a deformable-PVT stage: 64 x 64 map, 64 channels per head
+    Bb, H, P = max(1, B // 8), 64, 9
+    for mode in ("point", "channel"):
+        inp = torch.randn(Bb, H, H, 64, device=dev, generator=gen).bfloat16()
+        # one query per pixel looking at P points within a few pixels of itself, as the model's offsets do
+        ys, xs = torch.meshgrid(torch.arange(H, device=dev), torch.arange(H, device=dev), indexing="ij")
+        centre = torch.stack([xs, ys], dim=-1).reshape(1, H * H, 1, 2).float()
+        grid = (centre + 3.0 * torch.randn(Bb, H * H, P, 2, device=dev, generator=gen)).bfloat16()
+        weight = torch.randn(Bb, H * H, P if mode == "point" else 64, device=dev, generator=gen).bfloat16()
+        grad_out = torch.randn(Bb, H * H, 64 if mode == "point" else P, device=dev, generator=gen).bfloat16()
+        a, g_, w = (t.requires_grad_(True) for t in (inp, grid, weight))
+        us_f = _time_us(lambda: layers.bilinear_attention(inp, grid, weight, mode))
+        y = layers.bilinear_attention(a, g_, w, mode)
+        us_b = _time_us(lambda: torch.autograd.grad(y, (a, g_, w), grad_out, retain_graph=True), iters=10)
+        taps = Bb * H * H * P * 4 * 64 * 2          # bytes the four corner rows of every point hold
+        rows.append({"op": f"bilinear_attention {mode}", "shape": f"B*heads={Bb} map=64x64 C=64 P={P}",
+                     "forward_us": round(us_f, 1), "backward_us": round(us_b, 1),
+                     "forward_tap_GB/s": round(taps / us_f / 1e3)})
+    assert _lib.device_status() == 0
+    print(json.dumps({"train_ops_sweep": rows, "dtype": "bf16", "hbm_peak_gbs": pk["hbm_gbs"],
+                      "peaks": pk_kind}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -467,7 +555,12 @@ def main():
                     help="time one DGE layer over gate skew against the dense block and exit")
     ap.add_argument("--pvt-sweep", action="store_true",
                     help="time one PVT+DGE block per stage shape (256 px) and exit")
+    ap.add_argument("--train-ops-sweep", action="store_true",
+                    help="time the training-path and bilinear-sampling ops at model shapes and exit")
     args = ap.parse_args()
+    if args.train_ops_sweep:
+        train_ops_sweep(args)
+        return
     if args.profile:
         profile_case(args.profile)
         return

@@ -9,8 +9,11 @@
 // The reference runs one thread per (b, g) that walks the channels serially, so neighbouring
 // threads read addresses C elements apart.  Here one warp owns a (b, g) instance and its lanes walk
 // the channels: every corner read, every atomic of the input gradient and every output row is a
-// run of consecutive addresses.  All four kernels are bound by those gathers (4 corner rows per
-// point), not by arithmetic.
+// run of consecutive addresses; with an even C a lane takes two neighbouring channels, which halves
+// the loads and (packed float2 / bf16x2 atomics) the atomic traffic of the input gradient.  All four
+// kernels are bound by those gathers (4 corner rows per point), not by arithmetic.
+#include <initializer_list>
+
 #include "common.cuh"
 
 namespace vtp {
@@ -46,35 +49,80 @@ __device__ __forceinline__ float sane(float v, int extent) {
     return (v > -4.f && v < (float)extent + 4.f) ? v : -4.f;
 }
 
-template <typename T>
-struct Taps {
-    float lt, rt, lb, rb;
-    __device__ __forceinline__ void load(const T* __restrict__ img, const Corner& k, int W, int C, int c) {
-        const size_t o = ((size_t)k.y0 * W + k.x0) * C + c;   // only dereferenced where in-bounds
-        lt = k.in_lt ? to_f32(img[o]) : 0.f;
-        rt = k.in_rt ? to_f32(img[o + C]) : 0.f;
-        lb = k.in_lb ? to_f32(img[o + (size_t)W * C]) : 0.f;
-        rb = k.in_rb ? to_f32(img[o + (size_t)W * C + C]) : 0.f;
+// V consecutive channels per lane (2 when C is even: half the loads and half the atomics)
+template <typename T, int V> struct Pack;
+template <> struct Pack<float, 1> {
+    static __device__ __forceinline__ void load(const float* p, float (&f)[1]) { f[0] = *p; }
+    static __device__ __forceinline__ void store(float* p, const float (&f)[1]) { *p = f[0]; }
+    static __device__ __forceinline__ void atomic_add(float* p, const float (&f)[1]) { atomicAdd(p, f[0]); }
+};
+template <> struct Pack<float, 2> {
+    static __device__ __forceinline__ void load(const float* p, float (&f)[2]) {
+        const float2 v = *reinterpret_cast<const float2*>(p);
+        f[0] = v.x; f[1] = v.y;
     }
-    __device__ __forceinline__ float value(const Corner& k) const {
-        return k.w_lt * lt + k.w_rt * rt + k.w_lb * lb + k.w_rb * rb;
+    static __device__ __forceinline__ void store(float* p, const float (&f)[2]) {
+        *reinterpret_cast<float2*>(p) = make_float2(f[0], f[1]);
+    }
+    static __device__ __forceinline__ void atomic_add(float* p, const float (&f)[2]) {
+        atomicAdd(reinterpret_cast<float2*>(p), make_float2(f[0], f[1]));
+    }
+};
+template <> struct Pack<bf16, 1> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&f)[1]) { f[0] = __bfloat162float(*p); }
+    static __device__ __forceinline__ void store(bf16* p, const float (&f)[1]) { *p = __float2bfloat16_rn(f[0]); }
+    static __device__ __forceinline__ void atomic_add(bf16* p, const float (&f)[1]) {
+        atomicAdd(p, __float2bfloat16_rn(f[0]));
+    }
+};
+template <> struct Pack<bf16, 2> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&f)[2]) {
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+        f[0] = v.x; f[1] = v.y;
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&f)[2]) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(f[0], f[1]);
+    }
+    static __device__ __forceinline__ void atomic_add(bf16* p, const float (&f)[2]) {
+        atomicAdd(reinterpret_cast<__nv_bfloat162*>(p), __floats2bfloat162_rn(f[0], f[1]));
     }
 };
 
-__device__ __forceinline__ void atomic_add(float* p, float v) { atomicAdd(p, v); }
-__device__ __forceinline__ void atomic_add(bf16* p, float v) { atomicAdd(p, __float2bfloat16_rn(v)); }
+template <typename T, int V>
+struct Taps {
+    float lt[V], rt[V], lb[V], rb[V];
+    __device__ __forceinline__ void load(const T* __restrict__ img, const Corner& k, int W, int C, int c) {
+        const size_t o = ((size_t)k.y0 * W + k.x0) * C + c;   // only dereferenced where in-bounds
+#pragma unroll
+        for (int v = 0; v < V; ++v) lt[v] = rt[v] = lb[v] = rb[v] = 0.f;
+        if (k.in_lt) Pack<T, V>::load(img + o, lt);
+        if (k.in_rt) Pack<T, V>::load(img + o + C, rt);
+        if (k.in_lb) Pack<T, V>::load(img + o + (size_t)W * C, lb);
+        if (k.in_rb) Pack<T, V>::load(img + o + (size_t)W * C + C, rb);
+    }
+    __device__ __forceinline__ float value(const Corner& k, int v) const {
+        return k.w_lt * lt[v] + k.w_rt * rt[v] + k.w_lb * lb[v] + k.w_rb * rb[v];
+    }
+};
 
-template <typename T>
-__device__ __forceinline__ void scatter(T* __restrict__ gimg, const Corner& k, int W, int C, int c, float v) {
+template <typename T, int V>
+__device__ __forceinline__ void scatter(T* __restrict__ gimg, const Corner& k, int W, int C, int c, const float (&g)[V]) {
     const size_t o = ((size_t)k.y0 * W + k.x0) * C + c;
-    if (k.in_lt) atomic_add(gimg + o, v * k.w_lt);
-    if (k.in_rt) atomic_add(gimg + o + C, v * k.w_rt);
-    if (k.in_lb) atomic_add(gimg + o + (size_t)W * C, v * k.w_lb);
-    if (k.in_rb) atomic_add(gimg + o + (size_t)W * C + C, v * k.w_rb);
+    float t[V];
+#define VTP_BA_SCATTER(IN, OFF, WT)                              \
+    if (IN) {                                                    \
+        _Pragma("unroll") for (int v = 0; v < V; ++v) t[v] = g[v] * (WT); \
+        Pack<T, V>::atomic_add(gimg + o + (OFF), t);             \
+    }
+    VTP_BA_SCATTER(k.in_lt, 0, k.w_lt)
+    VTP_BA_SCATTER(k.in_rt, C, k.w_rt)
+    VTP_BA_SCATTER(k.in_lb, (size_t)W * C, k.w_lb)
+    VTP_BA_SCATTER(k.in_rb, (size_t)W * C + C, k.w_rb)
+#undef VTP_BA_SCATTER
 }
 
 // ---------------------------------------------------------------------------- forward
-template <typename T, bool POINT>
+template <typename T, bool POINT, int V>
 __global__ void __launch_bounds__(BA_WARPS * 32)
 bilinear_attention_fwd_kernel(const T* __restrict__ input, const T* __restrict__ grid, const T* __restrict__ weight,
                               T* __restrict__ out, int B, int H, int W, int C, int G, int P) {
@@ -87,25 +135,32 @@ bilinear_attention_fwd_kernel(const T* __restrict__ input, const T* __restrict__
         const T* pts = grid + (size_t)inst * P * 2;
         if (POINT) {
             const T* wt = weight + (size_t)inst * P;
-            for (int c = lane; c < C; c += 32) {
-                float acc = 0.f;
+            for (int c = lane * V; c < C; c += 32 * V) {
+                float acc[V];
+#pragma unroll
+                for (int v = 0; v < V; ++v) acc[v] = 0.f;
                 for (int p = 0; p < P; ++p) {
                     const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), H, W);
-                    Taps<T> t;
+                    Taps<T, V> t;
                     t.load(img, k, W, C, c);
-                    acc = fmaf(t.value(k), to_f32(wt[p]), acc);
+                    const float wp = to_f32(wt[p]);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) acc[v] = fmaf(t.value(k, v), wp, acc[v]);
                 }
-                out[(size_t)inst * C + c] = from_f32<T>(acc);
+                Pack<T, V>::store(out + (size_t)inst * C + c, acc);
             }
         } else {
             const T* wt = weight + (size_t)inst * C;
             for (int p = 0; p < P; ++p) {
                 const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), H, W);
                 float acc = 0.f;
-                for (int c = lane; c < C; c += 32) {
-                    Taps<T> t;
+                for (int c = lane * V; c < C; c += 32 * V) {
+                    Taps<T, V> t;
                     t.load(img, k, W, C, c);
-                    acc = fmaf(t.value(k), to_f32(wt[c]), acc);
+                    float wc[V];
+                    Pack<T, V>::load(wt + c, wc);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) acc = fmaf(t.value(k, v), wc[v], acc);
                 }
                 acc = warp_sum(acc);
                 if (lane == 0) out[(size_t)inst * P + p] = from_f32<T>(acc);
@@ -116,11 +171,12 @@ bilinear_attention_fwd_kernel(const T* __restrict__ input, const T* __restrict__
 
 // --------------------------------------------------------------------------- backward
 // grad_input must be zero on entry (the host wrapper clears it on the same stream).
-template <typename T, bool POINT>
+template <typename T, bool POINT, int V>
 __global__ void __launch_bounds__(BA_WARPS * 32)
 bilinear_attention_bwd_kernel(const T* __restrict__ grad_out, const T* __restrict__ input, const T* __restrict__ grid,
                               const T* __restrict__ weight, T* __restrict__ grad_input, T* __restrict__ grad_grid,
                               T* __restrict__ grad_weight, int B, int H, int W, int C, int G, int P) {
+    constexpr int J = BA_MAXCH / V;                        // channel groups per lane
     const int lane = threadIdx.x & 31;
     const long long n_inst = (long long)B * G;
     for (long long inst = (long long)blockIdx.x * BA_WARPS + (threadIdx.x >> 5); inst < n_inst;
@@ -129,29 +185,39 @@ bilinear_attention_bwd_kernel(const T* __restrict__ grad_out, const T* __restric
         const T* img = input + (size_t)b * H * W * C;
         T* gimg = grad_input + (size_t)b * H * W * C;
         const T* pts = grid + (size_t)inst * P * 2;
-        float gw_c[BA_MAXCH];                              // channel mode: this lane's weight gradients
+        // per lane and channel group: the upstream gradient (point mode) or the weight (channel mode),
+        // read once, and in channel mode the weight gradient accumulated over the points
+        float up[J][V], gw_c[J][V];
 #pragma unroll
-        for (int j = 0; j < BA_MAXCH; ++j) gw_c[j] = 0.f;
+        for (int j = 0; j < J; ++j) {
+            const int c = (lane + 32 * j) * V;
+#pragma unroll
+            for (int v = 0; v < V; ++v) up[j][v] = gw_c[j][v] = 0.f;
+            if (c < C) Pack<T, V>::load((POINT ? grad_out : weight) + (size_t)inst * C + c, up[j]);
+        }
         for (int p = 0; p < P; ++p) {
             const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), H, W);
-            const float wp = POINT ? to_f32(weight[(size_t)inst * P + p]) : 0.f;
-            const float gp = POINT ? 0.f : to_f32(grad_out[(size_t)inst * P + p]);
+            // scale turning up[] into g = d(loss) / d(sample(b, p, c))
+            const float sc = POINT ? to_f32(weight[(size_t)inst * P + p]) : to_f32(grad_out[(size_t)inst * P + p]);
             float gix = 0.f, giy = 0.f, giw = 0.f;
 #pragma unroll
-            for (int j = 0; j < BA_MAXCH; ++j) {
-                const int c = lane + 32 * j;
+            for (int j = 0; j < J; ++j) {
+                const int c = (lane + 32 * j) * V;
                 if (c < C) {
-                    // g = d(loss) / d(sample(b, p, c))
-                    const float g = POINT ? to_f32(grad_out[(size_t)inst * C + c]) * wp
-                                          : gp * to_f32(weight[(size_t)inst * C + c]);
-                    scatter<T>(gimg, k, W, C, c, g);
-                    Taps<T> t;
+                    float g[V];
+#pragma unroll
+                    for (int v = 0; v < V; ++v) g[v] = up[j][v] * sc;
+                    scatter<T, V>(gimg, k, W, C, c, g);
+                    Taps<T, V> t;
                     t.load(img, k, W, C, c);
-                    // d(sample)/dx and d(sample)/dy of the bilinear form
-                    gix += g * ((t.rt - t.lt) * (1.f - k.ty) + (t.rb - t.lb) * k.ty);
-                    giy += g * ((t.lb - t.lt) * (1.f - k.tx) + (t.rb - t.rt) * k.tx);
-                    if (POINT) giw += t.value(k) * to_f32(grad_out[(size_t)inst * C + c]);
-                    else gw_c[j] += t.value(k) * gp;
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        // d(sample)/dx and d(sample)/dy of the bilinear form
+                        gix += g[v] * ((t.rt[v] - t.lt[v]) * (1.f - k.ty) + (t.rb[v] - t.lb[v]) * k.ty);
+                        giy += g[v] * ((t.lb[v] - t.lt[v]) * (1.f - k.tx) + (t.rb[v] - t.rt[v]) * k.tx);
+                        if (POINT) giw += t.value(k, v) * up[j][v];
+                        else gw_c[j][v] += t.value(k, v) * sc;
+                    }
                 }
             }
             gix = warp_sum(gix);
@@ -165,9 +231,9 @@ bilinear_attention_bwd_kernel(const T* __restrict__ grad_out, const T* __restric
         }
         if (!POINT) {
 #pragma unroll
-            for (int j = 0; j < BA_MAXCH; ++j) {
-                const int c = lane + 32 * j;
-                if (c < C) grad_weight[(size_t)inst * C + c] = from_f32<T>(gw_c[j]);
+            for (int j = 0; j < J; ++j) {
+                const int c = (lane + 32 * j) * V;
+                if (c < C) Pack<T, V>::store(grad_weight + (size_t)inst * C + c, gw_c[j]);
             }
         }
     }
@@ -186,6 +252,15 @@ static int ba_check(const char* what, int dtype, int mode, int B, int H, int W, 
     return VTP_OK;
 }
 
+// channel pairs need an even C and every channel-indexed pointer aligned to a pair
+static bool ba_pairs(int dtype, int C, std::initializer_list<const void*> ptrs) {
+    if (C % 2) return false;
+    const uintptr_t mask = 2 * elem_size(dtype) - 1;
+    for (const void* p : ptrs)
+        if (reinterpret_cast<uintptr_t>(p) & mask) return false;
+    return true;
+}
+
 }  // namespace vtp
 
 using namespace vtp;
@@ -197,9 +272,16 @@ extern "C" int vtp_bilinear_attention_forward(const void* input, const void* gri
     if (int rc = ba_check("bilinear_attention", dtype, mode, B, H, W, C, G, P)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int blocks = ba_grid((long long)B * G);
+    const bool pairs = ba_pairs(dtype, C, {input, weight, out});
 #define VTP_BA_FWD(T, PT)                                                                                    \
-    bilinear_attention_fwd_kernel<T, PT><<<blocks, BA_WARPS * 32, 0, st>>>(                                  \
-        (const T*)input, (const T*)grid, (const T*)weight, (T*)out, B, H, W, C, G, P)
+    do {                                                                                                     \
+        if (pairs)                                                                                           \
+            bilinear_attention_fwd_kernel<T, PT, 2><<<blocks, BA_WARPS * 32, 0, st>>>(                       \
+                (const T*)input, (const T*)grid, (const T*)weight, (T*)out, B, H, W, C, G, P);               \
+        else                                                                                                 \
+            bilinear_attention_fwd_kernel<T, PT, 1><<<blocks, BA_WARPS * 32, 0, st>>>(                       \
+                (const T*)input, (const T*)grid, (const T*)weight, (T*)out, B, H, W, C, G, P);               \
+    } while (0)
     if (dtype == VTP_F32) { if (mode == 0) VTP_BA_FWD(float, true); else VTP_BA_FWD(float, false); }
     else { if (mode == 0) VTP_BA_FWD(bf16, true); else VTP_BA_FWD(bf16, false); }
 #undef VTP_BA_FWD
@@ -218,10 +300,18 @@ extern "C" int vtp_bilinear_attention_backward(const void* grad_out, const void*
     cudaError_t e = cudaMemsetAsync(grad_input, 0, (size_t)B * H * W * C * elem_size(dtype), st);
     if (e != cudaSuccess) return fail((int)e, "bilinear_attention_backward: clearing grad_input: %s", cudaGetErrorString(e));
     const int blocks = ba_grid((long long)B * G);
+    const bool pairs = ba_pairs(dtype, C, {grad_out, input, weight, grad_input, grad_weight});
 #define VTP_BA_BWD(T, PT)                                                                                    \
-    bilinear_attention_bwd_kernel<T, PT><<<blocks, BA_WARPS * 32, 0, st>>>(                                  \
-        (const T*)grad_out, (const T*)input, (const T*)grid, (const T*)weight, (T*)grad_input, (T*)grad_grid, \
-        (T*)grad_weight, B, H, W, C, G, P)
+    do {                                                                                                     \
+        if (pairs)                                                                                           \
+            bilinear_attention_bwd_kernel<T, PT, 2><<<blocks, BA_WARPS * 32, 0, st>>>(                       \
+                (const T*)grad_out, (const T*)input, (const T*)grid, (const T*)weight, (T*)grad_input,       \
+                (T*)grad_grid, (T*)grad_weight, B, H, W, C, G, P);                                           \
+        else                                                                                                 \
+            bilinear_attention_bwd_kernel<T, PT, 1><<<blocks, BA_WARPS * 32, 0, st>>>(                       \
+                (const T*)grad_out, (const T*)input, (const T*)grid, (const T*)weight, (T*)grad_input,       \
+                (T*)grad_grid, (T*)grad_weight, B, H, W, C, G, P);                                           \
+    } while (0)
     if (dtype == VTP_F32) { if (mode == 0) VTP_BA_BWD(float, true); else VTP_BA_BWD(float, false); }
     else { if (mode == 0) VTP_BA_BWD(bf16, true); else VTP_BA_BWD(bf16, false); }
 #undef VTP_BA_BWD
