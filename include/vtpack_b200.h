@@ -197,6 +197,18 @@ int vtp_bilinear_attention_backward(const void* grad_out, const void* input, con
                                     int G, int P, void* stream);
 
 /*
+ * Point-mode bilinear attention over PACKED queries (the variable-length layout of the DGE path):
+ *   grid [L,P,2], weight [L,P], batches int64 [L] = the image each query samples, out [L,C].
+ * A query whose image index is outside [0, B) reads zeros.
+ * Replaces sparse_bilinear_attention_pointwise_forward
+ * (vtpack/layers/csrc/sparse_bilinear_attention/sparse_bilinear_attention.cu:88-171; forward only
+ * in the reference as well).
+ */
+int vtp_sparse_bilinear_attention_forward(const void* input, const void* grid, const void* weight,
+                                          const long long* batches, void* out, int dtype, int B, int H,
+                                          int W, int C, int L, int P, void* stream);
+
+/*
  * LayerNorm over the last axis.  Row r of the input starts at x + r*in_row_stride
  * elements; output rows are dense.  rows_dev (device int32) overrides rows_max when set.
  * Replaces nn.LayerNorm norm2 / norm (vtpack/models/dge/deit_dge.py:128, :277).

@@ -50,6 +50,17 @@ def bilinear_attention_channelwise_forward(inp, grid, weight):
     return (_sample(inp, grid) * weight[:, :, None, :]).sum(dim=-1)
 
 
+def sparse_bilinear_attention_pointwise_forward(inp, grid, weight, batches):
+    """Packed queries: grid [L,P,2], weight [L,P], batches int64 [L] -> [L,C]
+    (``vtpack/layers/csrc/sparse_bilinear_attention/sparse_bilinear_attention.cu:88-171``): query i
+    samples image batches[i]; otherwise the point-wise forward."""
+    out = torch.empty(grid.shape[0], inp.shape[3], dtype=inp.dtype)
+    for b in batches.unique().tolist():
+        sel = batches == b
+        out[sel] = bilinear_attention_pointwise_forward(inp[b:b + 1], grid[sel][None], weight[sel][None])[0]
+    return out
+
+
 def _backward(g_sample, inp, grid):
     """Common part of both backward kernels, given g_sample = d loss / d sample [B,G,P,C]: the
     scattered input gradient (``:183-194`` / ``:312-323``) and the point gradients (``:205-219`` /

@@ -92,3 +92,27 @@ def test_dpvt_attention_usage(op):
     want = BO.bilinear_attention_pointwise_forward(v.double(), grid.double(), weight.double())
     got = op(v.to(DEV).contiguous(), grid.to(DEV), weight.to(DEV), "point")
     assert got.shape == (B * heads, N, d) and rel_err(got, want) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sparse_bilinear_attention_packed_queries(dtype):
+    """Packed (variable number per image) queries: equal to the dense op on each image's slice, and to
+    the CPU restatement; an image without queries and unsorted image indices included."""
+    from vtpack_b200.layers import bilinear_attention, sparse_bilinear_attention_pointwise_forward
+    B, H, W, C, P = 4, 9, 7, 48, 3
+    g = torch.Generator().manual_seed(12)
+    inp = torch.randn(B, H, W, C, generator=g)
+    batches = torch.tensor([0] * 5 + [3] * 11 + [1] * 2 + [3] * 4)          # image 2 has no query
+    L = batches.numel()
+    grid = torch.rand(L, P, 2, generator=g) * torch.tensor([W + 3.0, H + 3.0]) - 2.0
+    weight = torch.randn(L, P, generator=g)
+    rb = (lambda t: t.to(dtype).double())
+    want = BO.sparse_bilinear_attention_pointwise_forward(rb(inp), rb(grid), rb(weight), batches)
+    got = sparse_bilinear_attention_pointwise_forward(inp.to(DEV, dtype), grid.to(DEV, dtype), weight.to(DEV, dtype),
+                                                      batches.to(DEV))
+    assert got.shape == (L, C) and got.dtype == dtype
+    assert rel_err(got.float(), want) < (1e-5 if dtype == torch.float32 else 2e-2)
+    sel = batches == 3
+    dense = bilinear_attention(inp[3:4].to(DEV, dtype).contiguous(), grid[sel][None].to(DEV, dtype),
+                               weight[sel][None].to(DEV, dtype), "point")[0]
+    assert torch.equal(got[sel.to(DEV)], dense)

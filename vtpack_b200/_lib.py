@@ -62,6 +62,8 @@ PROTOTYPES = {
                                         c_void_p]),
     "vtp_bilinear_attention_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                c_int, c_int, c_int, c_int, c_void_p]),
+    "vtp_sparse_bilinear_attention_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                      c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "vtp_bilinear_attention_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                 c_void_p]),

@@ -125,12 +125,17 @@ __device__ __forceinline__ void scatter(T* __restrict__ gimg, const Corner& k, i
 template <typename T, bool POINT, int V>
 __global__ void __launch_bounds__(BA_WARPS * 32)
 bilinear_attention_fwd_kernel(const T* __restrict__ input, const T* __restrict__ grid, const T* __restrict__ weight,
-                              T* __restrict__ out, int B, int H, int W, int C, int G, int P) {
+                              T* __restrict__ out, int B, int H, int W, int C, int G, int P,
+                              const long long* __restrict__ batch_of) {
+    // batch_of == null: B * G instances, G per image; else G packed instances, instance i reads image batch_of[i]
     const int lane = threadIdx.x & 31;
-    const long long n_inst = (long long)B * G;
+    const long long n_inst = batch_of ? (long long)G : (long long)B * G;
     for (long long inst = (long long)blockIdx.x * BA_WARPS + (threadIdx.x >> 5); inst < n_inst;
          inst += (long long)gridDim.x * BA_WARPS) {
-        const int b = (int)(inst / G);
+        long long b = batch_of ? batch_of[inst] : inst / G;
+        const bool image_ok = b >= 0 && b < B;          // an instance naming no image reads zeros
+        if (!image_ok) b = 0;
+        const int Hb = image_ok ? H : 0;                 // no pixel is in bounds
         const T* img = input + (size_t)b * H * W * C;
         const T* pts = grid + (size_t)inst * P * 2;
         if (POINT) {
@@ -140,7 +145,7 @@ bilinear_attention_fwd_kernel(const T* __restrict__ input, const T* __restrict__
 #pragma unroll
                 for (int v = 0; v < V; ++v) acc[v] = 0.f;
                 for (int p = 0; p < P; ++p) {
-                    const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), H, W);
+                    const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), Hb, W);
                     Taps<T, V> t;
                     t.load(img, k, W, C, c);
                     const float wp = to_f32(wt[p]);
@@ -152,7 +157,7 @@ bilinear_attention_fwd_kernel(const T* __restrict__ input, const T* __restrict__
         } else {
             const T* wt = weight + (size_t)inst * C;
             for (int p = 0; p < P; ++p) {
-                const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), H, W);
+                const Corner k = corners_of(sane(to_f32(pts[2 * p]), W), sane(to_f32(pts[2 * p + 1]), H), Hb, W);
                 float acc = 0.f;
                 for (int c = lane * V; c < C; c += 32 * V) {
                     Taps<T, V> t;
@@ -265,27 +270,40 @@ static bool ba_pairs(int dtype, int C, std::initializer_list<const void*> ptrs) 
 
 using namespace vtp;
 
-extern "C" int vtp_bilinear_attention_forward(const void* input, const void* grid, const void* weight, void* out,
-                                              int dtype, int mode, int B, int H, int W, int C, int G, int P,
-                                              void* stream) {
+static int ba_forward(const void* input, const void* grid, const void* weight, void* out, int dtype, int mode, int B,
+                      int H, int W, int C, int G, int P, const long long* batch_of, void* stream) {
     VTP_REQUIRE(input && grid && weight && out, VTP_ERR_NULL, "bilinear_attention: null pointer");
     if (int rc = ba_check("bilinear_attention", dtype, mode, B, H, W, C, G, P)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int blocks = ba_grid((long long)B * G);
+    const int blocks = ba_grid(batch_of ? (long long)G : (long long)B * G);
     const bool pairs = ba_pairs(dtype, C, {input, weight, out});
 #define VTP_BA_FWD(T, PT)                                                                                    \
     do {                                                                                                     \
         if (pairs)                                                                                           \
             bilinear_attention_fwd_kernel<T, PT, 2><<<blocks, BA_WARPS * 32, 0, st>>>(                       \
-                (const T*)input, (const T*)grid, (const T*)weight, (T*)out, B, H, W, C, G, P);               \
+                (const T*)input, (const T*)grid, (const T*)weight, (T*)out, B, H, W, C, G, P, batch_of);     \
         else                                                                                                 \
             bilinear_attention_fwd_kernel<T, PT, 1><<<blocks, BA_WARPS * 32, 0, st>>>(                       \
-                (const T*)input, (const T*)grid, (const T*)weight, (T*)out, B, H, W, C, G, P);               \
+                (const T*)input, (const T*)grid, (const T*)weight, (T*)out, B, H, W, C, G, P, batch_of);     \
     } while (0)
     if (dtype == VTP_F32) { if (mode == 0) VTP_BA_FWD(float, true); else VTP_BA_FWD(float, false); }
     else { if (mode == 0) VTP_BA_FWD(bf16, true); else VTP_BA_FWD(bf16, false); }
 #undef VTP_BA_FWD
     return check_launch("bilinear_attention_forward");
+}
+
+extern "C" int vtp_bilinear_attention_forward(const void* input, const void* grid, const void* weight, void* out,
+                                              int dtype, int mode, int B, int H, int W, int C, int G, int P,
+                                              void* stream) {
+    return ba_forward(input, grid, weight, out, dtype, mode, B, H, W, C, G, P, nullptr, stream);
+}
+
+extern "C" int vtp_sparse_bilinear_attention_forward(const void* input, const void* grid, const void* weight,
+                                                     const long long* batches, void* out, int dtype, int B, int H,
+                                                     int W, int C, int L, int P, void* stream) {
+    VTP_REQUIRE(batches, VTP_ERR_NULL, "sparse_bilinear_attention: null batches");
+    if (L == 0) return VTP_OK;
+    return ba_forward(input, grid, weight, out, dtype, 0, B, H, W, C, L, P, batches, stream);
 }
 
 extern "C" int vtp_bilinear_attention_backward(const void* grad_out, const void* input, const void* grid,

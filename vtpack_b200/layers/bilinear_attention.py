@@ -53,3 +53,22 @@ class _BilinearAttention(Function):
 
 
 bilinear_attention = _BilinearAttention.apply
+
+
+def sparse_bilinear_attention_pointwise_forward(input, grid, weight, batches):
+    """Point-mode bilinear attention over packed queries: input [B,H,W,C], grid [L,P,2], weight [L,P],
+    batches int64 [L] (the image of each query) -> [L,C].  The counterpart of the reference's
+    ``_C.sparse_bilinear_attention_pointwise_forward`` (``vision.cpp:28``); forward only, as there."""
+    require_cuda(input, grid, weight, batches)
+    input = input.contiguous()
+    grid = grid.to(input.dtype).contiguous()
+    weight = weight.to(input.dtype).contiguous()
+    batches = batches.to(torch.int64).contiguous()
+    B, H, W, C = input.shape
+    L, P = grid.shape[0], grid.shape[1]
+    assert grid.shape == (L, P, 2) and weight.shape == (L, P) and batches.shape == (L,)
+    out = torch.empty(L, C, dtype=input.dtype, device=input.device)
+    _lib.check(_lib.lib().vtp_sparse_bilinear_attention_forward(
+        ptr(input), ptr(grid), ptr(weight), ptr(batches), ptr(out), dtype_code(input.dtype), B, H, W, C, L, P,
+        stream_ptr(input.device)))
+    return out
