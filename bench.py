@@ -299,6 +299,35 @@ def profile_case(which):
         x = torch.randn(256, 257, 384, device=dev).bfloat16()
         for _ in range(3):
             model.blocks[0](x)
+    elif which == "train_ops":          # one launch of each training-path / bilinear kernel at model shapes
+        from vtpack_b200 import layers
+        B, G, C, heads = 256, 16, 384, 6
+        N, d = G * G + 1, C // heads
+        gen = torch.Generator(dev).manual_seed(1)
+        indices = torch.randint(0, 3, (B, G // 4, G // 4), device=dev, generator=gen)
+        patches, lengths = layers.grained_sample_index_to_patch(indices, torch.tensor([4, 2, 1]), 4, 1)
+        L = patches.shape[0]
+        x = torch.randn(B, N, C, device=dev, generator=gen).bfloat16().requires_grad_(True)
+        comp = layers.grained_sample_compress(x, patches, G, G, 1)
+        comp.backward(torch.randn(L, C, device=dev, generator=gen).bfloat16())               # pool_grad
+        q = torch.randn(L, C, device=dev, generator=gen).bfloat16().requires_grad_(True)
+        tok = layers.grained_sample_decompress(q, patches, x.detach(), G, G, 1, True)
+        tok.backward(torch.randn(B, N, C, device=dev, generator=gen).bfloat16())             # unpool_grad
+        qh = torch.randn(heads, L, d, device=dev, generator=gen).bfloat16()
+        kh = torch.randn(heads, B * N, d, device=dev, generator=gen).bfloat16()
+        kv_len = torch.full([B], N, dtype=torch.long)
+        s_ = layers.batched_sparse_gemm(qh, kh, lengths, kv_len, False, True)                # ragged Q K^T
+        layers.batched_sparse_gemm(s_, kh, lengths, kv_len, False, False)                    # ragged P V
+        Bb, H, P = 32, 64, 9
+        ys, xs = torch.meshgrid(torch.arange(H, device=dev), torch.arange(H, device=dev), indexing="ij")
+        centre = torch.stack([xs, ys], dim=-1).reshape(1, H * H, 1, 2).float()
+        for mode in ("point", "channel"):
+            inp = torch.randn(Bb, H, H, 64, device=dev, generator=gen).bfloat16().requires_grad_(True)
+            grid = (centre + 3.0 * torch.randn(Bb, H * H, P, 2, device=dev, generator=gen)).bfloat16().requires_grad_(True)
+            wt = torch.randn(Bb, H * H, P if mode == "point" else 64, device=dev, generator=gen).bfloat16()
+            wt.requires_grad_(True)
+            y = layers.bilinear_attention(inp, grid, wt, mode)
+            y.backward(torch.randn_like(y))
     else:
         raise SystemExit(f"unknown profile case {which}")
     torch.cuda.synchronize()
@@ -549,7 +578,7 @@ def main():
                     help="element type of the pinned host images of the end-to-end leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-stage-profile", action="store_true")
-    ap.add_argument("--profile", default=None, choices=["linear_kv", "attention", "block"],
+    ap.add_argument("--profile", default=None, choices=["linear_kv", "attention", "block", "train_ops"],
                     help="run a small case of one kernel family (for ncu) and exit")
     ap.add_argument("--layer-sweep", action="store_true",
                     help="time one DGE layer over gate skew against the dense block and exit")
