@@ -589,3 +589,21 @@ def train_block_weights() -> Dict[str, torch.Tensor]:
 
 TRAIN_PVT_BLOCK = dict(dim=32, heads=1, grid=16, sr=2, mlp_ratio=8, batch=2, noise_seed=23, grad_seed=24,
                        weight_seed=7, token_seed=8)
+
+
+TRAIN_PVT_MODEL = dict(batch=2, weight_seed=0, image_seed=9, noise_seed=50, target=(3, 7),
+                       grads=("patch_embed1.proj.weight", "block1.0.dge.router.gate.weight",
+                              "block2.1.attn.sr.bias", "block2.1.attn.norm.weight", "block4.1.mlp.fc2.bias", "cls_token"))
+
+
+def train_pvt_model_noises(cfg: dict, img_size: int = 256):
+    """One Gumbel-noise tensor per block of a PVT+DGE model, in forward order (region grid of stage
+    i: img_size / (4 * 2^i) / 4 per side)."""
+    t = TRAIN_PVT_MODEL
+    noises, k = [], 0
+    for i, depth in enumerate(cfg["depths"]):
+        r = img_size // (4 * 2 ** i) // 4
+        for _ in range(depth):
+            noises.append(make_gumbel_noise((t["batch"], r, r, 3), t["noise_seed"] + k))
+            k += 1
+    return noises

@@ -33,6 +33,9 @@ Fixtures
                         (vtpack/layers/bilinear_attention.py) in both modes on B=2, 9x11 map, C=40,
                         G=23 queries, P=5 points reaching two pixels outside the map: output and the
                         three gradients.
+  train_pvt_model_fp32.npz  PVT+DGE tiny (pvt_dge_s124_tiny_256) in training mode with sparse_train on,
+                        fp32, B=2, one injected Gumbel-noise tensor per block: logits, cross-entropy
+                        loss, per-block query counts and six (small) parameter gradients.
 Inputs are regenerated from the seeds by the tests; each fixture carries a
 float64 sum of its inputs so RNG drift is detected rather than misread as a
 parity failure.
@@ -293,6 +296,36 @@ def bilinear_fixture():
     print("bilinear_attention_fp32.npz", {k: v.shape for k, v in out.items()})
 
 
+def train_pvt_model_fixture():
+    import importlib
+    import torch.nn.functional as F
+    ref_shim.install()
+    pvt = importlib.import_module("vtpack.models.dge.pvt_dge")
+    cfg, t = O.PVT_CONFIGS["tiny"], O.TRAIN_PVT_MODEL
+    m = pvt.pvt_dge_s124_tiny_256()
+    m.load_state_dict(O.make_pvt_state_dict(cfg, seed=t["weight_seed"]), strict=True)
+    m.train()
+    blocks = [b for i in range(4) for b in getattr(m, f"block{i + 1}")]
+    for b in blocks:
+        b.dge.sparse_train = True
+    x = O.make_images(t["batch"], 256, seed=t["image_seed"])
+    real = F.gumbel_softmax
+    F.gumbel_softmax = O.gumbel_softmax_fixed(O.train_pvt_model_noises(cfg))
+    try:
+        logits = m(x)
+        counts = np.stack([np.asarray(b.dge.states["batches"]) for b in blocks])
+        loss = F.cross_entropy(logits, torch.tensor(t["target"]))
+        loss.backward()
+    finally:
+        F.gumbel_softmax = real
+    params = dict(m.named_parameters())
+    out = {"logits": logits.detach().numpy(), "loss": np.float64(loss.item()), "counts": counts}
+    for name in t["grads"]:
+        out[f"grad.{name}"] = params[name].grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "train_pvt_model_fp32.npz"), **out)
+    print("train_pvt_model_fp32.npz loss", loss.item(), counts.tolist())
+
+
 if __name__ == "__main__":
     layer_fixture()
     model_fixture()
@@ -302,3 +335,4 @@ if __name__ == "__main__":
     train_block_fixture()
     train_pvt_block_fixture()
     bilinear_fixture()
+    train_pvt_model_fixture()

@@ -239,3 +239,46 @@ def test_training_pvt_block_matches_reference(golden_dir):
             assert rel_err(prm.grad, z[f"grad.{name}"]) < 5 * TOL, name
             checked += 1
     assert checked == 20          # DeiT block's 16 plus the reduction convolution and its LayerNorm
+
+
+def test_training_pvt_model_matches_reference(golden_dir):
+    """PVT+DGE tiny in training mode (sparse_train on, one injected Gumbel-noise tensor per block):
+    the same per-block query counts, logits, loss and parameter gradients as the reference."""
+    from vtpack_b200.models.dge import pvt_dge
+    z = _golden(golden_dir, "train_pvt_model_fp32.npz")
+    cfg, t = O.PVT_CONFIGS["tiny"], O.TRAIN_PVT_MODEL
+    m = pvt_dge.pvt_dge_s124_tiny_256()
+    m.load_state_dict(O.make_pvt_state_dict(cfg, seed=t["weight_seed"]), strict=True)
+    m.to(DEV).train()
+    blocks = [b for i in range(4) for b in getattr(m, f"block{i + 1}")]
+    for b in blocks:
+        b.dge.sparse_train = True
+    x = O.make_images(t["batch"], 256, seed=t["image_seed"]).to(DEV)
+    real = F.gumbel_softmax
+    F.gumbel_softmax = O.gumbel_softmax_fixed(O.train_pvt_model_noises(cfg))
+    prev = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False          # the patch and reduction convolutions in full fp32
+    try:
+        logits = m(x)
+        counts = torch.stack([b.dge.states["batches"].cpu() for b in blocks])
+        loss = F.cross_entropy(logits, torch.tensor(t["target"], device=DEV))
+        loss.backward()
+    finally:
+        F.gumbel_softmax = real
+        torch.backends.cudnn.allow_tf32 = prev
+    assert torch.equal(counts, z["counts"])
+    assert rel_err(logits, z["logits"]) < TOL
+    assert abs(float(loss) - float(z["loss"])) < 1e-4
+    params = dict(m.named_parameters())
+    for name in t["grads"]:
+        assert rel_err(params[name].grad, z[f"grad.{name}"]) < 1e-3, name
+    # the feature-pyramid variant returns the four stage maps
+    m.num_classes = 0
+    F.gumbel_softmax = O.gumbel_softmax_fixed(O.train_pvt_model_noises(cfg))
+    try:
+        with torch.no_grad():
+            feats = m(x)
+    finally:
+        F.gumbel_softmax = real
+    assert [tuple(feats[f"res{i}"].shape) for i in (2, 3, 4, 5)] == [(2, 64, 64, 64), (2, 128, 32, 32),
+                                                                       (2, 320, 16, 16), (2, 512, 8, 8)]

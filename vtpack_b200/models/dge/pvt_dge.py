@@ -156,6 +156,12 @@ class PatchEmbed(nn.Module):
         self.proj = nn.Conv2d(in_chans, embed_dim, kernel_size=patch_size, stride=patch_size)
         self.norm = nn.LayerNorm(embed_dim)
 
+    def forward(self, x):
+        """[B, C_in, H, W] -> (tokens [B, H/p * W/p, C], (H/p, W/p)) (``pvt_dge.py:170-179``); used by the
+        training-mode forward only, eval mode runs the embedding through the library."""
+        H, W = x.shape[2] // self.patch_size[0], x.shape[3] // self.patch_size[1]
+        return self.norm(self.proj(x).flatten(2).transpose(1, 2)), (H, W)
+
     def complexity(self, num_inputs, num_queries):
         comp = num_inputs * self.proj.in_channels * self.proj.out_channels
         comp += num_inputs / (self.patch_size[0] * self.patch_size[1]) * self.proj.out_channels  # norm
@@ -196,6 +202,8 @@ class PyramidVisionTransformer(nn.Module):
         self.depths = depths
         self.num_stages = num_stages
         self.img_size = img_size
+        dpr = [v.item() for v in torch.linspace(0, drop_path_rate, sum(depths))]   # drop rate grows with depth
+        cur = 0
         for i in range(num_stages):
             patch_embed = PatchEmbed(img_size=img_size if i == 0 else img_size // (2 ** (i + 1)),
                                      patch_size=patch_size if i == 0 else 2,
@@ -204,8 +212,9 @@ class PyramidVisionTransformer(nn.Module):
             pos_embed = nn.Parameter(torch.zeros(1, num_patches, embed_dims[i]))
             block = nn.ModuleList([Block(
                 dim=embed_dims[i], num_heads=num_heads[i], mlp_ratio=mlp_ratios[i], qkv_bias=qkv_bias,
-                qk_scale=qk_scale, drop=drop_rate, attn_drop=attn_drop_rate, norm_layer=norm_layer,
-                sr_ratio=sr_ratios[i], split_sizes=split_sizes[i]) for _ in range(depths[i])])
+                qk_scale=qk_scale, drop=drop_rate, attn_drop=attn_drop_rate, drop_path=dpr[cur + j],
+                norm_layer=norm_layer, sr_ratio=sr_ratios[i], split_sizes=split_sizes[i]) for j in range(depths[i])])
+            cur += depths[i]
             setattr(self, f"patch_embed{i + 1}", patch_embed)
             setattr(self, f"pos_embed{i + 1}", pos_embed)
             setattr(self, f"pos_drop{i + 1}", nn.Dropout(p=drop_rate))
@@ -228,11 +237,50 @@ class PyramidVisionTransformer(nn.Module):
                 m.router.init_parameters()
         self.last_counts = None
 
+    def _stage_pos_embed(self, pos_embed, patch_embed, H, W):
+        """The stage's position embedding, bilinearly resized when the token grid is not the one it
+        was made for (``pvt_dge.py:286-293``)."""
+        if H * W == patch_embed.num_patches:
+            return pos_embed
+        grid = pos_embed.reshape(1, patch_embed.H, patch_embed.W, -1).permute(0, 3, 1, 2)
+        grid = torch.nn.functional.interpolate(grid, size=(H, W), mode="bilinear", align_corners=False)
+        return grid.reshape(1, -1, H * W).permute(0, 2, 1)
+
+    def _forward_train(self, x):
+        """Training mode (``pvt_dge.py:295-337``): the stages op by op in the parameters' dtype and in
+        autograd, blocks in their training mode; with ``num_classes == 0`` the feature pyramid
+        ``{"res2": .., "res5": ..}`` of ``[B, C_i, H_i, W_i]`` maps is returned."""
+        B = x.shape[0]
+        x = x.to(self.cls_token.dtype)
+        outputs = {}
+        for i in range(self.num_stages):
+            patch_embed = getattr(self, f"patch_embed{i + 1}")
+            pos_embed = getattr(self, f"pos_embed{i + 1}")
+            x, (H, W) = patch_embed(x)
+            if i == self.num_stages - 1:
+                x = torch.cat((self.cls_token.expand(B, -1, -1), x), dim=1)
+                pos_embed = torch.cat((pos_embed[:, 0:1], self._stage_pos_embed(pos_embed[:, 1:], patch_embed, H, W)),
+                                      dim=1)
+            else:
+                pos_embed = self._stage_pos_embed(pos_embed, patch_embed, H, W)
+            x = getattr(self, f"pos_drop{i + 1}")(x + pos_embed)
+            for blk in getattr(self, f"block{i + 1}"):
+                x = blk(x, H, W)
+            if i != self.num_stages - 1:
+                x = x.reshape(B, H, W, -1).permute(0, 3, 1, 2).contiguous()
+                outputs[f"res{i + 2}"] = x
+            elif self.num_classes == 0:
+                outputs[f"res{i + 2}"] = x[:, 1:].reshape(B, H, W, -1).permute(0, 3, 1, 2).contiguous()
+        if self.num_classes == 0:
+            return outputs
+        return self.head(self.norm(x)[:, 0])
+
     def forward(self, x):
         """images [B,3,S,S] on the device -> logits fp32 [B,num_classes] (``pvt_dge.py:295-337``,
-        classification path at the training resolution)."""
+        classification path at the training resolution).  In training mode: the differentiable
+        op-by-op sequence (any input size the grids divide, feature-pyramid outputs included)."""
         if self.training:
-            raise NotImplementedError("training mode is mirrored for the blocks, not for the pyramid wrapper")
+            return self._forward_train(x)
         if self.num_classes <= 0:
             raise NotImplementedError("the feature-pyramid outputs (num_classes = 0) are not mirrored")
         require_cuda(x)
