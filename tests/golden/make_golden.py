@@ -36,6 +36,10 @@ Fixtures
   train_pvt_model_fp32.npz  PVT+DGE tiny (pvt_dge_s124_tiny_256) in training mode with sparse_train on,
                         fp32, B=2, one injected Gumbel-noise tensor per block: logits, cross-entropy
                         loss, per-block query counts and six (small) parameter gradients.
+  pvt_model_384_fp32.npz  PVT+DGE tiny in eval mode on 384 px images (position embeddings resized), fp32,
+                        B=1, weights seed 0, images seed 10: logits, per-block query counts, and the
+                        feature pyramid of the same weights with num_classes = 0 (every 8th pixel of each
+                        map and each map's float64 sum).
 Inputs are regenerated from the seeds by the tests; each fixture carries a
 float64 sum of its inputs so RNG drift is detected rather than misread as a
 parity failure.
@@ -326,6 +330,37 @@ def train_pvt_model_fixture():
     print("train_pvt_model_fp32.npz loss", loss.item(), counts.tolist())
 
 
+def pvt_384_fixture():
+    import importlib
+    ref_shim.install()
+    pvt = importlib.import_module("vtpack.models.dge.pvt_dge")
+    cfg = O.PVT_CONFIGS["tiny"]
+    sd = O.make_pvt_state_dict(cfg, seed=0)
+    x = O.make_images(1, 384, seed=10)
+    out = {}
+    m = pvt.pvt_dge_s124_tiny_256()
+    m.load_state_dict(sd, strict=True)
+    m.eval()
+    with torch.no_grad():
+        out["logits"] = m(x).numpy()
+    blocks = [b for i in range(4) for b in getattr(m, f"block{i + 1}")]
+    out["counts"] = np.stack([np.asarray(b.dge.states["batches"]) for b in blocks])
+    out["gate_margin"] = np.float64(min(float((t.values[..., 0] - t.values[..., 1]).min()) for t in
+                                        (b.dge.states["gate"].topk(2, dim=-1) for b in blocks)))
+    m0 = pvt.pvt_dge_s124_tiny_256(num_classes=0)
+    m0.load_state_dict({k: v for k, v in sd.items() if not k.startswith(("head.", "norm."))}, strict=True)
+    m0.eval()
+    with torch.no_grad():
+        feats = m0(x)
+    for k, v in feats.items():
+        out[f"{k}_sub"] = v[:, :, ::8, ::8].numpy()
+        out[f"{k}_sum"] = np.float64(v.double().sum().item())
+        out[f"{k}_shape"] = np.asarray(v.shape)
+    np.savez_compressed(os.path.join(HERE, "pvt_model_384_fp32.npz"), **out)
+    print("pvt_model_384_fp32.npz", out["counts"].tolist(), "min gate margin", out["gate_margin"],
+          {k: v.shape for k, v in feats.items()})
+
+
 if __name__ == "__main__":
     layer_fixture()
     model_fixture()
@@ -336,3 +371,4 @@ if __name__ == "__main__":
     train_pvt_block_fixture()
     bilinear_fixture()
     train_pvt_model_fixture()
+    pvt_384_fixture()

@@ -354,3 +354,29 @@ def test_pvt_model(golden_dir, dtype):
         assert rel_err(logits, ref) < 1e-4
     else:
         assert float((logits - ref).abs().max()) < 2e-2
+
+
+def test_pvt_model_other_input_size_and_pyramid(golden_dir):
+    """PVT+DGE tiny in eval mode on 384 px images (position embeddings resized bilinearly) and its
+    feature-pyramid variant (num_classes = 0), fp32, against the reference's own outputs."""
+    from vtpack_b200 import _lib
+    from vtpack_b200.models.dge.pvt_dge import pvt_dge_s124_tiny_256
+    g = np.load(os.path.join(golden_dir, "pvt_model_384_fp32.npz"))
+    sd = O.make_pvt_state_dict(O.PVT_CONFIGS["tiny"], seed=0)
+    img = O.make_images(1, 384, seed=10).to(DEV)
+    m = pvt_dge_s124_tiny_256()
+    m.load_state_dict(sd, strict=True)
+    m = m.eval().to(DEV)
+    logits = m(img).cpu()
+    assert _lib.device_status() == 0
+    assert float(g["gate_margin"]) > 1e-5
+    assert [c.tolist() for c in m.last_counts] == g["counts"].tolist()
+    assert rel_err(logits, torch.from_numpy(g["logits"])) < 1e-4
+    m0 = pvt_dge_s124_tiny_256(num_classes=0)
+    m0.load_state_dict({k: v for k, v in sd.items() if not k.startswith(("head.", "norm."))}, strict=True)
+    feats = m0.eval().to(DEV)(img)
+    assert sorted(feats) == ["res2", "res3", "res4", "res5"]
+    for k, v in feats.items():
+        assert list(v.shape) == g[f"{k}_shape"].tolist(), k
+        assert rel_err(v[:, :, ::8, ::8], torch.from_numpy(g[f"{k}_sub"])) < 1e-4, k
+        assert abs(float(v.double().sum()) - float(g[f"{k}_sum"])) < 1e-4 * float(v.double().abs().sum()), k

@@ -276,13 +276,13 @@ class PyramidVisionTransformer(nn.Module):
         return self.head(self.norm(x)[:, 0])
 
     def forward(self, x):
-        """images [B,3,S,S] on the device -> logits fp32 [B,num_classes] (``pvt_dge.py:295-337``,
-        classification path at the training resolution).  In training mode: the differentiable
-        op-by-op sequence (any input size the grids divide, feature-pyramid outputs included)."""
+        """images [B,3,S,S] on the device -> logits fp32 [B,num_classes], or with ``num_classes == 0``
+        the feature pyramid ``{"res2": .., "res5": ..}`` of ``[B, C_i, H_i, W_i]`` maps
+        (``pvt_dge.py:295-337``).  S may differ from the training resolution (the position embeddings
+        are resized bilinearly, ``pvt_dge.py:286-293``) as long as every stage's grid divides into 4 x 4
+        regions and reduction windows.  In training mode: the differentiable op-by-op sequence."""
         if self.training:
             return self._forward_train(x)
-        if self.num_classes <= 0:
-            raise NotImplementedError("the feature-pyramid outputs (num_classes = 0) are not mirrored")
         require_cuda(x)
         if x.dtype not in (torch.float32, torch.bfloat16):
             x = x.float()
@@ -290,16 +290,16 @@ class PyramidVisionTransformer(nn.Module):
         B, _, S, _ = x.shape
         dtype = self.cls_token.dtype
         lib, st = _lib.lib(), stream_ptr(x.device)
-        counts = []
+        counts, outputs = [], {}
         tokens, H, W = None, 0, 0
         for i in range(self.num_stages):
             pe = getattr(self, f"patch_embed{i + 1}")
-            pos = getattr(self, f"pos_embed{i + 1}").detach()[0].contiguous()
+            pos_full = getattr(self, f"pos_embed{i + 1}").detach()
             C = self.embed_dims[i]
             P = pe.patch_size[0]
             if i == 0:
-                if pe.H * P != S:
-                    raise NotImplementedError("position-embedding interpolation (other input sizes) is not mirrored")
+                if S % P:
+                    raise ValueError(f"input size {S} is not a multiple of the patch size {P}")
                 H = W = S // P
                 cols = torch.empty(B * H * W, 3 * P * P, dtype=dtype, device=x.device)
                 _lib.check(lib.vtp_patch_im2col(ptr(x), dtype_code(x.dtype), B, S, P, dtype_code(dtype), ptr(cols),
@@ -314,6 +314,12 @@ class PyramidVisionTransformer(nn.Module):
             y = _norm_rows(y, y.shape[0], C, C, pe.norm)
             HW = H * W
             last = i == self.num_stages - 1
+            # the stage's position rows ([cls row;] grid rows), resized when the grid is not the trained one
+            if last:
+                pos = torch.cat((pos_full[:, 0:1], self._stage_pos_embed(pos_full[:, 1:], pe, H, W)), dim=1)
+            else:
+                pos = self._stage_pos_embed(pos_full, pe, H, W)
+            pos = pos[0].to(dtype).contiguous()
             tokens = torch.empty(B, HW + (1 if last else 0), C, dtype=dtype, device=x.device)
             _lib.check(lib.vtp_add_rows(ptr(y), B * HW, ptr(pos), HW, 1 if last else 0, ptr(tokens), HW,
                                         HW + (1 if last else 0), 1 if last else 0, dtype_code(dtype), B * HW, C, st))
@@ -324,6 +330,12 @@ class PyramidVisionTransformer(nn.Module):
             for blk in getattr(self, f"block{i + 1}"):
                 tokens = blk(tokens, H, W)
                 counts.append(blk.dge.states["batches_device"])
+            if self.num_classes == 0:
+                grid_rows = tokens[:, 1:] if last else tokens
+                outputs[f"res{i + 2}"] = grid_rows.reshape(B, H, W, C).permute(0, 3, 1, 2).contiguous()
+        self.last_counts = counts
+        if self.num_classes == 0:
+            return outputs
         N = tokens.shape[1]
         C = tokens.shape[2]
         cls_n = _norm_rows(tokens, B, C, N * C, self.norm)
