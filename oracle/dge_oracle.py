@@ -607,3 +607,21 @@ def train_pvt_model_noises(cfg: dict, img_size: int = 256):
             noises.append(make_gumbel_noise((t["batch"], r, r, 3), t["noise_seed"] + k))
             k += 1
     return noises
+
+
+DPVT_ATTENTION = dict(dim=64, heads=4, points=3, H=8, W=6, batch=2, weight_seed=60, token_seed=61, grad_seed=62)
+
+
+def dpvt_attention_weights() -> Dict[str, torch.Tensor]:
+    """Seeded parameters of the deformable-attention fixture under the reference's state_dict keys
+    (``dpvt.py:61-71``): random matrices, and offset weights large enough that points leave the map."""
+    c = DPVT_ATTENTION
+    C, h, P = c["dim"], c["heads"], c["points"]
+    g = torch.Generator().manual_seed(c["weight_seed"])
+    rn = lambda *shape, std: torch.randn(*shape, generator=g) * std      # noqa: E731
+    return {
+        "v.weight": rn(C, C, std=0.1), "v.bias": rn(C, std=0.1),
+        "attn_weight.weight": rn(h * P, C, std=0.2), "attn_weight.bias": rn(h * P, std=0.2),
+        "proj.weight": rn(C, C, std=0.1), "proj.bias": rn(C, std=0.1),
+        "offsets.weight": rn(h * P * 2, C, std=0.3), "offsets.bias": rn(h * P * 2, std=2.0),
+    }

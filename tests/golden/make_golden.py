@@ -40,6 +40,9 @@ Fixtures
                         B=1, weights seed 0, images seed 10: logits, per-block query counts, and the
                         feature pyramid of the same weights with num_classes = 0 (every 8th pixel of each
                         map and each map's float64 sum).
+  dpvt_attention_fp32.npz  the reference's deformable attention module (dpvt.py Attention: dim 64, 4 heads,
+                        3 points, 8x6 map, B=2) forward and backward: output, input gradient and all eight
+                        parameter gradients for sum(out * g).
 Inputs are regenerated from the seeds by the tests; each fixture carries a
 float64 sum of its inputs so RNG drift is detected rather than misread as a
 parity failure.
@@ -361,6 +364,23 @@ def pvt_384_fixture():
           {k: v.shape for k, v in feats.items()})
 
 
+def dpvt_attention_fixture():
+    import importlib
+    ref_shim.install()
+    dpvt = importlib.import_module("vtpack.models.standard.dpvt")
+    c = O.DPVT_ATTENTION
+    att = dpvt.Attention(c["dim"], num_heads=c["heads"], qkv_bias=True, num_points=c["points"])
+    att.load_state_dict(O.dpvt_attention_weights(), strict=True)
+    x = O.randn_seeded((c["batch"], c["H"] * c["W"], c["dim"]), c["token_seed"]).requires_grad_(True)
+    y = att(x, c["H"], c["W"])
+    (y * O.randn_seeded(tuple(y.shape), c["grad_seed"])).sum().backward()
+    out = {"out": y.detach().numpy(), "grad_x": x.grad.numpy()}
+    for name, prm in att.named_parameters():
+        out[f"grad.{name}"] = prm.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "dpvt_attention_fp32.npz"), **out)
+    print("dpvt_attention_fp32.npz", len(out), "arrays")
+
+
 if __name__ == "__main__":
     layer_fixture()
     model_fixture()
@@ -372,3 +392,4 @@ if __name__ == "__main__":
     bilinear_fixture()
     train_pvt_model_fixture()
     pvt_384_fixture()
+    dpvt_attention_fixture()

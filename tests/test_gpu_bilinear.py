@@ -116,3 +116,25 @@ def test_sparse_bilinear_attention_packed_queries(dtype):
     dense = bilinear_attention(inp[3:4].to(DEV, dtype).contiguous(), grid[sel][None].to(DEV, dtype),
                                weight[sel][None].to(DEV, dtype), "point")[0]
     assert torch.equal(got[sel.to(DEV)], dense)
+
+
+def test_dpvt_attention_module_matches_reference(golden_dir):
+    """The deformable attention module (dpvt.py:51-115) over this library's op: output, input
+    gradient and all eight parameter gradients against the reference's own module."""
+    from oracle import dge_oracle as O
+    from vtpack_b200.models.standard.dpvt import Attention
+    z = np.load(os.path.join(golden_dir, "dpvt_attention_fp32.npz"))
+    c = O.DPVT_ATTENTION
+    att = Attention(c["dim"], num_heads=c["heads"], qkv_bias=True, num_points=c["points"])
+    att.load_state_dict(O.dpvt_attention_weights(), strict=True)
+    att.to(DEV)
+    x = O.randn_seeded((c["batch"], c["H"] * c["W"], c["dim"]), c["token_seed"]).to(DEV).requires_grad_(True)
+    y = att(x, c["H"], c["W"])
+    (y * O.randn_seeded(tuple(y.shape), c["grad_seed"]).to(DEV)).sum().backward()
+    assert rel_err(y, torch.from_numpy(z["out"])) < 1e-5
+    assert rel_err(x.grad, torch.from_numpy(z["grad_x"])) < 1e-4
+    n = 0
+    for name, prm in att.named_parameters():
+        assert rel_err(prm.grad, torch.from_numpy(z[f"grad.{name}"])) < 1e-4, name
+        n += 1
+    assert n == 8
