@@ -454,16 +454,20 @@ unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const 
     const size_t tok0 = (size_t)b * g.N + g.num_extra + (size_t)(ry * RG + w) * g.W + rx * RG + grp * TPG;
     const int prow = first + (w / step) * s;            // packed row of this grid row's first patch
 
-    // every row this group needs, requested up front: TPG reference rows and the patch rows they map to
+    // every row this group needs, requested up front: TPG reference rows and the patch rows they map to.
+    // At the finest grain a token is its own patch and comp[p] is a copy of ref[tok], so
+    // ref + (q - comp) is q: neither ref nor comp is read (a third of the regions on average; the
+    // grain is the same for the whole CTA, so nothing diverges)
+    const bool fine = step == 1;
     Vec<T> rrow[TPG][CPL], qrow[TPG][CPL], crow[TPG][CPL];
 #pragma unroll
     for (int j = 0; j < TPG; ++j) {
         const int col = grp * TPG + j;
-        load_row<T, CPL>(rrow[j], ref + (tok0 + j) * g.C, sub, G);
+        if (!fine) load_row<T, CPL>(rrow[j], ref + (tok0 + j) * g.C, sub, G);
         if (j == 0 || (col % step) == 0) {               // a new patch starts at this column
             const int p = prow + col / step;
             load_row<T, CPL>(qrow[j], q + (size_t)p * g.C, sub, G);
-            load_row<T, CPL>(crow[j], comp + (size_t)p * g.C, sub, G);
+            if (!fine) load_row<T, CPL>(crow[j], comp + (size_t)p * g.C, sub, G);
         }
     }
     float acc[CPL][VN];                                  // in-order sum of this group's output tokens
@@ -474,20 +478,29 @@ unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const 
     for (int j = 0; j < TPG; ++j) {
         const int col = grp * TPG + j;
         if (j == 0 || (col % step) == 0) {
-            float cf[CPL][VN];
             to_f<T, CPL>(d, qrow[j]);
-            to_f<T, CPL>(cf, crow[j]);
+            if (!fine) {
+                float cf[CPL][VN];
+                to_f<T, CPL>(cf, crow[j]);
+#pragma unroll
+                for (int ch = 0; ch < CPL; ++ch)
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) d[ch][i] -= cf[ch][i];
+            }
+        }
+        float o[CPL][VN];
+        if (fine) {
 #pragma unroll
             for (int ch = 0; ch < CPL; ++ch)
 #pragma unroll
-                for (int i = 0; i < VN; ++i) d[ch][i] -= cf[ch][i];
+                for (int i = 0; i < VN; ++i) o[ch][i] = d[ch][i];
+        } else {
+            to_f<T, CPL>(o, rrow[j]);
+#pragma unroll
+            for (int ch = 0; ch < CPL; ++ch)
+#pragma unroll
+                for (int i = 0; i < VN; ++i) o[ch][i] = d[ch][i] + o[ch][i];
         }
-        float o[CPL][VN];
-        to_f<T, CPL>(o, rrow[j]);
-#pragma unroll
-        for (int ch = 0; ch < CPL; ++ch)
-#pragma unroll
-            for (int i = 0; i < VN; ++i) o[ch][i] = d[ch][i] + o[ch][i];
         round_store<T, CPL>(o, out + (tok0 + j) * g.C, sub, G);       // o now holds the rounded values
         if (nx.stats_x) {
             const float2 st = mean_rstd(row_sums<T, G, CPL>(o), g.C, nx.eps);
