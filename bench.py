@@ -86,20 +86,30 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_reference_rate(model_kind, batch, steps, warmup):
+def alternate_gate_bias(batch, n_splits=3, big=1e4):
+    """BASELINE config 5's gate skew: even images forced all-coarse (the last split, 1x1), odd images
+    all-fine (the first split, 4x4), as a per-image offset of the router logits."""
+    bias = torch.zeros(batch, n_splits)
+    bias[0::2, n_splits - 1] = big
+    bias[1::2, 0] = big
+    return bias
+
+
+def cpu_reference_rate(model_kind, batch, steps, warmup, img_size=256, gate_skew="none"):
     """images/sec of the CPU restatement of the reference's eval forward (fp32, all host cores)."""
     from oracle import dge_oracle as O
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     cfg = O.MODEL_CONFIGS[model_kind]
-    sd = O.make_state_dict(cfg["embed_dim"], cfg["depth"], cfg["num_heads"], seed=0)
-    img = O.make_images(batch, 256, seed=1)
+    sd = O.make_state_dict(cfg["embed_dim"], cfg["depth"], cfg["num_heads"], img_size=img_size, seed=0)
+    img = O.make_images(batch, img_size, seed=1)
+    bias = alternate_gate_bias(batch) if gate_skew == "alternate" else None
     with torch.no_grad():
         for _ in range(warmup):
-            O.deit_dge_forward(img, sd, cfg["depth"], cfg["num_heads"], (4, 2, 1))
+            O.deit_dge_forward(img, sd, cfg["depth"], cfg["num_heads"], (4, 2, 1), gate_image_bias=bias)
         t0 = time.perf_counter()
         for _ in range(steps):
-            O.deit_dge_forward(img, sd, cfg["depth"], cfg["num_heads"], (4, 2, 1))
+            O.deit_dge_forward(img, sd, cfg["depth"], cfg["num_heads"], (4, 2, 1), gate_image_bias=bias)
         dt = time.perf_counter() - t0
     return batch * steps / dt, dt / steps * 1e3, cores
 
@@ -109,12 +119,14 @@ def run_reference(args):
     if rank != 0:
         return
     b = args.cpu_batch
-    rate, ms, cores = cpu_reference_rate(args.model, b, args.steps, args.warmup)
+    rate, ms, cores = cpu_reference_rate(args.model, b, args.steps, args.warmup, args.img_size, args.gate_skew)
     line = {
         "impl": "reference", "metric": "images/sec", "value": rate, "unit": "images/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"DeiT-{args.model}+DGE s124 256px eval forward, CPU, fp32", "batch_per_step": b},
+        "config": {"workload": f"DeiT-{args.model}+DGE s124 {args.img_size}px eval forward, CPU, fp32"
+                               + (", even images all-coarse / odd all-fine" if args.gate_skew == "alternate" else ""),
+                   "batch_per_step": b},
         "cpu_baseline": {"value": rate, "unit": "images/s", "cores": cores, "kind": "port",
                          "sample": f"{args.steps} forwards of {b} images (same model/config), torch CPU fp32"},
         "e2e": {"value": rate, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -122,15 +134,70 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def stage_profile(model, batch, device, iters, pk):
-    """Per-kernel times of one DGE block (block 0 weights) on N(0,1) tokens, from events the
-    library records between its launches; returns (rows, roofline of the dominant kernel)."""
+def region_grains(x, gate_w, gate_b, G, device):
+    """Grain index per region of tokens x [B, 1+G*G, C] under a router gate (the library's stand-alone gate kernel)."""
+    from vtpack_b200 import _lib
+    B, _, C = x.shape
+    idx = torch.empty(B * (G // 4) ** 2, dtype=torch.int32, device=device)
+    _lib.check(_lib.lib().vtp_router_gate(x.data_ptr(), 1 if x.dtype == torch.bfloat16 else 0, B, G, G, C, 1, 4,
+                                          gate_w.data_ptr(), gate_b.data_ptr(), 3, None, idx.data_ptr(),
+                                          torch.cuda.current_stream(device).cuda_stream))
+    return idx
+
+
+def unpool_rows(B, HW, L, fine):
+    """Token-row transfers of the unpool + residual kernel: it writes every token row and reads every packed row
+    of q; a region at the finest grain needs nothing else (its comp rows are copies of its tokens, so
+    ref + (q - comp) = q), the other regions and the cls row also read their token rows and their comp rows."""
+    N = HW + 1
+    return B * N + L + (B * (1.0 - fine) * HW + B) + (L - fine * B * HW)
+
+
+def front_back_ms(model, batch, device, image_bytes, iters=10):
+    """The launches of a forward outside the blocks (im2col + cls rows, patch-embedding Linear, final LayerNorm
+    of the cls rows, head), each timed as `iters` back-to-back launches through the C ABI."""
+    from vtpack_b200 import _lib
+    lib = _lib.lib()
+    C, S, P = model.embed_dim, model.img_size, model.patch_size
+    HW = (S // P) ** 2
+    dtype = model.compute_dtype()
+    t = model._pack.tensors
+    img = torch.randn(batch, 3, S, S, device=device, dtype=torch.float32 if image_bytes == 4 else torch.bfloat16)
+    cols = torch.empty(batch * HW, 3 * P * P, device=device, dtype=dtype)
+    x = torch.empty(batch, HW + 1, C, device=device, dtype=dtype)
+    cls_n = torch.empty(batch, C, device=device, dtype=dtype)
+    logits = torch.empty(batch, 1000, device=device)
+    st = torch.cuda.current_stream(device).cuda_stream
+    code = 1 if dtype == torch.bfloat16 else 0
+    calls = [
+        lambda: lib.vtp_patch_im2col(img.data_ptr(), 0 if image_bytes == 4 else 1, batch, S, P, code, cols.data_ptr(),
+                                     t["cls_token"].data_ptr(), t["pos_embed"].data_ptr(), C, x.data_ptr(), st),
+        lambda: lib.vtp_linear(cols.data_ptr(), 3 * P * P, t["patch_w"].data_ptr(), t["patch_b"].data_ptr(),
+                               x.data_ptr(), C, x.data_ptr(), C, code, batch * HW, None, C, 3 * P * P, 0, st),
+        lambda: lib.vtp_layernorm(x.data_ptr(), code, batch, None, C, (HW + 1) * C, t["norm_w"].data_ptr(),
+                                  t["norm_b"].data_ptr(), 1e-6, cls_n.data_ptr(), st),
+        lambda: lib.vtp_linear(cls_n.data_ptr(), C, t["head_w"].data_ptr(), t["head_b"].data_ptr(), None, 0,
+                               logits.data_ptr(), 1000, code, batch, None, 1000, C, _lib.FLAG_OUT_F32, st),
+    ]
+    total = 0.0
+    for fn in calls:
+        total += _time_us(lambda: _lib.check(fn()), iters=iters) * 1e-3
+    return total
+
+
+def stage_profile(model, batch, device, iters, pk, ms_per_step):
+    """Per-kernel times of one DGE block (a middle block's weights) on N(0,1) tokens, from events the library
+    records between its launches.  Every stage then sits between two event records, which keeps a launch from
+    queueing behind the one in front of it: these are upper bounds of what a kernel costs inside the replayed
+    graph.  `ms_in_step_est` scales them so that depth x block + the front/back launches equals the measured
+    step.  Returns (rows, the five Linear launches together, block summary)."""
     import ctypes
     from vtpack_b200 import _lib
     from vtpack_b200.models.dge.deit_dge import _pack_block
     from vtpack_b200.runtime import scratch
     blk = model.blocks[len(model.blocks) // 2]
-    C, N = model.embed_dim, (model.img_size // model.patch_size) ** 2 + 1
+    G = model.img_size // model.patch_size
+    C, N = model.embed_dim, G * G + 1
     dtype = model.compute_dtype()
     e = 2 if dtype == torch.bfloat16 else 4
     x = torch.randn(batch, N, C, device=device, generator=torch.Generator(device).manual_seed(3)).to(dtype)
@@ -154,8 +221,10 @@ def stage_profile(model, batch, device, iters, pk):
                                                    stream.cuda_stream))
     torch.cuda.synchronize(device)
     L = int(counts.sum().item())
+    grains = region_grains(x, blk._pack.tensors["gate_w"], blk._pack.tensors["gate_b"], G, device)
+    fine = float((grains == 0).float().mean().item())
     ms = [sum(evs[i][j].elapsed_time(evs[i][j + 1]) for i in range(iters)) / iters for j in range(len(STAGES))]
-    BN, H = batch * N, 4 * C
+    BN, H, HW = batch * N, 4 * C, G * G
     work = {   # (kind, algorithmic bytes or flops)
         # LayerNorm is folded into the GEMM epilogues on the bf16 path: the pool writes comp rows
         # and 8 bytes of statistics per row; there is no LN2 kernel (its slot measures ~0)
@@ -164,43 +233,51 @@ def stage_profile(model, batch, device, iters, pk):
         "kv_proj": ("tensor", 4 * BN * C * C), "attention": ("tensor", 4 * L * N * C),
         "out_proj": ("tensor", 2 * L * C * C), "ln2": ("hbm", 0),
         "fc1_gelu": ("tensor", 2 * L * C * H), "fc2": ("tensor", 2 * L * C * H),
-        "unpool_add": ("hbm", (2 * BN + 2 * L) * C * e),
+        "unpool_add": ("hbm", unpool_rows(batch, HW, L, fine) * C * e),
     }
+    depth = len(model.blocks)
+    fb_ms = front_back_ms(model, batch, device, 4)
+    # inside a model forward the gate and the patch list of blocks 2.. come out of the previous block's unpool
+    in_model = [t for name, t in zip(STAGES, ms) if name not in ("router_gate", "patch_list")]
+    scale = max(ms_per_step - fb_ms, 0.0) / (depth * sum(in_model))
     rows = []
     for name, t in zip(STAGES, ms):
         kind, amount = work[name]
         if amount == 0:
             continue
+        t_est = t * scale
         if kind == "hbm":
-            ach, peak, unit = amount / (t * 1e-3) / 1e9, pk["hbm_gbs"], "GB/s"
+            ach, peak, unit = amount / (t_est * 1e-3) / 1e9, pk["hbm_gbs"], "GB/s"
         else:
-            ach, peak, unit = amount / (t * 1e-3) / 1e12, pk["bf16_tflops_sustained"], "TFLOP/s"
-        rows.append({"kernel": name, "ms": round(t, 4), "bound": kind, "achieved": round(ach, 1), "unit": unit,
-                     "frac": round(ach / peak, 3)})
+            ach, peak, unit = amount / (t_est * 1e-3) / 1e12, pk["bf16_tflops_sustained"], "TFLOP/s"
+        row = {"kernel": name, "ms_event_bracketed": round(t, 4), "ms_in_step_est": round(t_est, 4), "bound": kind,
+               "achieved_in_step_est": round(ach, 1), "unit": unit, "frac_in_step_est": round(ach / peak, 3)}
+        if name in ("router_gate", "patch_list"):
+            row["note"] = "first block of a forward only"
+        rows.append(row)
     gemm = [r for r in rows if r["kernel"] in ("q_proj", "kv_proj", "out_proj", "fc1_gelu", "fc2")]
-    gemm_ms = sum(r["ms"] for r in gemm)
+    gemm_ms = sum(r["ms_event_bracketed"] for r in gemm)
     gemm_flops = sum(work[r["kernel"]][1] for r in gemm)
-    # the dominant kernel is the tcgen05 Linear; its roofline line is its largest launch (kv projection)
-    kv = next(r for r in rows if r["kernel"] == "kv_proj")
-    roof = {"kernel": "linear_tc_kernel, kv projection launch (M=B*N tokens, N=2C, K=C)", "bound": "tensor",
-            "achieved": kv["achieved"], "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
-            "frac": kv["frac"], "traffic": int(NCU_TRAFFIC_BYTES_PER_ROW * BN),
-            "algorithmic_bytes": (BN * C + 2 * C * C + BN * 2 * C) * e,
-            "all_linear_launches": {"achieved": round(gemm_flops / (gemm_ms * 1e-3) / 1e12, 1),
-                                    "frac": round(gemm_flops / (gemm_ms * 1e-3) / 1e12 / pk["bf16_tflops_sustained"], 3),
-                                    "share_of_block": round(gemm_ms / sum(ms), 3)}}
-    t_roof = sum(work[r["kernel"]][1] / ((pk["hbm_gbs"] * 1e9) if r["bound"] == "hbm"
-                                         else (pk["bf16_tflops_sustained"] * 1e12)) for r in rows
-                 if r["kernel"] != "patch_list")
-    return rows, roof, {"queries_per_image": L / batch, "block_ms": round(sum(ms), 4),
-                        "kernel_weighted_roofline_frac": round(t_roof / (sum(ms) * 1e-3), 3)}
+    tf_bracketed = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    tf_step = gemm_flops / (gemm_ms * scale * 1e-3) / 1e12
+    all_linear = {"launches": "q, kv, out, fc1, fc2 projections of one block", "gflop": round(gemm_flops / 1e9, 1),
+                  "achieved_event_bracketed": round(tf_bracketed, 1),
+                  "frac_event_bracketed": round(tf_bracketed / pk["bf16_tflops_sustained"], 3),
+                  "achieved_in_step_est": round(tf_step, 1),
+                  "frac_in_step_est": round(tf_step / pk["bf16_tflops_sustained"], 3),
+                  "peak": pk["bf16_tflops_sustained"], "peak_kind": "sustained cuBLAS bf16 (kernels timed inside a long step)",
+                  "share_of_block": round(gemm_ms / sum(in_model), 3)}
+    return rows, all_linear, {"queries_per_image": L / batch, "fine_region_fraction": round(fine, 3),
+                              "block_ms_event_bracketed": round(sum(in_model), 4),
+                              "block_ms_in_step_est": round(sum(in_model) * scale, 4),
+                              "front_back_ms": round(fb_ms, 4), "depth": depth,
+                              "check": "depth * block_ms_in_step_est + front_back_ms = ms_per_step"}
 
 
 def kv_launch_roofline(model, batch, device, pk, iters=20):
     """The dominant kernel's largest launch on its own: the kv projection (M = batch*N token rows,
     N = 2C, K = C; operands + output exceed L2), `iters` launches back to back between two CUDA
-    events on the launch stream.  The per-stage times of `stage_profile` bracket every launch with
-    event records, which keeps the next launch from being queued behind the running one."""
+    events on the launch stream.  A launch timed on its own is read against the burst cuBLAS figure."""
     from vtpack_b200 import _lib
     lib = _lib.lib()
     C, N = model.embed_dim, (model.img_size // model.patch_size) ** 2 + 1
@@ -228,13 +305,30 @@ def kv_launch_roofline(model, batch, device, pk, iters=20):
     flops = 2.0 * M * 2 * C * C
     ach = flops / (us * 1e-6) / 1e12
     return {"kernel": "linear_tc_kernel, kv projection launch (M=batch*N token rows, N=2C, K=C)", "bound": "tensor",
-            "achieved": round(ach, 1), "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
-            "frac": round(ach / pk["bf16_tflops_sustained"], 3), "traffic": int(NCU_TRAFFIC_BYTES_PER_ROW * M),
+            "achieved": round(ach, 1), "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": round(ach / pk["bf16_tflops"], 3), "peak_kind": "burst cuBLAS bf16 (launch timed on its own)",
+            "frac_of_sustained_peak": round(ach / pk["bf16_tflops_sustained"], 3),
+            "traffic": int(NCU_TRAFFIC_BYTES_PER_ROW * M),
+            "traffic_note": "constant: dram read + write bytes of one launch from the committed ncu capture "
+                            "(profiles/), scaled by the row count; not measured in this run",
             "algorithmic_bytes": (M * C + 2 * C * C + M * 2 * C) * 2, "launch_us": round(us, 2),
-            "timing": f"{iters} launches back to back between two CUDA events; 152 MB per launch at batch 256 (> L2)"}
+            "timing": f"{iters} launches back to back between two CUDA events; "
+                      f"{(M * C + M * 2 * C) * 2 / 1e6:.0f} MB per launch (> L2)"}
 
 
-def model_roofline(model, batch, counts, ms_per_step, pk, image_bytes):
+def fine_fraction(model, img_dev):
+    """Fraction of regions at the finest grain in each block of a forward (from the grain trace)."""
+    keep = model.trace
+    model.trace = "grains"
+    model(img_dev)
+    torch.cuda.synchronize(img_dev.device)
+    f = (model.last_grains == 0).float().mean(dim=(1, 2)).cpu().tolist()
+    model.trace = keep
+    model.last_grains = None
+    return f
+
+
+def model_roofline(model, batch, counts, ms_per_step, pk, image_bytes, fine):
     """Sum over the launches of one forward of the time the roofline allows each of them (the larger of
     flops / measured tensor peak and algorithmic bytes / measured copy bandwidth), against the measured step."""
     C, HW = model.embed_dim, (model.img_size // model.patch_size) ** 2
@@ -249,9 +343,11 @@ def model_roofline(model, batch, counts, ms_per_step, pk, image_bytes):
     for i in range(len(model.blocks)):
         L = float(counts[i].sum())
         t += (BN + L) * C * e / hbm + gemm(L, C, C) + gemm(BN, 2 * C, C) + gemm(L, C, C) + gemm(L, H, C) + gemm(L, C, H)
-        t += max(4.0 * L * N * C / tf, (2 * L * C + BN * 2 * C) * e / hbm) + (2 * BN + 2 * L) * C * e / hbm
+        t += max(4.0 * L * N * C / tf, (2 * L * C + BN * 2 * C) * e / hbm) + unpool_rows(batch, HW, L, fine[i]) * C * e / hbm
     return {"roofline_ms": round(t * 1e3, 4), "measured_ms": round(ms_per_step, 4), "frac": round(t * 1e3 / ms_per_step, 3),
-            "note": "kernel-weighted: sum of per-launch roofline times of one forward / measured ms_per_step"}
+            "fine_region_fraction": round(sum(fine) / len(fine), 3),
+            "note": "kernel-weighted: sum of per-launch roofline times of one forward / measured ms_per_step; "
+                    "unpool bytes are what the kernel moves (fine regions read neither ref nor comp)"}
 
 
 def launches_per_forward(model):
@@ -562,6 +658,28 @@ def train_ops_sweep(args):
                       "peaks": pk_kind}), flush=True)
 
 
+def h2d_rate_gbs(nbytes, device, world, iters=5):
+    """GB/s of a pinned host-to-device copy of one step's images, every rank copying at the same time
+    (max time over ranks): what the end-to-end leg's input traffic can reach on this host."""
+    import torch.distributed as dist
+    src = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    dst.copy_(src, non_blocking=True)
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        dst.copy_(src, non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return nbytes / (float(ms.item()) * 1e-3) / 1e9
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -570,12 +688,16 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--model", default="small", choices=["tiny", "small", "base"])
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
+    ap.add_argument("--img-size", type=int, default=256, help="input side in pixels (512: 32x32 tokens, 64 regions)")
+    ap.add_argument("--gate-skew", default="none", choices=["none", "alternate"],
+                    help="alternate: even images forced all-coarse, odd all-fine (per-image gate bias of 1e4)")
     ap.add_argument("--cpu-batch", type=int, default=8, help="images per step of the CPU arm")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
     ap.add_argument("--cuda-cores", action="store_true", help="bf16: CUDA-core GEMM/attention instead of tcgen05")
     ap.add_argument("--no-graph", action="store_true", help="launch kernel by kernel instead of replaying a CUDA graph")
-    ap.add_argument("--host-image-dtype", default="bf16", choices=["bf16", "f32"],
-                    help="element type of the pinned host images of the end-to-end leg")
+    ap.add_argument("--host-image-dtype", default="f32", choices=["bf16", "f32"],
+                    help="element type of the pinned host images of the end-to-end leg (f32: what the reference's "
+                         "data loader hands over)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-stage-profile", action="store_true")
     ap.add_argument("--profile", default=None, choices=["linear_kv", "attention", "block", "train_ops"],
@@ -605,7 +727,7 @@ def main():
 
     import torch.distributed as dist
     from vtpack_b200 import _lib, parallel, synthetic
-    from vtpack_b200.serve import HostPipeline
+    from vtpack_b200.serve import HostPipeline, LogitsGather
 
     rank, world, local = parallel.init_from_env("nccl")
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
@@ -613,25 +735,34 @@ def main():
     torch.cuda.set_device(device)
     _lib.lib()                                       # fails loudly if the CUDA library is missing
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
-    model = synthetic.build_model(args.model, device, dtype)
+    S = args.img_size
+    model = synthetic.build_model(args.model, device, dtype, img_size=S)
     if args.cuda_cores:
         model.flags = _lib.FLAG_CUDA_CORES
     B = args.batch
-    img_dev = synthetic.images(B, 256, seed=1 + rank).to(device)          # 201 MB at B=256: larger than L2
-    logits = torch.empty(B, 1000, device=device)
-    gathered = torch.empty(world * B, 1000, device=device) if world > 1 else None
+    if args.gate_skew == "alternate":
+        model.gate_image_bias = alternate_gate_bias(B).to(device)
+    img_dev = synthetic.images(B, S, seed=1 + rank).to(device)          # 201 MB at B=256, 256 px: larger than L2
+    # the logits leave on a side stream (all-gather when there are several ranks), double-buffered, so the
+    # collective of step i runs under the forward of step i+1
+    out = LogitsGather(B, 1000, device, world=world)
 
     use_graph = not args.no_graph
+    step_no = [0]
 
     def step():
+        slot = step_no[0] & 1
+        step_no[0] += 1
+        out.reusable(slot)
         if use_graph:
-            model.forward_graph(img_dev, logits)
+            model.forward_graph(img_dev, out.local[slot])
         else:
-            model(img_dev, logits_out=logits)
+            model(img_dev, logits_out=out.local[slot])
         if world > 1:
-            dist.all_gather_into_tensor(gathered, logits)
+            out.start(slot)
 
     def barrier():
+        out.wait_all()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(device)
@@ -647,22 +778,26 @@ def main():
     e0.record()
     for _ in range(args.steps):
         step()
+    out.wait_all()                                   # the last gathers are inside the timed region
     e1.record()
     barrier()
-    ms_total = torch.tensor([e0.elapsed_time(e1)], device=device)
+    ms_rank = e0.elapsed_time(e1)
+    ms_all = torch.tensor([ms_rank], device=device)
+    ms_min = ms_all.clone()
     if world > 1:
-        dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
-    ms_total = float(ms_total.item())
+        dist.all_reduce(ms_all, op=dist.ReduceOp.MAX)
+        dist.all_reduce(ms_min, op=dist.ReduceOp.MIN)
+    ms_total = float(ms_all.item())
     value = world * B * args.steps / (ms_total * 1e-3)
+    counts_cpu = model.last_counts.cpu()
 
     # end to end: pinned host images -> device -> forward -> (gather) -> host logits, copies overlapped
     host_dt = torch.bfloat16 if (args.host_image_dtype == "bf16" and dtype == torch.bfloat16) else torch.float32
-    pipe = HostPipeline(model, B, 256, device, world=world, image_dtype=host_dt, use_graph=use_graph)
-    host = [synthetic.images(B, 256, seed=100 + rank + 7 * i).to(host_dt).pin_memory() for i in range(2)]
+    pipe = HostPipeline(model, B, S, device, world=world, image_dtype=host_dt, use_graph=use_graph)
+    host = [synthetic.images(B, S, seed=100 + rank + 7 * i).to(host_dt).pin_memory() for i in range(2)]
     batches = [host[i & 1] for i in range(args.steps)]
     pipe.run(batches[:max(args.warmup, 3)])
     barrier()
-    t0 = time.perf_counter()
     e0.record()
     pipe.run(batches)
     e1.record()
@@ -671,15 +806,16 @@ def main():
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_value = world * B * args.steps / (float(e2e_ms.item()) * 1e-3)
-    _ = t0
     clocks = sampler.stop() if sampler else None
+    h2d_gbs = h2d_rate_gbs(pipe.h2d_bytes, device, world)
     # the same leg with the host images in the other element type (1 GPU only, to keep multi-GPU runs short):
     # fp32 is what the reference's data loader hands over, bf16 is what this model rounds the pixels to anyway
     e2e_other = None
     if world == 1 and dtype == torch.bfloat16:
         other_dt = torch.float32 if host_dt == torch.bfloat16 else torch.bfloat16
-        pipe2 = HostPipeline(model, B, 256, device, world=world, image_dtype=other_dt, use_graph=use_graph)
-        host2 = [synthetic.images(B, 256, seed=200 + 7 * i).to(other_dt).pin_memory() for i in range(2)]
+        del pipe
+        pipe2 = HostPipeline(model, B, S, device, world=world, image_dtype=other_dt, use_graph=use_graph)
+        host2 = [synthetic.images(B, S, seed=200 + 7 * i).to(other_dt).pin_memory() for i in range(2)]
         batches2 = [host2[i & 1] for i in range(args.steps)]
         pipe2.run(batches2[:3])
         torch.cuda.synchronize(device)
@@ -690,39 +826,55 @@ def main():
         e2e_other = {"host_images": str(other_dt).replace("torch.", ""),
                      "value": B * args.steps / (e0.elapsed_time(e1) * 1e-3), "unit": "images/s",
                      "h2d_bytes_per_step": pipe2.h2d_bytes}
+        h2d_bytes, d2h_bytes = B * 3 * S * S * host[0].element_size(), B * 1000 * 4
+    else:
+        h2d_bytes, d2h_bytes = pipe.h2d_bytes, pipe.d2h_bytes
     status = _lib.device_status()
 
     if rank == 0:
         pk, pk_src = peaks()
+        skew = ", even images all-coarse / odd all-fine" if args.gate_skew == "alternate" else \
+            " (budget 0.5 stand-in: free-running random-init gate)"
         line = {
             "metric": "images/sec", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
-            "config": {"workload": f"DeiT-{args.model}+DGE s124 (budget 0.5 stand-in: free-running random-init gate) "
-                                   f"256px eval forward, batch {B}/GPU, logits all-gathered",
+            "config": {"workload": f"DeiT-{args.model}+DGE s124{skew} {S}px eval forward, batch {B}/GPU, "
+                                   f"logits all-gathered",
                        "batch_per_gpu": B, "global_batch": B * world, "parallelism": f"dp{world}",
-                       "l2": "inputs larger than L2 (fp32 images 201 MB/step at B=256)",
-                       "cuda_graph": use_graph, "e2e_host_images": str(host_dt).replace("torch.", "")},
-            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": pipe.h2d_bytes,
-                    "d2h_bytes_per_step": pipe.d2h_bytes},
+                       "img_size": S, "gate_skew": args.gate_skew,
+                       "queries_per_image": round(float(counts_cpu.float().mean()), 1),
+                       "l2": f"inputs larger than L2 (fp32 images {B * 3 * S * S * 4 / 1e6:.0f} MB/step)",
+                       "cuda_graph": use_graph, "e2e_host_images": str(host_dt).replace("torch.", ""),
+                       "logits_gather": "side stream, double-buffered" if world > 1 else "single rank: none"},
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": d2h_bytes,
+                    "h2d_copy_alone_gbs_per_gpu": round(h2d_gbs, 1),
+                    "h2d_note": "pinned-host-to-device copy of one step's images with nothing else running, all "
+                                "ranks at once, max over ranks"},
             # per forward: im2col, cls rows, patch-embed GEMM, final LayerNorm, head GEMM, first block's gate,
             # and per block: count, patch list, pool, 5 GEMMs, attention, unpool
             "gpu_launches": args.steps * launches_per_forward(model),
             "clocks": clocks, "device_status": status, "peaks": pk_src,
+            "rank_step_ms": {"max": ms_total / args.steps, "min": float(ms_min.item()) / args.steps},
         }
         if e2e_other:
             line["e2e_other_host_dtype"] = e2e_other
         if dtype == torch.bfloat16 and not args.cuda_cores:
             line["roofline"] = kv_launch_roofline(model, B, device, pk)
-            line["model_roofline"] = model_roofline(model, B, model.last_counts.cpu(), ms_total / args.steps, pk,
-                                                    img_dev.element_size())
-        if not args.no_stage_profile and dtype == torch.bfloat16:
-            rows, roof, extra = stage_profile(model, B, device, 10, pk)
-            line["roofline"]["all_linear_launches_of_a_block"] = roof["all_linear_launches"]
+            line["model_roofline"] = model_roofline(model, B, counts_cpu, ms_total / args.steps, pk,
+                                                    img_dev.element_size(), fine_fraction(model, img_dev))
+        if not args.no_stage_profile and dtype == torch.bfloat16 and not args.cuda_cores:
+            rows, all_linear, extra = stage_profile(model, B, device, 10, pk, ms_total / args.steps)
+            line["roofline"]["all_linear_launches_of_a_block"] = all_linear
+            line["roofline"]["frac_all_launches"] = all_linear["frac_in_step_est"]
             line["kernels"] = rows
+            line["kernels_note"] = ("ms_event_bracketed: every stage sits between two event records, which keeps the "
+                                    "next launch from queueing behind the running one: an upper bound. ms_in_step_est "
+                                    "= that share scaled so that depth x block + front/back equals ms_per_step")
             line["block"] = extra
         if world == 1 and not args.no_cpu_baseline:
-            rate, ms, cores = cpu_reference_rate(args.model, args.cpu_batch, 3, 1)
+            rate, ms, cores = cpu_reference_rate(args.model, args.cpu_batch, 3, 1, S, args.gate_skew)
             line["cpu_baseline"] = {"value": rate, "unit": "images/s", "cores": cores, "kind": "port",
                                     "sample": f"3 forwards of {args.cpu_batch} images after 1 warm-up, fp32 torch CPU"}
         print(json.dumps(line), flush=True)

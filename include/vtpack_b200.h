@@ -331,6 +331,8 @@ typedef struct {
     int sr_ratio;    /* 0 or 1: keys = tokens (DeiT).  > 1: PVT spatial reduction, needs num_extra = 0,
                         H and W multiples of it; the block then has H*W/sr^2 keys per image */
     float sr_eps;    /* epsilon of the LayerNorm after the reduction */
+    float attn_scale; /* softmax scale of the attention (Attention.scale = qk_scale or head_dim^-0.5,
+                         vtpack/models/dge/deit_dge.py:52-53); 0 selects head_dim^-0.5 */
 } vtp_dge_shape;
 
 /* Scratch bytes vtp_dge_block_forward needs for this shape (16-byte aligned slices). */
@@ -389,6 +391,29 @@ int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weights* m,
                          const vtp_block_weights* blocks, const void* images, float* logits,
                          int32_t* counts_out, void* workspace, long long workspace_bytes,
                          void* stream);
+
+/* Optional inputs and outputs of vtp_deit_dge_forward_ex; every pointer may be null. */
+typedef struct {
+    /* fp32 [B, n_splits], added to the router logits of every region of image b in every block before the
+     * argmax.  Large offsets force an image to one grain whatever its content: the measurement
+     * configuration with half the images all-coarse and half all-fine is set up this way.  The reference
+     * has one gate bias per grain for all images (vtpack/layers/dge.py:125). */
+    const float* gate_image_bias;
+    /* model dtype [depth, B, N, C]: the tokens each block received (block 0: patch embedding + position) */
+    void* tokens_trace;
+    /* int32 [depth, B, (H/region)*(W/region)]: the grain index each block's gate chose per region */
+    int32_t* grain_trace;
+} vtp_forward_options;
+
+/*
+ * vtp_deit_dge_forward with the options above (opt may be null).  The traces let a test feed the
+ * reference's router (vtpack/layers/dge.py:61-76,145-150) the very activations the device gate saw and
+ * compare decisions layer by layer; they cost one device-to-device copy per block.
+ */
+int vtp_deit_dge_forward_ex(const vtp_dge_shape* s, const vtp_model_weights* m,
+                            const vtp_block_weights* blocks, const void* images, float* logits,
+                            int32_t* counts_out, const vtp_forward_options* opt, void* workspace,
+                            long long workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

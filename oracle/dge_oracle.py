@@ -230,7 +230,10 @@ def dge_block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], num_heads: in
                       split_sizes: Sequence[int], eps: float = 1e-6,
                       forced_gate: Optional[torch.Tensor] = None,
                       trace: Optional[dict] = None, grid: Optional[Tuple[int, int]] = None,
-                      sr_ratio: int = 1, sr_eps: float = 1e-5) -> torch.Tensor:
+                      sr_ratio: int = 1, sr_eps: float = 1e-5,
+                      gate_image_bias: Optional[torch.Tensor] = None,
+                      qk_scale: Optional[float] = None,
+                      forced_indices: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Eval forward of one DeiT+DGE block, or of one PVT+DGE block when ``grid`` / ``sr_ratio``
     are given.
 
@@ -244,7 +247,12 @@ def dge_block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], num_heads: in
     ``Attention.forward`` (``deit_dge.py:70-98``) and ``Mlp.forward`` (``:38-44``).
     ``w`` uses the reference's state_dict keys relative to the block
     (``norm1.weight``, ``attn.q.weight``, ``dge.router.gate.weight`` ...).
-    ``forced_gate`` replaces the router output (teacher forcing).
+    ``forced_gate`` replaces the router output (teacher forcing).  ``gate_image_bias``
+    (``[B, n_splits]``) is added to the router output of every region of image b: the reference
+    has no such input, measurement configurations that force whole images to one grain do
+    (large offsets).  ``qk_scale`` overrides ``head_dim ** -0.5`` (``deit_dge.py:52-53``).
+    ``forced_indices`` (int ``[B, Hr, Wr]``) replaces the argmax of the gate: the block then follows
+    grain decisions made elsewhere (e.g. by the device on its bf16 activations).
     """
     B, N, C = x.shape
     if grid is None:
@@ -261,13 +269,15 @@ def dge_block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], num_heads: in
                               w["dge.router.gate.weight"], w["dge.router.gate.bias"], region)
     else:
         gate = forced_gate
-    indices = gate.argmax(dim=-1)
+    if gate_image_bias is not None:
+        gate = gate + gate_image_bias[:, None, None, :]
+    indices = gate.argmax(dim=-1) if forced_indices is None else forced_indices.to(torch.int64)
     patches, batches = grained_sample_index_to_patch(indices, splits, region, num_extra)
     comp = grained_sample_compress(x, patches, H, W, num_extra)
 
     # attention ------------------------------------------------------------
     d = C // num_heads
-    scale = d ** -0.5
+    scale = qk_scale or d ** -0.5
     xn = F.layer_norm(x, (C,), w["norm1.weight"], w["norm1.bias"], eps)
     qn = F.layer_norm(comp, (C,), w["norm1.weight"], w["norm1.bias"], eps)
     q = F.linear(qn, w["attn.q.weight"], w.get("attn.q.bias")).reshape(-1, num_heads, d).permute(1, 0, 2)
@@ -329,7 +339,10 @@ def block_weights(sd: Dict[str, torch.Tensor], i: int) -> Dict[str, torch.Tensor
 
 def deit_dge_forward(images: torch.Tensor, sd: Dict[str, torch.Tensor], depth: int,
                      num_heads: int, split_sizes: Sequence[int], patch: int = 16,
-                     eps: float = 1e-6, trace: Optional[List[dict]] = None) -> torch.Tensor:
+                     eps: float = 1e-6, trace: Optional[List[dict]] = None,
+                     gate_image_bias: Optional[torch.Tensor] = None,
+                     features: Optional[list] = None,
+                     forced_indices: Optional[Sequence[torch.Tensor]] = None) -> torch.Tensor:
     """Eval forward of DeiT+DGE, images ``[B,3,S,S] -> logits [B,classes]``.
 
     Follows ``VisionTransformer.forward_features/forward``
@@ -343,10 +356,16 @@ def deit_dge_forward(images: torch.Tensor, sd: Dict[str, torch.Tensor], depth: i
     x = torch.cat((cls, x), dim=1) + sd["pos_embed"]
     for i in range(depth):
         t = {} if trace is not None else None
-        x = dge_block_forward(x, block_weights(sd, i), num_heads, split_sizes, eps, trace=t)
+        if t is not None:
+            t["x_in"] = x
+        x = dge_block_forward(x, block_weights(sd, i), num_heads, split_sizes, eps, trace=t,
+                              gate_image_bias=gate_image_bias,
+                              forced_indices=None if forced_indices is None else forced_indices[i])
         if trace is not None:
             trace.append(t)
     x = F.layer_norm(x, (x.shape[-1],), sd["norm.weight"], sd["norm.bias"], eps)
+    if features is not None:
+        features.append(x[:, 0])          # the normed cls rows the head reads
     return F.linear(x[:, 0], sd["head.weight"], sd["head.bias"])
 
 

@@ -38,11 +38,20 @@ def test_cuda_arm_line():
     assert d["metric"] == "images/sec" and d["dtype"] == "bf16" and d["n_gpus"] == 1 and d["scaling"] == "weak"
     assert d["value"] > 0 and d["vs_baseline"] is None and d["device_status"] == 0
     assert 0 < d["e2e"]["value"] <= d["value"] * 1.05
-    assert d["e2e"]["h2d_bytes_per_step"] == 32 * 3 * 256 * 256 * 2 and d["e2e"]["d2h_bytes_per_step"] == 32 * 1000 * 4
+    # host images are fp32 by default (what the reference's loader hands over); bf16 is the secondary figure
+    assert d["e2e"]["h2d_bytes_per_step"] == 32 * 3 * 256 * 256 * 4 and d["e2e"]["d2h_bytes_per_step"] == 32 * 1000 * 4
+    assert d["config"]["e2e_host_images"] == "float32" and d["e2e_other_host_dtype"]["host_images"] == "bfloat16"
     assert d["gpu_launches"] == 3 * (9 + 8 * 12)
     rf = d["roofline"]
     assert rf["bound"] == "tensor" and rf["unit"] == "TFLOP/s" and rf["peak"] > 0
     assert abs(rf["frac"] - rf["achieved"] / rf["peak"]) < 2e-3 and rf["traffic"] > 0
+    assert 0 < rf["frac_all_launches"] < 1.5
+    # the per-kernel estimates add up to the measured step
+    blk = d["block"]
+    assert abs(blk["depth"] * blk["block_ms_in_step_est"] + blk["front_back_ms"] - d["ms_per_step"]) < 0.02 * d["ms_per_step"]
+    in_model = sum(k["ms_in_step_est"] for k in d["kernels"] if "note" not in k)
+    assert abs(in_model - blk["block_ms_in_step_est"]) < 0.03 * blk["block_ms_in_step_est"] + 0.002   # rounded to 1e-4 ms
+    assert 0 < d["model_roofline"]["frac"] < 1.5
     cb = d["cpu_baseline"]
     assert cb["kind"] == "port" and cb["value"] > 0 and cb["cores"] >= 1
     assert {"sm_mhz", "sm_max_mhz", "reasons"} <= set(d["clocks"])

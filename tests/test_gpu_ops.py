@@ -285,3 +285,87 @@ def test_linear_bf16_narrow_reduction_uses_cuda_cores(vl):
     _lib, _ = vl
     got, ref = _linear_case(500, 64, 48, torch.bfloat16, False, False, 0)
     assert rel_err(got.float(), ref) < 8e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_patch_rows_outside_the_declared_shape_are_skipped(vl, dtype):
+    """A patch row whose image index or coordinates do not fit the declared [B, N] token array is skipped
+    and a code is left in the device status word.  The buffers here are allocated for 4 images and the
+    calls declare 2, so the bad rows (image 3; a 4x4 patch starting at column 14 of a 16-wide grid) still
+    point inside memory this test owns: even a missing guard could not touch anything else."""
+    _lib, _ = vl
+    lib = _lib.lib()
+    B_alloc, B, G, C = 4, 2, 16, 64
+    N = G * G + 1
+    code = 0 if dtype == torch.float32 else 1
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(B_alloc, N, C, generator=g).to(dtype).to(DEV)
+    good = [[0, -1, 0, 1], [0, 0, 0, 4], [1, 4, 8, 2], [1, 15, 15, 1]]
+    bad = [[3, 0, 0, 4], [1, 0, 14, 4], [1, 14, 0, 4], [0, -2, 0, 1], [-1, 0, 0, 1], [0, 0, 0, 0]]
+    rows = torch.tensor(good[:2] + bad[:3] + good[2:] + bad[3:], dtype=torch.int32, device=DEV)
+    L = rows.shape[0]
+    is_good = torch.tensor([r in good for r in rows.tolist()])
+    assert _lib.device_status() == 0
+    comp = torch.full((L, C), 7.0, dtype=dtype, device=DEV)
+    _lib.check(lib.vtp_pool(x.data_ptr(), code, B, N, C, G, 1, rows.data_ptr(), None, L, comp.data_ptr(), None, None,
+                            0.0, None, None, None))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 64
+    ref = O.grained_sample_compress(x[:B].cpu(), rows.cpu().long()[is_good], G, G, 1)
+    assert torch.equal(comp.cpu()[is_good], ref)
+    assert bool((comp.cpu()[~is_good] == 7.0).all())            # skipped rows were not written
+    out = torch.full((B_alloc, N, C), 5.0, dtype=dtype, device=DEV)
+    q = torch.randn(L, C, generator=g).to(dtype).to(DEV)
+    _lib.check(lib.vtp_unpool_add(q.data_ptr(), None, code, B, N, C, G, 1, rows.data_ptr(), None, L, None,
+                                  out.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 64
+    assert bool((out[B:] == 5.0).all())                          # nothing beyond the declared images
+    touched = (out[:B] != 5.0).any(-1).cpu()
+    expect = torch.zeros(B, N, dtype=torch.bool)
+    expect[0, 0] = True
+    expect[0, 1:].view(G, G)[0:4, 0:4] = True
+    expect[1, 1:].view(G, G)[4:6, 8:10] = True
+    expect[1, 1:].view(G, G)[15, 15] = True
+    assert torch.equal(touched, expect)
+    # a later tensor-core launch still runs: the bad-index code does not void launches the way a timed-out wait does
+    a = torch.randn(256, 64, generator=g).bfloat16().to(DEV)
+    w = torch.randn(64, 64, generator=g).bfloat16().to(DEV)
+    y = torch.zeros(256, 64, dtype=torch.bfloat16, device=DEV)
+    _lib.check(lib.vtp_pool(x.data_ptr(), code, B, N, C, G, 1, rows.data_ptr(), None, L, comp.data_ptr(), None, None,
+                            0.0, None, None, None))
+    _lib.check(lib.vtp_linear(a.data_ptr(), 64, w.data_ptr(), None, None, 0, y.data_ptr(), 64, 1, 256, None, 64, 64,
+                              0, None))
+    torch.cuda.synchronize()
+    assert rel_err(y.float(), a.float() @ w.float().t()) < 1e-2
+    assert _lib.device_status() == 64
+
+
+def test_attention_offsets_beyond_the_buffers_are_clamped(vl):
+    """Offsets that claim more packed rows than q / out hold (offsets[B] > l_max): the rows that exist are
+    computed, nothing at or beyond l_max is written, and the status word carries the bad-index code.  The
+    out buffer is allocated larger than declared so the check itself stays inside owned memory."""
+    _lib, _ = vl
+    lib = _lib.lib()
+    B, N, h, d = 2, 65, 2, 64
+    C = h * d
+    l_max, l_alloc = 40, 128
+    g = torch.Generator().manual_seed(41)
+    q = torch.randn(l_alloc, C, generator=g).bfloat16().to(DEV)
+    kv = torch.randn(B, N, 2 * C, generator=g).bfloat16().to(DEV)
+    off = torch.tensor([0, 30, 70], dtype=torch.int32, device=DEV)       # image 1 claims rows 30..69
+    for flags in (0, _lib.FLAG_CUDA_CORES):
+        out = torch.full((l_alloc, C), 3.0, dtype=torch.bfloat16, device=DEV)
+        assert _lib.device_status() == 0
+        _lib.check(lib.vtp_sparse_attention(q.data_ptr(), C, d, kv.data_ptr(), kv.data_ptr() + C * 2, N * 2 * C, 2 * C,
+                                            d, out.data_ptr(), C, d, 1, B, N, h, d, off.data_ptr(), l_max, 64,
+                                            d ** -0.5, flags, None))
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 64
+        assert bool((out[l_max:] == 3.0).all())
+        k = kv[..., :C].reshape(B, N, h, d).permute(2, 0, 1, 3).float().cpu()
+        v = kv[..., C:].reshape(B, N, h, d).permute(2, 0, 1, 3).float().cpu()
+        qh = q[:l_max].reshape(l_max, h, d).permute(1, 0, 2).float().cpu()
+        ref = O.batched_sparse_attention_forward(qh, k, v, torch.tensor([30, 10]), d ** -0.5)
+        got = out[:l_max].reshape(l_max, h, d).permute(1, 0, 2).float().cpu()
+        assert rel_err(got, ref) < 2e-2

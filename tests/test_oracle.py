@@ -329,3 +329,20 @@ def test_bilinear_attention_golden_and_autograd(golden_dir, mode):
     far = grid.clone()
     far[..., 0] = -1.5
     assert not fwd(inp, far, weight).any()
+
+
+def test_forced_indices_and_image_bias_hooks():
+    """The two hooks the parity tests and the bench use change nothing when they restate what the oracle
+    does anyway, and force what they say when they do not."""
+    sd = O.make_state_dict(192, 2, 3, seed=0)
+    img = O.make_images(2, 256, seed=1)
+    tr = []
+    ref = O.deit_dge_forward(img, sd, 2, 3, (4, 2, 1), trace=tr)
+    same = O.deit_dge_forward(img, sd, 2, 3, (4, 2, 1), forced_indices=[t["indices"] for t in tr])
+    assert torch.equal(ref, same)
+    bias = torch.zeros(2, 3)
+    bias[0, 2] = 1e4            # image 0 all-coarse
+    bias[1, 0] = 1e4            # image 1 all-fine
+    tr2 = []
+    O.deit_dge_forward(img, sd, 2, 3, (4, 2, 1), trace=tr2, gate_image_bias=bias)
+    assert all(t["batches"].tolist() == [17, 257] for t in tr2)

@@ -61,6 +61,35 @@ def test_static_scratch_matches_caller_scratch_twice():
         assert 17 * B <= L <= 257 * B
         assert torch.equal(offsets.cpu(), ref_off)                 # integer work: bit-exact
         assert torch.equal(patches.cpu()[:L], ref_pat[:L])
+        # and against the CPU oracle: the reference's router on the same bf16 tokens, then its patch list
+        from oracle import dge_oracle as O
+        logits = O.router_forward(x.float().cpu()[:, 1:].reshape(B, G, G, C), gw.cpu(), gb.cpu(), 4)
+        top2 = logits.topk(2, -1).values
+        assert float((top2[..., 0] - top2[..., 1]).min()) > 1e-5   # no near-tie in these inputs
+        o_pat, o_len = O.grained_sample_index_to_patch(logits.argmax(-1), torch.tensor([4, 2, 1]), 4, 1)
+        assert torch.equal(offsets.cpu().long()[1:] - offsets.cpu().long()[:-1], o_len)
+        assert torch.equal(patches.cpu()[:L].long(), o_pat)
+
+
+@pytest.mark.gpu
+def test_static_scratch_at_its_limits():
+    """Exactly 4096 images and 65536 regions (16 x 16 tokens, 4 x 4 regions, 8 channels): both halves of the
+    fixed array are used to their last entry, and the result equals the caller-scratch path."""
+    from vtpack_b200 import _lib
+    lib = _lib.lib()
+    B, G, C = 4096, 16, 8
+    splits = (ctypes.c_int * 3)(4, 2, 1)
+    x, gw, gb = _inputs(23, B, G, C)
+    x, gw, gb = x.to(DEV), gw.to(DEV), gb.to(DEV)
+    ref_off, ref_pat = _reference_path(lib, _lib, x, gw, gb, B, G, C)
+    offsets = torch.empty(B + 1, dtype=torch.int32, device=DEV)
+    patches = torch.zeros(B * (G * G + 1), 4, dtype=torch.int32, device=DEV)
+    _lib.check(lib.vtp_gate_compact_static(x.data_ptr(), 1, B, G, G, C, 1, 4, gw.data_ptr(), gb.data_ptr(),
+                                           splits, 3, offsets.data_ptr(), patches.data_ptr(), None))
+    torch.cuda.synchronize()
+    L = int(ref_off[-1])
+    assert torch.equal(offsets.cpu(), ref_off)
+    assert torch.equal(patches.cpu()[:L], ref_pat[:L])
 
 
 def test_static_scratch_rejects_oversized_calls():
@@ -74,3 +103,14 @@ def test_static_scratch_rejects_oversized_calls():
     assert b"exceed the static scratch" in lib.vtp_last_error_string()
     assert lib.vtp_gate_compact_static(p, 1, 4096, 32, 32, 384, 1, 4, p, p, splits, 3, p, p, None) == -2
     assert lib.vtp_gate_compact_static(None, 1, 2, 16, 16, 384, 1, 4, p, p, splits, 3, p, p, None) == -1
+    # everything the two underlying calls would reject is rejected up front, before the first launch:
+    # more than 8192 regions in one image, a split that does not divide the region, an unknown dtype,
+    # rows that are not whole 16-byte chunks, an unaligned pointer
+    assert lib.vtp_gate_compact_static(p, 1, 1, 512, 512, 384, 1, 4, p, p, splits, 3, p, p, None) == -2
+    assert b"8192" in lib.vtp_last_error_string()
+    bad_splits = (ctypes.c_int * 3)(4, 3, 1)
+    assert lib.vtp_gate_compact_static(p, 1, 2, 16, 16, 384, 1, 4, p, p, bad_splits, 3, p, p, None) == -2
+    assert lib.vtp_gate_compact_static(p, 9, 2, 16, 16, 384, 1, 4, p, p, splits, 3, p, p, None) == -3
+    assert lib.vtp_gate_compact_static(p, 1, 2, 16, 16, 60, 1, 4, p, p, splits, 3, p, p, None) == -2
+    q = ctypes.c_void_p(4100)
+    assert lib.vtp_gate_compact_static(q, 1, 2, 16, 16, 384, 1, 4, p, p, splits, 3, p, p, None) == -4

@@ -27,7 +27,7 @@ class DgeShape(C.Structure):
     _fields_ = [("dtype", c_int), ("B", c_int), ("H", c_int), ("W", c_int), ("num_extra", c_int),
                 ("C", c_int), ("heads", c_int), ("hidden", c_int), ("region", c_int),
                 ("n_splits", c_int), ("splits", c_int * 8), ("eps", c_float), ("flags", c_uint),
-                ("sr_ratio", c_int), ("sr_eps", c_float)]
+                ("sr_ratio", c_int), ("sr_eps", c_float), ("attn_scale", c_float)]
 
 
 class ModelWeights(C.Structure):
@@ -35,6 +35,10 @@ class ModelWeights(C.Structure):
                 ("pos_embed", c_void_p), ("norm_w", c_void_p), ("norm_b", c_void_p),
                 ("head_w", c_void_p), ("head_b", c_void_p), ("depth", c_int), ("patch", c_int),
                 ("img_size", c_int), ("num_classes", c_int), ("image_dtype", c_int)]
+
+
+class ForwardOptions(C.Structure):
+    _fields_ = [("gate_image_bias", c_void_p), ("tokens_trace", c_void_p), ("grain_trace", c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/vtpack_b200.h declares
@@ -92,6 +96,9 @@ PROTOTYPES = {
     "vtp_model_workspace_bytes": (c_ll, [C.POINTER(DgeShape), C.POINTER(ModelWeights)]),
     "vtp_deit_dge_forward": (c_int, [C.POINTER(DgeShape), C.POINTER(ModelWeights), C.POINTER(BlockWeights),
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p]),
+    "vtp_deit_dge_forward_ex": (c_int, [C.POINTER(DgeShape), C.POINTER(ModelWeights), C.POINTER(BlockWeights),
+                                        c_void_p, c_void_p, c_void_p, C.POINTER(ForwardOptions), c_void_p, c_ll,
+                                        c_void_p]),
 }
 
 _lib = None

@@ -10,6 +10,7 @@
 // (vtpack/layers/csrc/batched_sparse_gemm/batched_sparse_gemm.cu:219-305): scale is applied
 // to Q K^T before the softmax exactly as the reference passes it as the GEMM alpha (:275).
 #include "attention.h"
+#include "runtime.h"
 
 namespace vtp {
 
@@ -22,7 +23,7 @@ __global__ void __launch_bounds__(128)
 attn_simt_kernel(const T* __restrict__ q, long long q_rs, long long q_hs, const T* __restrict__ k,
                  const T* __restrict__ v, long long kv_bs, long long kv_rs, long long kv_hs,
                  T* __restrict__ out, long long o_rs, long long o_hs, int n_keys, int n_keys_pad,
-                 const int32_t* __restrict__ offsets, float scale) {
+                 const int32_t* __restrict__ offsets, int l_max, float scale, int* status) {
     extern __shared__ float smem[];
     float* Qs = smem;                       // [AQ][AD]
     float* KV = Qs + AQ * AD;               // [AKC][AD + 1]
@@ -31,7 +32,15 @@ attn_simt_kernel(const T* __restrict__ q, long long q_rs, long long q_hs, const 
 
     const int b = blockIdx.z, h = blockIdx.y;
     const int row0 = __ldg(offsets + b) + blockIdx.x * AQ;
-    const int row_end = __ldg(offsets + b + 1);
+    int row_end = __ldg(offsets + b + 1);
+#if VTP_INDEX_GUARDS
+    // caller-supplied offsets: rows outside [0, l_max) are not touched
+    if (row0 < 0 || row_end > l_max) {
+        if (threadIdx.x == 0 && status) atomicOr(status, STATUS_BAD_INDEX);
+        if (row0 < 0) return;
+        row_end = l_max;
+    }
+#endif
     if (row0 >= row_end) return;
     const int nq = min(AQ, row_end - row0);
     const int tid = threadIdx.x;
@@ -108,6 +117,7 @@ attn_simt_kernel(const T* __restrict__ q, long long q_rs, long long q_hs, const 
 
 int attention_cuda_cores(const AttnArgs& p, cudaStream_t st) {
     VTP_REQUIRE(p.head_dim == AD, VTP_ERR_UNSUPPORTED, "attention: head_dim %d (only %d)", p.head_dim, AD);
+    VTP_REQUIRE(p.B <= 65535 && p.heads <= 65535, VTP_ERR_SHAPE, "attention (CUDA cores): %d images x %d heads exceed the grid", p.B, p.heads);
     const int n_pad = (int)round_up(p.n_keys, 4) + 1;
     const size_t smem = (size_t)(AQ * AD + AKC * (AD + 1) + AQ * n_pad) * sizeof(float);
     VTP_REQUIRE(smem <= 200 * 1024, VTP_ERR_SHAPE, "attention: %d keys do not fit in shared memory", p.n_keys);
@@ -119,13 +129,13 @@ int attention_cuda_cores(const AttnArgs& p, cudaStream_t st) {
         if (e == cudaSuccess)
             attn_simt_kernel<float><<<grid, 128, smem, st>>>(
                 (const float*)p.q, p.q_rs, p.q_hs, (const float*)p.k, (const float*)p.v, p.kv_bs, p.kv_rs,
-                p.kv_hs, (float*)p.out, p.o_rs, p.o_hs, p.n_keys, n_pad, p.offsets, p.scale);
+                p.kv_hs, (float*)p.out, p.o_rs, p.o_hs, p.n_keys, n_pad, p.offsets, p.l_max, p.scale, device_status_ptr());
     } else {
         e = cudaFuncSetAttribute(attn_simt_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             attn_simt_kernel<bf16><<<grid, 128, smem, st>>>(
                 (const bf16*)p.q, p.q_rs, p.q_hs, (const bf16*)p.k, (const bf16*)p.v, p.kv_bs, p.kv_rs,
-                p.kv_hs, (bf16*)p.out, p.o_rs, p.o_hs, p.n_keys, n_pad, p.offsets, p.scale);
+                p.kv_hs, (bf16*)p.out, p.o_rs, p.o_hs, p.n_keys, n_pad, p.offsets, p.l_max, p.scale, device_status_ptr());
     }
     if (e != cudaSuccess) {
         set_error("attention (CUDA cores): %s", cudaGetErrorString(e));

@@ -86,7 +86,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                const __grid_constant__ CUtensorMap tmap_v, const bf16* __restrict__ kptr,
                const bf16* __restrict__ vptr, long long q_hs, long long kv_bs, long long kv_rs, long long kv_hs,
                bf16* __restrict__ out, long long o_rs, long long o_hs, int B, int heads, int n_keys, int KC,
-               int n_chunks, const int32_t* __restrict__ offsets, float scale_log2e, int* status) {
+               int n_chunks, const int32_t* __restrict__ offsets, int l_max, int max_q, float scale_log2e,
+               int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + SM_BAR);
@@ -127,8 +128,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     griddep_wait();
     // tile_prefix[b] = number of 128-query tiles of the images in front of b.  All threads fetch the
     // per-image tile counts at once (one global-load latency), then warp 0 scans them in shared memory.
-    for (int b = threadIdx.x; b < B; b += blockDim.x)
-        tile_prefix[b] = (offsets[b + 1] - offsets[b] + QT - 1) / QT;
+    // (the offsets come from the caller: a count outside [0, max_q] is clamped, so the item list
+    // always fits the grid's bound, and rows at or beyond l_max are never stored below)
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        int cnt = offsets[b + 1] - offsets[b];
+#if VTP_INDEX_GUARDS
+        if (cnt < 0 || cnt > max_q || offsets[b] < 0 || offsets[b + 1] > l_max) {
+            if (status && blockIdx.x == 0) atomicOr(status, STATUS_BAD_INDEX);
+            cnt = (offsets[b] < 0) ? 0 : min(max(cnt, 0), max_q);
+        }
+#endif
+        tile_prefix[b] = (cnt + QT - 1) / QT;
+    }
     __syncthreads();
     if (warp == 0) {
         int run = 0;
@@ -151,7 +162,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const bool void_launch = status && *reinterpret_cast<volatile int*>(status) != 0;
+    const bool void_launch = status && (*reinterpret_cast<volatile int*>(status) & STATUS_WAIT_MASK) != 0;
     const int n_work = void_launch ? 0 : tile_prefix[B] * heads;
     const int n_main = (n_keys / 16) * 16;          // keys handled by the tensor cores
     const int tail = n_keys - n_main;               // 0..15 keys handled on CUDA cores
@@ -372,7 +383,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 }
             }
             mbar_arrive(&q_free[qb]);
-            if (r < it.nq) {
+            if (r < it.nq && it.row0 + r < l_max) {
                 const float inv = 1.0f / l;
                 bf16* dst = out + (size_t)(it.row0 + r) * o_rs + it.h * o_hs;
 #pragma unroll
@@ -441,7 +452,7 @@ int attention_tcgen05(const AttnArgs& p, cudaStream_t st) {
     const int grid = (int)(worst < 2ll * sm_count() ? worst : 2ll * sm_count());
     const cudaError_t le = launch_pdl(attn_tc_kernel, dim3(grid), dim3(192), (size_t)smem, st, tq, tk, tv,
                                       (const bf16*)p.k, (const bf16*)p.v, p.q_hs, p.kv_bs, p.kv_rs, p.kv_hs, (bf16*)p.out,
-                                      p.o_rs, p.o_hs, p.B, p.heads, p.n_keys, KC, n_chunks, p.offsets,
+                                      p.o_rs, p.o_hs, p.B, p.heads, p.n_keys, KC, n_chunks, p.offsets, p.l_max, p.max_q,
                                       p.scale * 1.4426950408889634f, device_status_ptr());
     if (le != cudaSuccess) {
         cudaGetLastError();

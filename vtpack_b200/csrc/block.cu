@@ -124,7 +124,13 @@ struct BlockChain {
     bool have_gate = false;
     int parity = 0;
     const vtp_block_weights* next = nullptr;
+    const float* image_bias = nullptr;   // fp32 [B, n_splits] added to this and the next block's router logits
 };
+
+// softmax scale of the attention: the shape's attn_scale, or head_dim^-0.5 when it is 0
+static float attn_scale(const vtp_dge_shape& s) {
+    return s.attn_scale != 0.f ? s.attn_scale : 1.0f / sqrtf((float)(s.C / s.heads));
+}
 
 static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, const void* x_in, void* x_out,
                          const float* forced_logits, int32_t* counts_out, void* ws, cudaStream_t st,
@@ -159,6 +165,8 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     // chained: gate decisions, per-image counts and token statistics came from the previous
     // block's unpool; the pool kernel then also derives the row offsets itself
     const bool chained = chain.have_gate && fold && !forced_logits;
+    VTP_REQUIRE(!chain.image_bias || by_region, VTP_ERR_UNSUPPORTED,
+                "block: a per-image gate bias needs the region-parallel gate (4x4-token regions)");
 
     if (chained) {
         stats_x_ready = true;
@@ -168,7 +176,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     } else if (by_region) {
         RegionGateArgs ga;
         ga.g = g; ga.x = x_in; ga.gw = w.gate_w; ga.gb = w.gate_b; ga.S = s.n_splits; ga.logits_out = b.logits[par];
-        ga.idx_out = idx; ga.eps = s.eps;
+        ga.idx_out = idx; ga.eps = s.eps; ga.image_bias = chain.image_bias;
         if (fold) { ga.stats_x = stats_x; stats_x_ready = true; }
         rc = region_gate(ga, s.dtype, st);
     } else {
@@ -235,7 +243,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     at.kv_bs = (long long)n_keys * 2 * C; at.kv_rs = 2 * C; at.kv_hs = d;
     at.out = b.ao; at.o_rs = C; at.o_hs = d;
     at.dtype = s.dtype; at.B = s.B; at.n_keys = n_keys; at.heads = s.heads; at.head_dim = d;
-    at.offsets = b.offsets; at.l_max = rows; at.max_q = N; at.scale = 1.0f / sqrtf((float)d); at.flags = kflag;
+    at.offsets = b.offsets; at.l_max = rows; at.max_q = N; at.scale = attn_scale(s); at.flags = kflag;
     if ((rc = attention(at, st)) || (rc = marks.mark(6))) return rc;
 
     LinearArgs lp;   // q1 = comp + attn_out Wp^T + b   (and, when folding, the row sums LN2 needs)
@@ -274,6 +282,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
             ua.next.gw = chain.next->gate_w; ua.next.gb = chain.next->gate_b; ua.next.S = s.n_splits;
             ua.next.logits = b.logits[par ^ 1]; ua.next.idx = b.idx[par ^ 1];
             ua.next.counts = b.counts[par ^ 1];
+            ua.next.image_bias = chain.image_bias;
             if (!chained) {
                 // this block's pool did not reset the next block's counts: start them at the extra tokens
                 fill_i32_kernel<<<ceil_div(s.B, 256), 256, 0, st>>>(b.counts[par ^ 1], s.B, s.num_extra);
@@ -321,7 +330,7 @@ static int dense_block_forward(const vtp_dge_shape& s, const vtp_block_weights& 
     at.kv_bs = (long long)N * 2 * C; at.kv_rs = 2 * C; at.kv_hs = d;
     at.out = b.ao; at.o_rs = C; at.o_hs = d;
     at.dtype = s.dtype; at.B = s.B; at.n_keys = N; at.heads = s.heads; at.head_dim = d;
-    at.offsets = b.offsets; at.l_max = rows; at.max_q = N; at.scale = 1.0f / sqrtf((float)d); at.flags = kflag;
+    at.offsets = b.offsets; at.l_max = rows; at.max_q = N; at.scale = attn_scale(s); at.flags = kflag;
     if ((rc = attention(at, st))) return rc;
     LinearArgs lp;
     lp.a = b.ao; lp.lda = C; lp.w = w.proj_w; lp.bias = w.proj_b; lp.res = x_in; lp.ldr = C; lp.y = b.q1;
@@ -411,6 +420,14 @@ extern "C" int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weig
                                     const vtp_block_weights* blocks, const void* images, float* logits,
                                     int32_t* counts_out, void* workspace, long long workspace_bytes,
                                     void* stream) {
+    return vtp_deit_dge_forward_ex(s, m, blocks, images, logits, counts_out, nullptr, workspace, workspace_bytes,
+                                   stream);
+}
+
+extern "C" int vtp_deit_dge_forward_ex(const vtp_dge_shape* s, const vtp_model_weights* m,
+                                       const vtp_block_weights* blocks, const void* images, float* logits,
+                                       int32_t* counts_out, const vtp_forward_options* opt, void* workspace,
+                                       long long workspace_bytes, void* stream) {
     if (int rc = check_shape(s)) return rc;
     VTP_REQUIRE(m && blocks && images && logits && workspace, VTP_ERR_NULL, "model: null pointer");
     VTP_REQUIRE(m->depth > 0 && m->patch > 0 && m->num_classes > 0, VTP_ERR_SHAPE, "model: bad shape");
@@ -435,14 +452,30 @@ extern "C" int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weig
     pe.out_grp = HW; pe.out_skip = 1; pe.res_mod = HW; pe.res_off = 1;
     if ((rc = linear(pe, st))) return rc;
     bool chained = false;      // block i-1's unpool prepared block i's gate
+    const BlockScratch bs = carve_block(*s, ms.block_ws);
+    const long long R = (long long)(s->H / s->region) * (s->W / s->region);
     for (int i = 0; i < m->depth; ++i) {
         BlockChain chain;
         chain.have_gate = chained;
         chain.parity = i & 1;
         chain.next = (i + 1 < m->depth) ? &blocks[i + 1] : nullptr;
+        chain.image_bias = opt ? opt->gate_image_bias : nullptr;
+        if (opt && opt->tokens_trace) {
+            const size_t nb = (size_t)s->B * N * C * e;
+            const cudaError_t ce = cudaMemcpyAsync(static_cast<char*>(opt->tokens_trace) + (size_t)i * nb, ms.x, nb,
+                                                   cudaMemcpyDeviceToDevice, st);
+            if (ce != cudaSuccess) return fail((int)ce, "model: tokens trace copy: %s", cudaGetErrorString(ce));
+        }
         rc = block_forward(*s, blocks[i], ms.x, ms.x, nullptr, counts_out ? counts_out + (size_t)i * s->B : nullptr,
                            ms.block_ws, st, StageMarks(), chain);
         if (rc) return rc;
+        if (opt && opt->grain_trace) {
+            // the block's grain indices stay in its slot of the scratch (its unpool writes the other slot)
+            const size_t nb = (size_t)s->B * R * sizeof(int32_t);
+            const cudaError_t ce = cudaMemcpyAsync(opt->grain_trace + (size_t)i * s->B * R, bs.idx[i & 1], nb,
+                                                   cudaMemcpyDeviceToDevice, st);
+            if (ce != cudaSuccess) return fail((int)ce, "model: grain trace copy: %s", cudaGetErrorString(ce));
+        }
         RegionGeom g;
         g.B = s->B; g.Hr = s->H / s->region; g.Wr = s->W / s->region; g.W = s->W; g.N = N; g.C = C;
         g.num_extra = s->num_extra; g.region = s->region;
@@ -455,6 +488,5 @@ extern "C" int vtp_deit_dge_forward(const vtp_dge_shape* s, const vtp_model_weig
     hd.a = ms.cls_n; hd.lda = C; hd.w = m->head_w; hd.bias = m->head_b; hd.y = logits; hd.ldy = m->num_classes;
     hd.dtype = s->dtype; hd.m_max = s->B; hd.N = m->num_classes; hd.K = C;
     hd.flags = (s->flags & VTP_FLAG_CUDA_CORES) | VTP_FLAG_OUT_F32;
-    (void)e;
     return linear(hd, st);
 }

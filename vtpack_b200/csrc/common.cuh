@@ -59,7 +59,16 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 enum : int {
     STATUS_GEMM_PRODUCER = 1, STATUS_GEMM_MMA = 2, STATUS_GEMM_EPILOGUE = 4,
     STATUS_ATTN_LOAD = 8, STATUS_ATTN_MMA = 16, STATUS_ATTN_SOFTMAX = 32,
+    STATUS_BAD_INDEX = 64,      // a caller-supplied patch row or row offset pointed outside the declared arrays
+    STATUS_WAIT_MASK = 63,      // the bounded-wait codes: while one is set, tensor-core launches return at once
 };
+
+// Index guards: kernels that follow caller-supplied indices (patch lists, packed-row offsets) check them
+// against the declared shapes, skip what does not fit and OR STATUS_BAD_INDEX into the status word.
+// Four integer compares per patch row; compile with -DVTP_INDEX_GUARDS=0 to leave them out.
+#ifndef VTP_INDEX_GUARDS
+#define VTP_INDEX_GUARDS 1
+#endif
 
 // ---------------------------------------------------------------- element vectors
 // A Vec<T> is 16 bytes of T: 4 floats or 8 bf16.

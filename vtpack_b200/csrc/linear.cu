@@ -19,7 +19,9 @@ int linear(const LinearArgs& p, cudaStream_t st) {
     if (int rc = linear_validate(p)) return rc;
     // the tensor-core kernel takes K in 64-element TMA boxes; a narrower reduction (PVT's 4x4x3 patch
     // embedding, K = 48) is small enough for the CUDA-core kernel
-    const bool tc_shape = p.K % 64 == 0 || p.ln_mode != 0 || p.emit_stats;
+    // and so does an output width that is not a whole number of 16-byte chunks (e.g. a 10-class head)
+    const bool tc_shape = (p.K % 64 == 0 && p.N % 8 == 0 && p.lda % 8 == 0 && p.ldy % 8 == 0 &&
+                           (!p.res || p.ldr % 8 == 0)) || p.ln_mode != 0 || p.emit_stats;
     if (p.dtype == VTP_BF16 && !(p.flags & VTP_FLAG_CUDA_CORES) && tc_shape) return linear_tcgen05(p, st);
     VTP_REQUIRE(p.ln_mode == 0 && !p.emit_stats, VTP_ERR_UNSUPPORTED,
                 "linear (CUDA cores): folded LayerNorm is a feature of the tcgen05 kernel");

@@ -174,7 +174,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (m_dev) M = min(*reinterpret_cast<const volatile int32_t*>(m_dev), m_max);
     const int n_tiles = (N + BN - 1) / BN;
     // no tiles for this CTA, or an earlier CTA gave up on a wait (the launch is void): skip the work
-    const bool void_launch = status && *reinterpret_cast<volatile int*>(status) != 0;
+    const bool void_launch = status && (*reinterpret_cast<volatile int*>(status) & STATUS_WAIT_MASK) != 0;
     const int total = void_launch ? 0 : ((M + TBM - 1) / TBM) * n_tiles;
     // Tail splitting.  A CTA takes tiles blockIdx.x, + gridDim.x, ...; the R tiles left for the last,
     // partial round are cut into `parts` column strips of BN / parts columns, one strip per CTA, so that

@@ -49,15 +49,27 @@ using namespace vtp;
 extern "C" int vtp_gate_compact_static(const void* x, int dtype, int B, int H, int W, int C, int num_extra,
                                        int region, const float* gate_w, const float* gate_b, const int* splits,
                                        int n_splits, int32_t* offsets, int32_t* patches, void* stream) {
+    // Every argument check of the two calls below is repeated here, in front of the first launch, so that a
+    // rejected call has launched nothing and has not touched the shared array.
     VTP_REQUIRE(x && gate_w && gate_b && splits && offsets && patches, VTP_ERR_NULL,
                 "gate_compact_static: null pointer");
+    VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "gate_compact_static: dtype %d", dtype);
     VTP_REQUIRE(B > 0 && H > 0 && W > 0 && region > 0 && H % region == 0 && W % region == 0, VTP_ERR_SHAPE,
                 "gate_compact_static: grid %dx%d not divisible by region %d", H, W, region);
+    VTP_REQUIRE(num_extra >= 0, VTP_ERR_SHAPE, "gate_compact_static: num_extra %d", num_extra);
+    VTP_REQUIRE(C > 0 && C % (16 / (int)elem_size(dtype)) == 0 && C % 4 == 0, VTP_ERR_SHAPE,
+                "gate_compact_static: C=%d must be a multiple of 16 bytes", C);
     const long long regions = (long long)B * (H / region) * (W / region);
     VTP_REQUIRE(B <= kStaticMaxImages && regions <= kStaticMaxRegions, VTP_ERR_SHAPE,
                 "gate_compact_static: %d images / %lld regions exceed the static scratch (at most %d images and %d "
                 "regions); use vtp_router_gate + vtp_index_to_patch with caller-provided buffers",
                 B, regions, kStaticMaxImages, kStaticMaxRegions);
+    VTP_REQUIRE((H / region) * (W / region) <= 8192, VTP_ERR_SHAPE, "gate_compact_static: %d regions per image (at most 8192)",
+                (H / region) * (W / region));
+    Splits sp;
+    if (int rc = make_splits(&sp, splits, n_splits, region)) return rc;
+    VTP_REQUIRE(aligned16(x) && aligned16(gate_w) && aligned16(patches), VTP_ERR_ALIGN,
+                "gate_compact_static: unaligned pointer");
     int32_t *idx = nullptr, *counts = nullptr;
     if (int rc = static_scratch(&idx, &counts)) return rc;
     // Nothing in the scratch has to start at zero: every entry read below is written first.

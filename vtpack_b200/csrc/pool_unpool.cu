@@ -7,8 +7,25 @@
 // (vtpack/layers/csrc/grained_sample/grained_sample.cu:31-69, 71-144) and the nn.LayerNorm
 // calls of Block.forward (vtpack/models/dge/deit_dge.py:127-128).
 #include "common.cuh"
+#include "runtime.h"
 
 namespace vtp {
+
+// True when every token a patch row [b, y, x, step] names lies inside the declared [B, N] token array
+// (N = num_extra + H*W); extra-token rows are [b, -idx-1, *, 1].
+__device__ __forceinline__ bool patch_in_range(const int4& pt, int B, int N, int W, int num_extra) {
+#if VTP_INDEX_GUARDS
+    if ((unsigned)pt.x >= (unsigned)B) return false;
+    if (pt.y < 0) return -(long long)pt.y - 1 < (long long)num_extra;
+    const int H = (N - num_extra) / W;
+    return pt.w >= 1 && pt.w <= H && pt.y <= H - pt.w && pt.z >= 0 && pt.w <= W && pt.z <= W - pt.w;
+#else
+    return true;
+#endif
+}
+__device__ __forceinline__ void flag_bad_index(int* status) {
+    if (status) atomicOr(status, STATUS_BAD_INDEX);
+}
 
 template <typename T, int MAXCH>
 struct RowRegs {
@@ -73,10 +90,10 @@ __device__ __forceinline__ void load_vecs(float (&dst)[MAXCH][Vec<T>::N], const 
 // form measured 40 us instead of 50 us at DeiT-S batch 256; four blocks were no better.
 template <typename T, int MAXCH, bool WITH_LN>
 __global__ void __launch_bounds__(256, 3)
-pool_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
+pool_kernel(const T* __restrict__ x, int B, int N, int C, int W, int num_extra,
             const int4* __restrict__ patches, const int32_t* __restrict__ n_dev, int n_max,
             T* __restrict__ comp, const float* __restrict__ lnw, const float* __restrict__ lnb,
-            float eps, T* __restrict__ xn, T* __restrict__ qn, int mean) {
+            float eps, T* __restrict__ xn, T* __restrict__ qn, int mean, int* status) {
     constexpr int VN = Vec<T>::N;
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -92,6 +109,10 @@ pool_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
 
     for (int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; p < L; p += warps) {
         const int4 pt = __ldg(patches + p);
+        if (!patch_in_range(pt, B, N, W, num_extra)) {      // skip the row, leave a mark for the host
+            if (lane == 0) flag_bad_index(status);
+            continue;
+        }
         const bool extra = pt.y < 0;
         const int step = extra ? 1 : pt.w;
         const int tok0 = extra ? (-pt.y - 1) : (num_extra + pt.y * W + pt.z);
@@ -158,9 +179,9 @@ pool_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
 // Algorithmic bytes: (2*B*N + L)*C*e (+ L*C*e for comp).
 template <typename T, int MAXCH>
 __global__ void __launch_bounds__(256)
-unpool_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, int C, int W,
+unpool_kernel(const T* __restrict__ q, const T* __restrict__ comp, int B, int N, int C, int W,
               int num_extra, const int4* __restrict__ patches, const int32_t* __restrict__ n_dev,
-              int n_max, const T* ref, T* out, int inv_area) {
+              int n_max, const T* ref, T* out, int inv_area, int* status) {
     constexpr int VN = Vec<T>::N;
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -170,6 +191,10 @@ unpool_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, int C,
 
     for (int p = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; p < L; p += warps) {
         const int4 pt = __ldg(patches + p);
+        if (!patch_in_range(pt, B, N, W, num_extra)) {      // skip the row, leave a mark for the host
+            if (lane == 0) flag_bad_index(status);
+            continue;
+        }
         const bool extra = pt.y < 0;
         const int step = extra ? 1 : pt.w;
         const int tok0 = extra ? (-pt.y - 1) : (num_extra + pt.y * W + pt.z);
@@ -247,9 +272,9 @@ unpool_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, int C,
 // grained_sample.cu:31-69 and :107-144.
 template <typename T>
 __global__ void __launch_bounds__(256)
-pool_any_c_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
+pool_any_c_kernel(const T* __restrict__ x, int B, int N, int C, int W, int num_extra,
                   const int4* __restrict__ patches, const int32_t* __restrict__ n_dev, int n_max,
-                  T* __restrict__ comp, int mean) {
+                  T* __restrict__ comp, int mean, int* status) {
     int L = n_max;
     if (n_dev) L = min(__ldg(n_dev), n_max);
     const long long total = (long long)L * C;
@@ -257,6 +282,10 @@ pool_any_c_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
          e += (long long)gridDim.x * blockDim.x) {
         const int p = (int)(e / C), c = (int)(e % C);
         const int4 pt = __ldg(patches + p);
+        if (!patch_in_range(pt, B, N, W, num_extra)) {      // skip the row, leave a mark for the host
+            if (c == 0) flag_bad_index(status);
+            continue;
+        }
         const bool extra = pt.y < 0;
         const int step = extra ? 1 : pt.w;
         const int tok0 = extra ? (-pt.y - 1) : (num_extra + pt.y * W + pt.z);
@@ -271,9 +300,9 @@ pool_any_c_kernel(const T* __restrict__ x, int N, int C, int W, int num_extra,
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-unpool_any_c_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, int C, int W, int num_extra,
+unpool_any_c_kernel(const T* __restrict__ q, const T* __restrict__ comp, int B, int N, int C, int W, int num_extra,
                     const int4* __restrict__ patches, const int32_t* __restrict__ n_dev, int n_max,
-                    const T* ref, T* out, int inv_area) {
+                    const T* ref, T* out, int inv_area, int* status) {
     int L = n_max;
     if (n_dev) L = min(__ldg(n_dev), n_max);
     const long long total = (long long)L * C;
@@ -281,6 +310,10 @@ unpool_any_c_kernel(const T* __restrict__ q, const T* __restrict__ comp, int N, 
          e += (long long)gridDim.x * blockDim.x) {
         const int p = (int)(e / C), c = (int)(e % C);
         const int4 pt = __ldg(patches + p);
+        if (!patch_in_range(pt, B, N, W, num_extra)) {      // skip the row, leave a mark for the host
+            if (c == 0) flag_bad_index(status);
+            continue;
+        }
         const bool extra = pt.y < 0;
         const int step = extra ? 1 : pt.w;
         const int tok0 = extra ? (-pt.y - 1) : (num_extra + pt.y * W + pt.z);
@@ -343,13 +376,13 @@ static int row_grid(int rows) {
 }
 
 template <typename T>
-static int launch_pool(const void* x, int N, int C, int W, int num_extra, const int32_t* patches,
+static int launch_pool(const void* x, int B, int N, int C, int W, int num_extra, const int32_t* patches,
                        const int32_t* n_dev, int n_max, void* comp, const float* lnw,
                        const float* lnb, float eps, void* xn, void* qn, int mean, cudaStream_t st) {
     if (C % Vec<T>::N != 0) {
         if (lnw) return fail(VTP_ERR_SHAPE, "pool: fused LayerNorm needs C=%d in whole 16-byte chunks", C);
         pool_any_c_kernel<T><<<elem_grid((long long)n_max * C), 256, 0, st>>>(
-            (const T*)x, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp, mean);
+            (const T*)x, B, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp, mean, device_status_ptr());
         return check_launch("pool");
     }
     const int maxch = ceil_div(C / Vec<T>::N, 32);
@@ -359,12 +392,12 @@ static int launch_pool(const void* x, int N, int C, int W, int num_extra, const 
     do {                                                                                             \
         if (ln)                                                                                      \
             pool_kernel<T, M, true><<<grid, 256, 0, st>>>(                                           \
-                (const T*)x, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp, lnw,  \
-                lnb, eps, (T*)xn, (T*)qn, mean);                                                     \
+                (const T*)x, B, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp, lnw,  \
+                lnb, eps, (T*)xn, (T*)qn, mean, device_status_ptr());                                \
         else                                                                                         \
             pool_kernel<T, M, false><<<grid, 256, 0, st>>>(                                          \
-                (const T*)x, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp,       \
-                nullptr, nullptr, eps, nullptr, nullptr, mean);                                      \
+                (const T*)x, B, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (T*)comp,    \
+                nullptr, nullptr, eps, nullptr, nullptr, mean, device_status_ptr());                 \
     } while (0)
     if (maxch <= 1) VTP_POOL(1);
     else if (maxch == 2) VTP_POOL(2);
@@ -377,21 +410,21 @@ static int launch_pool(const void* x, int N, int C, int W, int num_extra, const 
 }
 
 template <typename T>
-static int launch_unpool(const void* q, const void* comp, int N, int C, int W, int num_extra,
+static int launch_unpool(const void* q, const void* comp, int B, int N, int C, int W, int num_extra,
                          const int32_t* patches, const int32_t* n_dev, int n_max, const void* ref,
                          void* out, int inv_area, cudaStream_t st) {
     if (C % Vec<T>::N != 0) {
         unpool_any_c_kernel<T><<<elem_grid((long long)n_max * C), 256, 0, st>>>(
-            (const T*)q, (const T*)comp, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (const T*)ref,
-            (T*)out, inv_area);
+            (const T*)q, (const T*)comp, B, N, C, W, num_extra, (const int4*)patches, n_dev, n_max, (const T*)ref,
+            (T*)out, inv_area, device_status_ptr());
         return check_launch("unpool_add");
     }
     const int maxch = ceil_div(C / Vec<T>::N, 32);
     const int grid = row_grid(n_max);
 #define VTP_UNPOOL(M)                                                                           \
-    unpool_kernel<T, M><<<grid, 256, 0, st>>>((const T*)q, (const T*)comp, N, C, W, num_extra,  \
+    unpool_kernel<T, M><<<grid, 256, 0, st>>>((const T*)q, (const T*)comp, B, N, C, W, num_extra,  \
                                               (const int4*)patches, n_dev, n_max, (const T*)ref,      \
-                                              (T*)out, inv_area)
+                                              (T*)out, inv_area, device_status_ptr())
     if (maxch <= 1) VTP_UNPOOL(1);
     else if (maxch == 2) VTP_UNPOOL(2);
     else if (maxch == 3) VTP_UNPOOL(3);
@@ -454,14 +487,15 @@ extern "C" int vtp_pool(const void* x, int dtype, int B, int N, int C, int W, in
     VTP_REQUIRE(ln_w || (!xn && !qn), VTP_ERR_NULL, "pool: xn/qn need LayerNorm weights");
     VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
                 "pool: bad shape");
+    VTP_REQUIRE(N > num_extra && (N - num_extra) % W == 0, VTP_ERR_SHAPE, "pool: N - num_extra = %d is not a whole number of grid rows of %d tokens", N - num_extra, W);
     if (int rc = check_token_rows("pool", dtype, C, x, comp, xn, qn)) return rc;
     VTP_REQUIRE(aligned16(patches), VTP_ERR_ALIGN, "pool: unaligned patch list");
     if (n_patches_max == 0) return VTP_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == VTP_F32)
-        return launch_pool<float>(x, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, comp,
+        return launch_pool<float>(x, B, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, comp,
                                   ln_w, ln_b, eps, xn, qn, 1, st);
-    return launch_pool<bf16>(x, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, comp, ln_w,
+    return launch_pool<bf16>(x, B, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, comp, ln_w,
                              ln_b, eps, xn, qn, 1, st);
 }
 
@@ -471,14 +505,15 @@ extern "C" int vtp_unpool_add(const void* q, const void* comp, int dtype, int B,
     VTP_REQUIRE(q && patches && out, VTP_ERR_NULL, "unpool: null pointer");
     VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
                 "unpool: bad shape");
+    VTP_REQUIRE(N > num_extra && (N - num_extra) % W == 0, VTP_ERR_SHAPE, "unpool: N - num_extra = %d is not a whole number of grid rows of %d tokens", N - num_extra, W);
     if (int rc = check_token_rows("unpool", dtype, C, q, out, comp, ref)) return rc;
     VTP_REQUIRE(aligned16(patches), VTP_ERR_ALIGN, "unpool: unaligned patch list");
     if (n_patches_max == 0) return VTP_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == VTP_F32)
-        return launch_unpool<float>(q, comp, N, C, W, num_extra, patches, n_patches_dev, n_patches_max,
+        return launch_unpool<float>(q, comp, B, N, C, W, num_extra, patches, n_patches_dev, n_patches_max,
                                     ref, out, 0, st);
-    return launch_unpool<bf16>(q, comp, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, ref,
+    return launch_unpool<bf16>(q, comp, B, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, ref,
                                out, 0, st);
 }
 
@@ -490,14 +525,15 @@ extern "C" int vtp_pool_grad(const void* grad_comp, int dtype, int B, int N, int
     VTP_REQUIRE(grad_comp && patches && grad_x, VTP_ERR_NULL, "pool_grad: null pointer");
     VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
                 "pool_grad: bad shape");
+    VTP_REQUIRE(N > num_extra && (N - num_extra) % W == 0, VTP_ERR_SHAPE, "pool_grad: N - num_extra = %d is not a whole number of grid rows of %d tokens", N - num_extra, W);
     if (int rc = check_token_rows("pool_grad", dtype, C, grad_comp, grad_x, nullptr, nullptr)) return rc;
     VTP_REQUIRE(aligned16(patches), VTP_ERR_ALIGN, "pool_grad: unaligned patch list");
     if (n_patches_max == 0) return VTP_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == VTP_F32)
-        return launch_unpool<float>(grad_comp, nullptr, N, C, W, num_extra, patches, n_patches_dev,
+        return launch_unpool<float>(grad_comp, nullptr, B, N, C, W, num_extra, patches, n_patches_dev,
                                     n_patches_max, nullptr, grad_x, 1, st);
-    return launch_unpool<bf16>(grad_comp, nullptr, N, C, W, num_extra, patches, n_patches_dev, n_patches_max,
+    return launch_unpool<bf16>(grad_comp, nullptr, B, N, C, W, num_extra, patches, n_patches_dev, n_patches_max,
                                nullptr, grad_x, 1, st);
 }
 
@@ -507,14 +543,15 @@ extern "C" int vtp_unpool_grad(const void* grad_out, int dtype, int B, int N, in
     VTP_REQUIRE(grad_out && patches && grad_q, VTP_ERR_NULL, "unpool_grad: null pointer");
     VTP_REQUIRE(B > 0 && N > 0 && W > 0 && num_extra >= 0 && n_patches_max >= 0, VTP_ERR_SHAPE,
                 "unpool_grad: bad shape");
+    VTP_REQUIRE(N > num_extra && (N - num_extra) % W == 0, VTP_ERR_SHAPE, "unpool_grad: N - num_extra = %d is not a whole number of grid rows of %d tokens", N - num_extra, W);
     if (int rc = check_token_rows("unpool_grad", dtype, C, grad_out, grad_q, nullptr, nullptr)) return rc;
     VTP_REQUIRE(aligned16(patches), VTP_ERR_ALIGN, "unpool_grad: unaligned patch list");
     if (n_patches_max == 0) return VTP_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == VTP_F32)
-        return launch_pool<float>(grad_out, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, grad_q,
+        return launch_pool<float>(grad_out, B, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, grad_q,
                                   nullptr, nullptr, 0.f, nullptr, nullptr, 0, st);
-    return launch_pool<bf16>(grad_out, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, grad_q,
+    return launch_pool<bf16>(grad_out, B, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, grad_q,
                              nullptr, nullptr, 0.f, nullptr, nullptr, 0, st);
 }
 

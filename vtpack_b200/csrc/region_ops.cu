@@ -365,7 +365,7 @@ template <typename T, int G, int CPL>
 __device__ __forceinline__ void gate_from_partials(const float* part, int C, int sub, const float* __restrict__ gw,
                                                    const float* __restrict__ gb, int S, float* __restrict__ logits_out,
                                                    int32_t* __restrict__ idx_out, int rid, int32_t* counts_img,
-                                                   const Splits& sp) {
+                                                   const Splits& sp, const float* __restrict__ img_bias) {
     constexpr int VN = Vec<T>::N;
     constexpr bool both_halves = Lay<T, G, CPL>::TPG != 4;
     float acc[CPL][VN];
@@ -396,6 +396,7 @@ __device__ __forceinline__ void gate_from_partials(const float* part, int C, int
             }
         }
         pdot = group_sum<G>(pdot) + __ldg(gb + sI);
+        if (img_bias) pdot += __ldg(img_bias + sI);          // per-image offset of the logits (forced grain mixes)
         if (sub == 0 && logits_out) logits_out[(size_t)rid * S + sI] = pdot;
         if (sI == 0 || pdot > best) { best = pdot; best_i = sI; }
     }
@@ -516,7 +517,8 @@ unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const 
     publish_partials<T, G, CPL>(part, acc, w, grp, sub, g.C);
     if (w != 0 || grp != 0) return;
     gate_from_partials<T, G, CPL>(part, g.C, sub, nx.gw, nx.gb, nx.S, nx.logits, nx.idx, rid,
-                                  nx.counts ? nx.counts + b : nullptr, sp);
+                                  nx.counts ? nx.counts + b : nullptr, sp,
+                                  nx.image_bias ? nx.image_bias + (size_t)b * nx.S : nullptr);
 }
 
 // Stand-alone gate (first block of a model, or a block called on its own); optionally also
@@ -525,7 +527,8 @@ template <typename T, int G, int CPL>
 __global__ void __launch_bounds__(128)
 gate_region_kernel(const T* __restrict__ x, RegionGeom g, const float* __restrict__ gw,
                    const float* __restrict__ gb, int S, float* __restrict__ logits_out,
-                   int32_t* __restrict__ idx_out, float2* __restrict__ stats_x, float eps) {
+                   int32_t* __restrict__ idx_out, float2* __restrict__ stats_x, float eps,
+                   const float* __restrict__ image_bias) {
     using L = Lay<T, G, CPL>;
     constexpr int VN = L::VN, GROUPS = L::GROUPS, TPG = L::TPG;
     extern __shared__ float part[];          // [4][2][C]
@@ -571,7 +574,8 @@ gate_region_kernel(const T* __restrict__ x, RegionGeom g, const float* __restric
     if (w != 0 || grp != 0) return;
     Splits none;
     none.n = 1; none.v[0] = 0;
-    gate_from_partials<T, G, CPL>(part, g.C, sub, gw, gb, S, logits_out, idx_out, rid, nullptr, none);
+    gate_from_partials<T, G, CPL>(part, g.C, sub, gw, gb, S, logits_out, idx_out, rid, nullptr, none,
+                                  image_bias ? image_bias + (size_t)b * S : nullptr);
 }
 
 // ------------------------------------------------------------------------------- host
@@ -614,7 +618,7 @@ static void launch_gate_t(const RegionGateArgs& a, cudaStream_t st) {
     const int R = a.g.Hr * a.g.Wr;
     const int grid = a.g.B * R + (a.stats_x ? ceil_div(a.g.B * a.g.num_extra, RG * (32 / G)) : 0);
     gate_region_kernel<T, G, CPL><<<grid, 128, (size_t)8 * a.g.C * sizeof(float), st>>>(
-        (const T*)a.x, a.g, a.gw, a.gb, a.S, a.logits_out, a.idx_out, a.stats_x, a.eps);
+        (const T*)a.x, a.g, a.gw, a.gb, a.S, a.logits_out, a.idx_out, a.stats_x, a.eps, a.image_bias);
 }
 
 #define VTP_DISPATCH_LAYOUT(FN, T, ARGS, ST)                                    \

@@ -41,6 +41,7 @@ struct NextBlock {
     const float* gw = nullptr; const float* gb = nullptr; int S = 0;
     float* logits = nullptr; int32_t* idx = nullptr;
     int32_t* counts = nullptr;               // [B] per-image query counts, accumulated with atomics
+    const float* image_bias = nullptr;       // [B, S] added to the logits of every region of image b, or null
 };
 
 struct RegionUnpoolArgs {
@@ -56,6 +57,7 @@ struct RegionGateArgs {
     const float* gw = nullptr; const float* gb = nullptr; int S = 0;
     float* logits_out = nullptr; int32_t* idx_out = nullptr;
     float2* stats_x = nullptr; float eps = 1e-6f;     // optional: also the token rows' (mean, rstd)
+    const float* image_bias = nullptr;                // [B, S] added to the logits of every region of image b, or null
 };
 
 bool region_ops_supported(const RegionGeom& g, int dtype);

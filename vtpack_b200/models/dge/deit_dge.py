@@ -21,7 +21,7 @@ import torch.nn as nn
 
 from ... import _lib
 from ...layers import DynamicGrainedEncoder, batched_sparse_attention, batched_sparse_gemm
-from ...runtime import dtype_code, ptr, require_cuda, scratch, stream_ptr
+from ...runtime import dtype_code, ptr, require_cuda, scratch, scratch_generation, stream_ptr
 
 __all__ = [
     "deit_dge_s124_tiny_patch16_256", "deit_dge_s124_small_patch16_256",
@@ -214,7 +214,7 @@ def _pack_block(blk, dtype) -> _lib.BlockWeights:
     return pk.struct
 
 
-def _shape_struct(x_dtype, B, H, W, num_extra, C, heads, hidden, splits, eps, flags):
+def _shape_struct(x_dtype, B, H, W, num_extra, C, heads, hidden, splits, eps, flags, attn_scale=0.0):
     s = _lib.DgeShape()
     s.dtype = dtype_code(x_dtype)
     s.B, s.H, s.W, s.num_extra = B, H, W, num_extra
@@ -225,6 +225,7 @@ def _shape_struct(x_dtype, B, H, W, num_extra, C, heads, hidden, splits, eps, fl
         s.splits[i] = int(v)
     s.eps = float(eps)
     s.flags = int(flags)
+    s.attn_scale = float(attn_scale)      # Attention.scale (qk_scale or head_dim ** -0.5)
     return s
 
 
@@ -258,7 +259,7 @@ class Block(nn.Module):
         B, N, C = x.shape
         H = W = int(math.sqrt(N))
         return _shape_struct(x.dtype, B, H, W, N - H * W, C, self.attn.num_heads, self.mlp.fc1.out_features,
-                             self.split_sizes, self.norm1.eps, self.flags)
+                             self.split_sizes, self.norm1.eps, self.flags, self.attn.scale)
 
     def forward(self, x, forced_gate=None, dense=False):
         """One C-ABI call for the whole block (``deit_dge.py:123-130``).  ``forced_gate``
@@ -363,6 +364,12 @@ class VisionTransformer(nn.Module):
         self._pack = _WeightPack()
         self._graphs = {}
         self.last_counts = None
+        # eval-mode options of the fused forward (vtp_forward_options):
+        self.gate_image_bias = None     # fp32 [B, n_splits] added to every block's router logits of image b
+        self.trace = False              # True: keep each block's input tokens and grain indices of the last
+                                        # forward; "grains": the grain indices only
+        self.last_tokens = None         # [depth, B, N, C] when trace
+        self.last_grains = None         # int32 [depth, B, regions] when trace
         self._init_weights()
 
     def _init_weights(self):
@@ -413,6 +420,7 @@ class VisionTransformer(nn.Module):
                 blk.fold_layernorm = self.fold_layernorm
                 blocks[i] = _pack_block(blk, dtype)
             pk.key, pk.tensors, pk.struct = key, t, (m, blocks)
+            self._graphs.clear()        # captured graphs hold the addresses of the previous pack
         return pk.struct
 
     def forward_graph(self, x, logits_out):
@@ -436,7 +444,7 @@ class VisionTransformer(nn.Module):
         G = self.img_size // self.patch_size
         blk0 = self.blocks[0]
         s = _shape_struct(dtype, B, G, G, 1, self.embed_dim, blk0.attn.num_heads, blk0.mlp.fc1.out_features,
-                          self.split_sizes, self.norm.eps, self.flags)
+                          self.split_sizes, self.norm.eps, self.flags, blk0.attn.scale)
         m, blocks = self._pack_model(dtype)
         m.image_dtype = dtype_code(x.dtype)
         lib = _lib.lib()
@@ -445,8 +453,25 @@ class VisionTransformer(nn.Module):
         logits = logits_out if logits_out is not None else torch.empty(
             B, self.num_classes, dtype=torch.float32, device=x.device)
         counts = torch.empty(self.depth, B, dtype=torch.int32, device=x.device)
-        _lib.check(lib.vtp_deit_dge_forward(ctypes.byref(s), ctypes.byref(m), blocks, ptr(x), ptr(logits),
-                                            ptr(counts), ptr(ws), nbytes, stream_ptr(x.device)))
+        opt = _lib.ForwardOptions()
+        if self.gate_image_bias is not None:
+            bias = self.gate_image_bias
+            if (not bias.is_cuda or bias.dtype != torch.float32 or not bias.is_contiguous()
+                    or tuple(bias.shape) != (B, len(self.split_sizes))):
+                raise ValueError("gate_image_bias must be a contiguous fp32 CUDA tensor [B, n_splits]")
+            opt.gate_image_bias = bias.data_ptr()
+        if self.trace:
+            if self.trace != "grains":
+                self.last_tokens = torch.empty(self.depth, B, G * G + 1, self.embed_dim, dtype=dtype,
+                                               device=x.device)
+            self.last_grains = torch.empty(self.depth, B, (G // max(self.split_sizes)) ** 2, dtype=torch.int32,
+                                           device=x.device)
+            opt.grain_trace = self.last_grains.data_ptr()
+            if self.trace != "grains":
+                opt.tokens_trace = self.last_tokens.data_ptr()
+        _lib.check(lib.vtp_deit_dge_forward_ex(ctypes.byref(s), ctypes.byref(m), blocks, ptr(x), ptr(logits),
+                                               ptr(counts), ctypes.byref(opt), ptr(ws), nbytes,
+                                               stream_ptr(x.device)))
         self.last_counts = counts
         # what get_complexity() of each block's encoder needs (dge.py:40-59): shapes only, and the
         # per-image query counts, which stay on the device
@@ -481,11 +506,28 @@ class VisionTransformer(nn.Module):
         return {"static": comp_static, "dynamic": comp_dynamic}
 
 
+class _CapturedForward:
+    """A captured forward and everything whose address it holds."""
+
+    def __init__(self, graph, keep, scratch_gen):
+        self.graph, self.keep, self.scratch_gen = graph, keep, scratch_gen
+
+
 def _graph_forward(model, x, logits_out):
     """Replay (capturing on first use) a CUDA graph of model.forward(x, logits_out) for these
-    exact buffers: removes per-launch host work and shortens the gaps between kernels."""
-    key = (x.data_ptr(), tuple(x.shape), x.dtype, logits_out.data_ptr())
+    exact buffers: removes per-launch host work and shortens the gaps between kernels.
+
+    A captured graph holds raw addresses: the input and output buffers, the packed (and folded)
+    weights, the per-device scratch and the optional gate bias.  It is dropped, and captured
+    again, when a parameter has changed since (load_state_dict, an optimizer step), when the
+    scratch buffer has been replaced by a larger one, or when another gate bias tensor is set."""
+    model._pack_model(model.compute_dtype())       # repacks after a parameter change and drops stale graphs
+    bias = model.gate_image_bias
+    key = (x.data_ptr(), tuple(x.shape), x.dtype, logits_out.data_ptr(), None if bias is None else bias.data_ptr(),
+           model.trace, int(model.flags))
     g = model._graphs.get(key)
+    if g is not None and g.scratch_gen != scratch_generation(x.device):
+        g = None
     if g is None:
         cur = torch.cuda.current_stream(x.device)
         side = torch.cuda.Stream(x.device)
@@ -495,11 +537,17 @@ def _graph_forward(model, x, logits_out):
                 model.forward(x, logits_out)
         cur.wait_stream(side)
         torch.cuda.synchronize(x.device)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
             model.forward(x, logits_out)
+        keep = (x, logits_out, bias, model._pack.tensors, [blk._pack.tensors for blk in model.blocks],
+                scratch(x.device, 1), model.last_counts, model.last_tokens, model.last_grains)
+        g = _CapturedForward(graph, keep, scratch_generation(x.device))
         model._graphs[key] = g
-    g.replay()
+    g.graph.replay()
+    model.last_counts = g.keep[6]
+    if model.trace:
+        model.last_tokens, model.last_grains = g.keep[7], g.keep[8]
     return logits_out
 
 

@@ -123,7 +123,7 @@ class Block(nn.Module):
         x = x.contiguous()
         B, N, C = x.shape
         s = _shape_struct(x.dtype, B, H, W, N - H * W, C, self.attn.num_heads, self.mlp.fc1.out_features,
-                          self.split_sizes, self.norm1.eps, self.flags)
+                          self.split_sizes, self.norm1.eps, self.flags, self.attn.scale)
         if self.attn.sr_ratio > 1:
             s.sr_ratio = self.attn.sr_ratio
             s.sr_eps = float(self.attn.norm.eps)
