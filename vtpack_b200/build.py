@@ -42,7 +42,8 @@ def _headers_mtime():
 
 
 def _compile(nvcc, src, obj, verbose):
-    cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+    # VTP_NVCC_FLAGS: extra compiler flags (e.g. -DVTP_INDEX_GUARDS=0); pass --force when changing them
+    cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("VTP_NVCC_FLAGS", "").split(), "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -11,7 +11,7 @@ int attention(const AttnArgs& p, cudaStream_t st) {
     if (p.l_max == 0 || p.max_q == 0) return VTP_OK;
     // the tensor-core kernel is written for 64-wide heads and at least one 16-key MMA step; other
     // shapes (and fp32) take the CUDA-core kernel
-    const bool tc_shape = p.head_dim == 64 && p.n_keys >= 16 && p.B <= 16384;
+    const bool tc_shape = p.head_dim == 64 && p.n_keys >= 16 && p.B <= attention_tcgen05_max_images();
     if (p.dtype == VTP_BF16 && !(p.flags & VTP_FLAG_CUDA_CORES) && tc_shape) return attention_tcgen05(p, st);
     return attention_cuda_cores(p, st);
 }

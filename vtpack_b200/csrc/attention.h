@@ -21,6 +21,7 @@ struct AttnArgs {
 
 int attention_cuda_cores(const AttnArgs& p, cudaStream_t st);
 int attention_tcgen05(const AttnArgs& p, cudaStream_t st);
+int attention_tcgen05_max_images();   // images per call the tensor-core kernel's shared-memory tile table holds
 int attention(const AttnArgs& p, cudaStream_t st);
 
 }  // namespace vtp

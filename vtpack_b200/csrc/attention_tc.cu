@@ -259,6 +259,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             ok = mbar_wait(&q_full[qb], (li >> 1) & 1, abort_flag, status, STATUS_ATTN_SOFTMAX);
             if (!ok) break;
             const AttnItem it = items[qb];
+            // a warp whose 32 rows all lie beyond the item's queries only keeps the barriers moving: its rows
+            // of P and O are never stored, so what the tensor core computes for them does not matter, and
+            // the special-function unit and the issue slots go to the warps that have rows to compute
+            const bool live = (warp & 3) * 32 < it.nq;
             float m = -INFINITY, l = 0.f;
             float o[HD];
 #pragma unroll
@@ -268,6 +272,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 ok = mbar_wait(s_full, ph, abort_flag, status, STATUS_ATTN_SOFTMAX);
                 if (!ok) break;
                 tc_fence_after_sync();
+                if (!live) {
+                    mbar_arrive(p_full);
+                    ok = mbar_wait(o_full, ph, abort_flag, status, STATUS_ATTN_SOFTMAX);
+                    if (!ok) break;
+                    mbar_arrive(o_free);
+                    continue;
+                }
                 const int n_valid = min(KC, n_main - c * KC);
                 const bool full = n_valid == KC && (KC & 31) == 0;     // no column needs masking
                 // Two sweeps over the S columns, 32 at a time: row maximum, then exp2 + P.  The
@@ -347,9 +358,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 mbar_arrive(o_free);
             }
             if (!ok) break;
+            if (!live) {
+                mbar_arrive(&q_free[qb]);
+                continue;
+            }
+            const uint8_t* qrow = base + SM_Q + qb * (QT * HD * 2) + r * 128;
             if (tail > 0) {
                 // ---- the last n_keys % 16 keys on CUDA cores, one online-softmax step per key
-                const uint8_t* qrow = base + SM_Q + qb * (QT * HD * 2) + r * 128;
                 const uint8_t* tb = base + SM_TAIL + qb * (2 * TAIL_ROWS * HD * 2);
                 for (int t = 0; t < tail; ++t) {
                     const uint4* krow = reinterpret_cast<const uint4*>(tb + t * (HD * 2));
@@ -382,10 +397,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     }
                 }
             }
-            mbar_arrive(&q_free[qb]);
-            if (r < it.nq && it.row0 + r < l_max) {
+            // ---- normalise, then out through the warp's own 32 rows of the Q tile (no longer needed) so that
+            // eight lanes write one full 128-byte line of a row instead of every lane a piece of its own row
+            {
                 const float inv = 1.0f / l;
-                bf16* dst = out + (size_t)(it.row0 + r) * o_rs + it.h * o_hs;
+                __syncwarp();                                   // every lane has read its Q row (tail scores)
+                uint8_t* my = const_cast<uint8_t*>(qrow);
 #pragma unroll
                 for (int ch = 0; ch < HD / 8; ++ch) {
                     float v8[8];
@@ -393,9 +410,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     for (int i = 0; i < 8; ++i) v8[i] = o[8 * ch + i] * inv;
                     Vec<bf16> ov;
                     ov.from_float(v8);
-                    ov.store(dst + 8 * ch);
+                    *reinterpret_cast<uint4*>(my + ((ch ^ (r & 7)) << 4)) = ov.raw;
                 }
+                __syncwarp();
+                const uint8_t* wq = base + SM_Q + qb * (QT * HD * 2) + (warp & 3) * 32 * 128;
+                const int ch = lane & 7;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int rr = i * 4 + (lane >> 3);          // row within the warp's 32
+                    const int row = (warp & 3) * 32 + rr;
+                    const uint4 v = *reinterpret_cast<const uint4*>(wq + rr * 128 + ((ch ^ (rr & 7)) << 4));
+                    if (row < it.nq && it.row0 + row < l_max)
+                        *reinterpret_cast<uint4*>(out + (size_t)(it.row0 + row) * o_rs + it.h * o_hs + ch * 8) = v;
+                }
+                __syncwarp();
+                fence_proxy_async_smem();                       // the next Q tile is written by TMA
             }
+            mbar_arrive(&q_free[qb]);
         }
     }
     if (*abort_flag) {
@@ -406,6 +437,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, ATT_TMEM_COLS);
 }
+
+int attention_tcgen05_max_images() { return 16384; }
 
 int attention_tcgen05(const AttnArgs& p, cudaStream_t st) {
     VTP_REQUIRE(p.dtype == VTP_BF16, VTP_ERR_DTYPE, "attention (tcgen05): bf16 only");
