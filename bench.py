@@ -358,7 +358,10 @@ def launches_per_forward(model):
     LayerNorm and gate kernels per block."""
     depth = len(model.blocks)
     if model.compute_dtype() == torch.bfloat16 and not model.flags:
-        return 9 + 8 * depth
+        C = model.embed_dim
+        # the q and kv projections share one launch when both widths tile by 256 with 0, 64 or 128 columns left
+        paired = C >= 256 and C % 256 in (0, 64, 128) and (2 * C) % 256 in (0, 64, 128)
+        return 9 + (7 if paired else 8) * depth
     return 5 + 12 * depth
 
 

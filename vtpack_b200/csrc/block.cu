@@ -215,10 +215,10 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     lq.a = fold ? b.comp : b.qn; lq.lda = C; lq.w = fold ? w.q_wf : w.q_w; lq.bias = fold ? w.q_c : w.q_b;
     lq.y = b.qp; lq.ldy = C; lq.dtype = s.dtype; lq.m_max = rows; lq.m_dev = L_dev; lq.N = C; lq.K = C; lq.flags = kflag;
     if (fold) { lq.ln_mode = 1; lq.ln_stats = b.stats_q; lq.ln_s = w.q_s; }
-    if ((rc = linear(lq, st)) || (rc = marks.mark(4))) return rc;
 
     const void* keys_in = fold ? x_in : b.xn;
     if (reduce) {
+        if ((rc = linear(lq, st)) || (rc = marks.mark(4))) return rc;
         // x_ = norm(sr(LN1(x) as [B,C,H,W])): the stride-sr convolution as im2col rows times a matrix
         const int krows = s.B * n_keys, KS = s.sr_ratio * s.sr_ratio * C;
         if ((rc = token_im2col(b.xn, s.dtype, s.B, s.H, s.W, C, s.sr_ratio, b.sr_cols, st))) return rc;
@@ -234,7 +234,13 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     lkv.a = keys_in; lkv.lda = C; lkv.w = fold ? w.kv_wf : w.kv_w; lkv.bias = fold ? w.kv_c : w.kv_b;
     lkv.y = b.kv; lkv.ldy = 2 * C; lkv.dtype = s.dtype; lkv.m_max = s.B * n_keys; lkv.N = 2 * C; lkv.K = C; lkv.flags = kflag;
     if (fold) { lkv.ln_mode = 1; lkv.ln_stats = stats_x; lkv.ln_s = w.kv_s; }
-    if ((rc = linear(lkv, st)) || (rc = marks.mark(5))) return rc;
+    if (fold && !marks.events && linear_pair_supported(lkv, lq)) {
+        // the two projections do not depend on each other: one launch, the q tiles fill the kv tail
+        if ((rc = linear_tcgen05_pair(lkv, lq, st))) return rc;
+    } else {
+        if (!reduce && ((rc = linear(lq, st)) || (rc = marks.mark(4)))) return rc;
+        if ((rc = linear(lkv, st)) || (rc = marks.mark(5))) return rc;
+    }
 
     AttnArgs at;
     const long long e = (long long)elem_size(s.dtype);

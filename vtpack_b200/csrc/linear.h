@@ -45,6 +45,8 @@ int linear_validate(const LinearArgs& p);
 int linear_cuda_cores(const LinearArgs& p, cudaStream_t st);   // fp32 or bf16 inputs, CUDA cores
 int linear_tcgen05(const LinearArgs& p, cudaStream_t st);      // bf16 inputs, tcgen05 + TMA
 int linear(const LinearArgs& p, cudaStream_t st);              // picks by dtype / flags
+bool linear_pair_supported(const LinearArgs& a, const LinearArgs& b);
+int linear_tcgen05_pair(const LinearArgs& a, const LinearArgs& b, cudaStream_t st);   // two problems, one launch
 
 struct RowMap { int out_grp, out_skip, res_mod, res_off; };
 __device__ __forceinline__ long long map_out_row(const RowMap& r, int m) {

@@ -112,14 +112,22 @@ __device__ __forceinline__ void gelu8(float* v) {
 // GELU / LayerNorm arithmetic issued, predicated off, by every GEMM).
 constexpr int EPI_GELU = 1, EPI_LN = 2, EPI_EMIT = 4;
 
-template <int BN, int STAGES, typename OutT, int EPI>
+// One GEMM problem of a launch: its tensor maps and epilogue operands.
+struct TcProblem {
+    CUtensorMap ta, tw, tw2, tw3, ty, tr;    // A, W (tile / half / quarter height boxes), output, residual
+    const float* bias; const bf16* res; long long ldr;
+    void* y; long long ldy;
+    int m_max; const int32_t* m_dev; int N;
+    int use_tma_store;
+    RowMap rm; LnFold ln;
+};
+// A launch works through one problem or two independent ones (same K, tile shape and epilogue kind): the
+// tiles of the second fill the last, partial round of the first, and one launch's ramp and tail is saved.
+struct TcLaunch { TcProblem p[2]; int n; };
+
+template <int BN, int STAGES, typename OutT, int EPI, int NPROB>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
-                 const __grid_constant__ CUtensorMap tmap_w2, const __grid_constant__ CUtensorMap tmap_w3,
-                 const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_r,
-                 int use_tma_store, const float* __restrict__ bias, const bf16* __restrict__ res, long long ldr,
-                 OutT* __restrict__ y, long long ldy, int m_max, const int32_t* __restrict__ m_dev, int N,
-                 int K, unsigned flags, RowMap rm, LnFold ln, int* status) {
+linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
     using S = TcSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -170,16 +178,25 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // here on its results (row count, operands, residual, statistics) are read.
     griddep_launch();
     griddep_wait();
-    int M = m_max;
-    if (m_dev) M = min(*reinterpret_cast<const volatile int32_t*>(m_dev), m_max);
-    const int n_tiles = (N + BN - 1) / BN;
+    // valid rows, column tiles and tile count of each problem
+    int Mp[2], ntp[2], totp[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        Mp[i] = ntp[i] = totp[i] = 0;
+        if (i < NPROB) {
+            Mp[i] = L.p[i].m_max;
+            if (L.p[i].m_dev) Mp[i] = min(*reinterpret_cast<const volatile int32_t*>(L.p[i].m_dev), L.p[i].m_max);
+            ntp[i] = (L.p[i].N + BN - 1) / BN;
+            totp[i] = ((Mp[i] + TBM - 1) / TBM) * ntp[i];
+        }
+    }
     // no tiles for this CTA, or an earlier CTA gave up on a wait (the launch is void): skip the work
     const bool void_launch = status && (*reinterpret_cast<volatile int*>(status) & STATUS_WAIT_MASK) != 0;
-    const int total = void_launch ? 0 : ((M + TBM - 1) / TBM) * n_tiles;
+    const int total = void_launch ? 0 : totp[0] + totp[1];
     // Tail splitting.  A CTA takes tiles blockIdx.x, + gridDim.x, ...; the R tiles left for the last,
     // partial round are cut into `parts` column strips of BN / parts columns, one strip per CTA, so that
     // the round costs a fraction of a tile instead of a whole one with most SMs idle.  Strips use their
-    // own W boxes (tmap_w2 / tmap_w3) and a narrower MMA; kernels that keep per-tile row statistics
+    // own W boxes (tw2 / tw3) and a narrower MMA; kernels that keep per-tile row statistics
     // (EPI_EMIT) do not split.
     const int full_items = (total / (int)gridDim.x) * (int)gridDim.x;
     int parts = 1;
@@ -191,11 +208,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             else parts = (R * 2 <= G) ? 2 : 1;
         }
     }
-    // j-th work item of this CTA: rows m0.., columns ct0 .. ct0 + width of the output
-    struct Item { int m0, nt, ct0, width; };
+    // j-th work item of this CTA: problem p, rows m0.., columns ct0 .. ct0 + width of its output.  The last
+    // column tile of a problem whose N is not a multiple of BN is as wide as the columns left, in 64s.
+    struct Item { int p, m0, nt, ct0, width; };
     auto item_at = [&](int j, Item& it) -> bool {
         const int idx = (int)blockIdx.x + j * (int)gridDim.x;
-        int tile, sub = 0, p = 1;
+        int tile, sub = 0, pr = 1;
         if (idx < full_items) {
             tile = idx;
         } else {
@@ -203,26 +221,35 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (u >= (total - full_items) * parts) return false;
             tile = full_items + u / parts;
             sub = u % parts;
-            p = parts;
+            pr = parts;
         }
-        it.m0 = (tile / n_tiles) * TBM;
-        it.nt = tile % n_tiles;
-        it.width = BN / p;
+        it.p = (NPROB == 2 && tile >= totp[0]) ? 1 : 0;       // one-problem launches index their problem statically
+        const int lt = tile - (it.p ? totp[0] : 0);
+        const int n_tiles = ntp[it.p];
+        it.m0 = (lt / n_tiles) * TBM;
+        it.nt = lt % n_tiles;
+        int tile_w = BN;
+        if (NPROB == 2) {
+            // narrow last column tile where a W box of that height exists (128 or 64 columns at BN = 256)
+            const int cols_left = ((L.p[it.p].N - it.nt * BN + 63) / 64) * 64;
+            if (BN == 256 && (cols_left == 64 || cols_left == 128)) tile_w = cols_left;
+        }
+        it.width = pr == 1 ? tile_w : BN / pr;
         it.ct0 = it.nt * BN + sub * it.width;
-        return true;
+        return sub * it.width < tile_w;        // a strip beyond a narrow tile's columns does not exist
     };
 
     if (warp == 0) {
         if (lane == 0) {
             // ------------------------------------------------------------ TMA producer
-            prefetch_tmap(&tmap_a);
-            prefetch_tmap(&tmap_w);
+            for (int i = 0; i < NPROB; ++i) { prefetch_tmap(&L.p[i].ta); prefetch_tmap(&L.p[i].tw); }
             int it = 0;
             bool ok = true;
             Item wi;
             for (int j = 0; ok && item_at(j, wi); ++j) {
                 // the W box that is as tall as the item is wide
-                const CUtensorMap* wm = wi.width == BN ? &tmap_w : ((BN == 256 && wi.width == 64) ? &tmap_w3 : &tmap_w2);
+                const TcProblem& P = L.p[wi.p];
+                const CUtensorMap* wm = wi.width == BN ? &P.tw : ((BN == 256 && wi.width == 64) ? &P.tw3 : &P.tw2);
                 const uint32_t bytes = S::A_BYTES + (uint32_t)wi.width * TBK * 2;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -230,7 +257,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, status, STATUS_GEMM_PRODUCER);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&full[s], bytes);
-                    tma_load_2d(smem_a + s * S::A_BYTES, &tmap_a, &full[s], kb * TBK, wi.m0);
+                    tma_load_2d(smem_a + s * S::A_BYTES, &P.ta, &full[s], kb * TBK, wi.m0);
                     tma_load_2d(smem_b + s * S::B_BYTES, wm, &full[s], kb * TBK, wi.ct0);
                 }
             }
@@ -270,20 +297,31 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         __syncwarp();
     } else if (warp == 2 + EPI_THREADS / 32) {
-        if (lane == 0 && use_tma_store) {
+        if (lane == 0 && L.p[0].use_tma_store) {
             // -------------------------------------------------------------- store thread
             // Walks the staged slabs in the epilogue's order: (item j, slab sl) of every item whose 128 rows
             // are all valid (the items with the last, partial rows come last and store from registers).
             struct Cursor { int j, sl; Item it; bool ok; };
-            auto first = [&]() { Cursor c; c.j = 0; c.sl = 0; c.ok = item_at(0, c.it) && c.it.m0 + TBM <= M; return c; };
+            // the staged items: all 128 rows valid.  (Items with the last, partial rows of a problem store from
+            // registers; they are skipped here exactly as the epilogue warps skip the staging for them.)
+            auto staged = [&](const Item& it) { return it.m0 + TBM <= Mp[it.p]; };
+            auto seek = [&](Cursor& c) {                  // first staged item at or after c.j
+                for (;;) {
+                    if (!item_at(c.j, c.it)) { c.ok = false; return; }
+                    if (staged(c.it)) { c.ok = true; return; }
+                    ++c.j;
+                }
+            };
+            auto first = [&]() { Cursor c; c.j = 0; c.sl = 0; seek(c); return c; };
             auto advance = [&](Cursor& c) {
-                if (++c.sl == c.it.width / 64) { c.sl = 0; ++c.j; c.ok = item_at(c.j, c.it) && c.it.m0 + TBM <= M; }
+                if (++c.sl == c.it.width / 64) { c.sl = 0; ++c.j; seek(c); }
             };
             auto load_residual = [&](const Cursor& c, int b) {
                 mbar_arrive_expect_tx(&res_full[b], TBM * 128);
-                tma_load_2d(smem_out + b * (TBM * 128), &tmap_r, &res_full[b], c.it.ct0 + c.sl * 64, c.it.m0);
+                tma_load_2d(smem_out + b * (TBM * 128), &L.p[c.it.p].tr, &res_full[b], c.it.ct0 + c.sl * 64, c.it.m0);
             };
             Cursor cur = first(), ahead = cur;        // `ahead` runs two slabs in front (residual prefetch)
+            const bool res = L.p[0].res != nullptr;
             if (res) {
                 for (int b = 0; b < 2 && ahead.ok; ++b) { load_residual(ahead, b); advance(ahead); }
             }
@@ -292,7 +330,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int b = slab_no & 1;
                 ok = mbar_wait(&slab_full[b], (slab_no >> 1) & 1, abort_flag, status, STATUS_GEMM_EPILOGUE);
                 if (!ok) break;
-                tma_store_2d(&tmap_y, smem_out + b * (TBM * 128), cur.it.ct0 + cur.sl * 64, cur.it.m0);
+                tma_store_2d(&L.p[cur.it.p].ty, smem_out + b * (TBM * 128), cur.it.ct0 + cur.sl * 64, cur.it.m0);
                 bulk_commit_group();
                 bulk_wait_group_read0();              // the slab has been read: it can be written again
                 if (res) {
@@ -313,12 +351,17 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         bool ok = true;
         Item wi;
         for (int j = 0; ok && item_at(j, wi); ++j, ++lt) {
+            const TcProblem& P = L.p[wi.p];
+            const int M = Mp[wi.p], N = P.N;
+            const float* __restrict__ bias = P.bias;
+            const bf16* __restrict__ res = P.res;
+            const LnFold& ln = P.ln;
             const int m0 = wi.m0;
             const int nt0 = wi.ct0;                   // first output column of the item
             const int NSLAB = wi.width / 64;          // 64-column slabs in it
             const int buf = lt & 1;
             const uint32_t aph = (lt >> 1) & 1;
-            const bool tma_path = use_tma_store && m0 + TBM <= M;
+            const bool tma_path = P.use_tma_store && m0 + TBM <= M;
             if (tma_path) {
                 // this tile's bias slice -> shared memory (one value per thread), so the column
                 // loop reads it as a broadcast instead of through the global-load path
@@ -362,7 +405,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (EPI & EPI_LN) {
                 // warm L1 with the row statistics the next tile of this CTA will start with
                 Item nxt;
-                const int mn = item_at(j + 1, nxt) ? nxt.m0 + row : M;
+                const int mn = (item_at(j + 1, nxt) && nxt.p == wi.p) ? nxt.m0 + row : M;
                 if (mn < M) {
                     const float2* nxt = ln.stats + (size_t)mn * (ln.mode == 2 ? STAT_SLOTS : 1);
                     asm volatile("prefetch.global.L1 [%0];" ::"l"(nxt));
@@ -459,8 +502,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // ---- boundary tile / row-remapped / fp32 output: store straight from registers
             const int m = m0 + row;
             const bool row_ok = m < M;
-            const long long orow = map_out_row(rm, row_ok ? m : m0);
-            const long long rrow = map_res_row(rm, row_ok ? m : m0);
+            const long long orow = map_out_row(P.rm, row_ok ? m : m0);
+            const long long rrow = map_res_row(P.rm, row_ok ? m : m0);
+            OutT* __restrict__ y = static_cast<OutT*>(P.y);
+            const long long ldy = P.ldy, ldr = P.ldr;
             // same column split as the staged path (16 columns of each 64-column slab per warp), so a
             // row's statistics do not depend on which kind of tile it falls in
 #pragma unroll 1
@@ -567,66 +612,82 @@ int make_tmap_bf16(CUtensorMap* map, const void* base, int rank, const unsigned 
     return VTP_OK;
 }
 
-template <int BN, int STAGES, typename OutT, int EPI>
-static int launch_tc(const LinearArgs& p, cudaStream_t st) {
-    using S = TcSmem<BN, STAGES>;
-    CUtensorMap ta, tw;
+template <int BN, typename OutT>
+static int fill_problem(TcProblem& q, const LinearArgs& p) {
     {
         const unsigned long long dims[2] = {(unsigned long long)p.K, (unsigned long long)p.m_max};
         const unsigned long long strides[1] = {(unsigned long long)p.lda * 2ull};
         const unsigned box[2] = {TBK, TBM};
-        if (int rc = make_tmap_bf16(&ta, p.a, 2, dims, strides, box)) return rc;
+        if (int rc = make_tmap_bf16(&q.ta, p.a, 2, dims, strides, box)) return rc;
     }
     {
+        // W boxes: a whole tile, and the column strips of split tail tiles / narrow last tiles (half, or a
+        // third for BN = 192, and a quarter)
         const unsigned long long dims[2] = {(unsigned long long)p.K, (unsigned long long)p.N};
         const unsigned long long strides[1] = {(unsigned long long)p.K * 2ull};
         const unsigned box[2] = {TBK, BN};
-        if (int rc = make_tmap_bf16(&tw, p.w, 2, dims, strides, box)) return rc;
-    }
-    // W boxes for the column strips of split tail tiles: half (third for BN = 192) and quarter height
-    CUtensorMap tw2 = tw, tw3 = tw;
-    {
-        const unsigned long long dims[2] = {(unsigned long long)p.K, (unsigned long long)p.N};
-        const unsigned long long strides[1] = {(unsigned long long)p.K * 2ull};
+        if (int rc = make_tmap_bf16(&q.tw, p.w, 2, dims, strides, box)) return rc;
         const unsigned box2[2] = {TBK, BN == 256 ? 128u : 64u};
-        if (int rc = make_tmap_bf16(&tw2, p.w, 2, dims, strides, box2)) return rc;
+        if (int rc = make_tmap_bf16(&q.tw2, p.w, 2, dims, strides, box2)) return rc;
         const unsigned box3[2] = {TBK, 64u};
-        if (int rc = make_tmap_bf16(&tw3, p.w, 2, dims, strides, box3)) return rc;
+        if (int rc = make_tmap_bf16(&q.tw3, p.w, 2, dims, strides, box3)) return rc;
     }
     // Output map for the TMA-store epilogue (bf16 output, rows not remapped).
-    const int use_tma_store = (sizeof(OutT) == 2 && p.out_grp == 0) ? 1 : 0;
-    CUtensorMap ty = tw, tr = tw;
-    if (use_tma_store) {
+    q.use_tma_store = (sizeof(OutT) == 2 && p.out_grp == 0) ? 1 : 0;
+    q.ty = q.tw;
+    q.tr = q.tw;
+    if (q.use_tma_store) {
         const unsigned long long dims[2] = {(unsigned long long)p.N, (unsigned long long)p.m_max};
         const unsigned long long strides[1] = {(unsigned long long)p.ldy * 2ull};
         const unsigned box[2] = {64, TBM};
-        if (int rc = make_tmap_bf16(&ty, p.y, 2, dims, strides, box)) return rc;
+        if (int rc = make_tmap_bf16(&q.ty, p.y, 2, dims, strides, box)) return rc;
         if (p.res) {
             const unsigned long long rstrides[1] = {(unsigned long long)p.ldr * 2ull};
-            if (int rc = make_tmap_bf16(&tr, p.res, 2, dims, rstrides, box)) return rc;
+            if (int rc = make_tmap_bf16(&q.tr, p.res, 2, dims, rstrides, box)) return rc;
         }
     }
-    auto kern = linear_tc_kernel<BN, STAGES, OutT, EPI>;
-    static bool attr_set[64] = {};   // per instantiation and device
+    q.bias = p.bias; q.res = (const bf16*)p.res; q.ldr = p.ldr; q.y = p.y; q.ldy = p.ldy;
+    q.m_max = p.m_max; q.m_dev = p.m_dev; q.N = p.N;
+    q.rm = RowMap{p.out_grp, p.out_skip, p.res_mod, p.res_off};
+    VTP_REQUIRE(!p.emit_stats || ceil_div(p.N, BN) * 4 <= STAT_SLOTS, VTP_ERR_SHAPE,
+                "linear (tcgen05): N=%d has too many column tiles for the row-statistics slots", p.N);
+    q.ln = LnFold{p.ln_stats, p.ln_s, p.ln_mode, p.ln_dim, p.ln_eps, p.emit_stats, p.ln_slots};
+    return VTP_OK;
+}
+
+// p1 = null: one problem.  Otherwise two problems of the same K and epilogue kind in one launch.
+template <int BN, int STAGES, typename OutT, int EPI>
+static int launch_tc(const LinearArgs& p, const LinearArgs* p1, cudaStream_t st) {
+    using S = TcSmem<BN, STAGES>;
+    TcLaunch L;
+    L.n = p1 ? 2 : 1;
+    if (int rc = fill_problem<BN, OutT>(L.p[0], p)) return rc;
+    if (p1) {
+        if (int rc = fill_problem<BN, OutT>(L.p[1], *p1)) return rc;
+    } else {
+        L.p[1] = L.p[0];
+    }
+    if (p1 && !(BN == 256 && EPI == EPI_LN && sizeof(OutT) == 2))
+        return fail(VTP_ERR_UNSUPPORTED, "linear (tcgen05): two-problem launches are built for 256-wide LayerNorm-fold tiles");
+    auto kern = (p1 && BN == 256 && EPI == EPI_LN && sizeof(OutT) == 2) ? linear_tc_kernel<BN, STAGES, OutT, EPI, (BN == 256 && EPI == EPI_LN && sizeof(OutT) == 2) ? 2 : 1>
+                                                                       : linear_tc_kernel<BN, STAGES, OutT, EPI, 1>;
+    static bool attr_set[64][2] = {};   // per instantiation, device and problem count
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    const int np = p1 ? 1 : 0;
+    if (dev < 0 || dev >= 64 || !attr_set[dev][np]) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
         if (e != cudaSuccess) {
             set_error("linear (tcgen05): cannot reserve %d bytes of shared memory: %s", S::TOTAL,
                       cudaGetErrorString(e));
             return (int)e;
         }
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev][np] = true;
     }
-    const long long tiles = (long long)ceil_div(p.N, BN) * ceil_div(p.m_max, TBM);
+    long long tiles = (long long)ceil_div(p.N, BN) * ceil_div(p.m_max, TBM);
+    if (p1) tiles += (long long)ceil_div(p1->N, BN) * ceil_div(p1->m_max, TBM);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    const RowMap rm{p.out_grp, p.out_skip, p.res_mod, p.res_off};
-    VTP_REQUIRE(!p.emit_stats || ceil_div(p.N, BN) * 4 <= STAT_SLOTS, VTP_ERR_SHAPE,
-                "linear (tcgen05): N=%d has too many column tiles for the row-statistics slots", p.N);
-    const LnFold ln{p.ln_stats, p.ln_s, p.ln_mode, p.ln_dim, p.ln_eps, p.emit_stats, p.ln_slots};
-    const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), (size_t)S::TOTAL, st, ta, tw, tw2, tw3, ty, tr, use_tma_store, p.bias, (const bf16*)p.res, p.ldr, (OutT*)p.y, p.ldy, p.m_max,
-                                      p.m_dev, p.N, p.K, p.flags, rm, ln, device_status_ptr());
+    const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), (size_t)S::TOTAL, st, L, p.K, device_status_ptr());
     if (le != cudaSuccess) {
         cudaGetLastError();
         set_error("linear (tcgen05): %s", cudaGetErrorString(le));
@@ -646,6 +707,40 @@ static int pick_bn(int N) {
 
 int linear_stat_slots(int N) { return ceil_div(N, pick_bn(N)) * 4; }
 
+static int check_tc_args(const LinearArgs& p) {
+    VTP_REQUIRE(p.dtype == VTP_BF16, VTP_ERR_DTYPE, "linear (tcgen05): bf16 operands only");
+    VTP_REQUIRE(p.K % TBK == 0, VTP_ERR_SHAPE, "linear (tcgen05): K=%d must be a multiple of %d", p.K, TBK);
+    VTP_REQUIRE(p.N % 8 == 0, VTP_ERR_SHAPE, "linear (tcgen05): N=%d must be a multiple of 8", p.N);
+    VTP_REQUIRE(p.ln_mode == 0 || (p.ln_stats && p.ln_s && p.out_grp == 0 &&
+                                   (p.ln_mode == 1 || (p.ln_dim > 0 && p.ln_slots > 0 && p.ln_slots <= STAT_SLOTS))),
+                VTP_ERR_NULL, "linear (tcgen05): folded LayerNorm needs row statistics and the column sums");
+    VTP_REQUIRE(p.lda % 8 == 0 && p.ldy % 8 == 0 && (!p.res || p.ldr % 8 == 0), VTP_ERR_ALIGN,
+                "linear (tcgen05): row strides must be multiples of 16 bytes");
+    return VTP_OK;
+}
+
+// Two independent Linears that follow the same kind of LayerNorm fold (the q and kv projections of a block)
+// in ONE launch of 128 x 256 tiles: the tiles of the second problem fill the last, partial round of the first,
+// and one launch's ramp and tail is saved.  Both: bf16 output, bias + folded LayerNorm (ln_mode 1), no
+// residual, no row remap; an N that is not a multiple of 256 must leave 64 or 128 columns.
+bool linear_pair_supported(const LinearArgs& a, const LinearArgs& b) {
+    auto ok = [](const LinearArgs& p) {
+        const int rem = p.N % 256;
+        return p.dtype == VTP_BF16 && p.ln_mode == 1 && !p.res && !p.emit_stats && p.out_grp == 0 && p.flags == 0 &&
+               p.m_max > 0 && p.N >= 256 && (rem == 0 || rem == 64 || rem == 128);
+    };
+    return ok(a) && ok(b) && a.K == b.K;
+}
+
+int linear_tcgen05_pair(const LinearArgs& a, const LinearArgs& b, cudaStream_t st) {
+    if (int rc = linear_validate(a)) return rc;
+    if (int rc = linear_validate(b)) return rc;
+    if (int rc = check_tc_args(a)) return rc;
+    if (int rc = check_tc_args(b)) return rc;
+    VTP_REQUIRE(linear_pair_supported(a, b), VTP_ERR_UNSUPPORTED, "linear (tcgen05): these two problems cannot share a launch");
+    return launch_tc<256, 4, bf16, EPI_LN>(a, &b, st);
+}
+
 int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
     if (p.m_max == 0) return VTP_OK;
     VTP_REQUIRE(p.dtype == VTP_BF16, VTP_ERR_DTYPE, "linear (tcgen05): bf16 operands only");
@@ -661,15 +756,15 @@ int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
     const int epi = ((p.flags & VTP_FLAG_GELU) ? EPI_GELU : 0) | (p.ln_mode ? EPI_LN : 0) | (p.emit_stats ? EPI_EMIT : 0);
     if (f32) {
         VTP_REQUIRE(epi == 0, VTP_ERR_UNSUPPORTED, "linear (tcgen05): fp32 output supports bias and residual only");
-        if (bn == 256) return launch_tc<256, 4, float, 0>(p, st);
-        if (bn == 192) return launch_tc<192, 4, float, 0>(p, st);
-        return launch_tc<128, 5, float, 0>(p, st);
+        if (bn == 256) return launch_tc<256, 4, float, 0>(p, nullptr, st);
+        if (bn == 192) return launch_tc<192, 4, float, 0>(p, nullptr, st);
+        return launch_tc<128, 5, float, 0>(p, nullptr, st);
     }
 #define VTP_TC_CASE(E)                                                  \
     if (epi == (E)) {                                                   \
-        if (bn == 256) return launch_tc<256, 4, bf16, (E)>(p, st);      \
-        if (bn == 192) return launch_tc<192, 4, bf16, (E)>(p, st);      \
-        return launch_tc<128, 5, bf16, (E)>(p, st);                     \
+        if (bn == 256) return launch_tc<256, 4, bf16, (E)>(p, nullptr, st);      \
+        if (bn == 192) return launch_tc<192, 4, bf16, (E)>(p, nullptr, st);      \
+        return launch_tc<128, 5, bf16, (E)>(p, nullptr, st);                     \
     }
     VTP_TC_CASE(0)
     VTP_TC_CASE(EPI_GELU)
