@@ -185,9 +185,10 @@ def front_back_ms(model, batch, device, image_bytes, iters=10):
     return total
 
 
-def stage_profile(model, batch, device, iters, pk, ms_per_step):
-    """Per-kernel times of one DGE block (a middle block's weights) on N(0,1) tokens, from events the library
-    records between its launches.  Every stage then sits between two event records, which keeps a launch from
+def stage_profile(model, batch, device, iters, pk, ms_per_step, tokens=None, forced=None):
+    """Per-kernel times of one DGE block (the middle block's weights, on the tokens that block received in the
+    model's own forward when `tokens` is given, else on N(0,1) tokens), from events the library records
+    between its launches.  Every stage then sits between two event records, which keeps a launch from
     queueing behind the one in front of it: these are upper bounds of what a kernel costs inside the replayed
     graph.  `ms_in_step_est` scales them so that depth x block + the front/back launches equals the measured
     step.  Returns (rows, the five Linear launches together, block summary)."""
@@ -200,7 +201,10 @@ def stage_profile(model, batch, device, iters, pk, ms_per_step):
     C, N = model.embed_dim, G * G + 1
     dtype = model.compute_dtype()
     e = 2 if dtype == torch.bfloat16 else 4
-    x = torch.randn(batch, N, C, device=device, generator=torch.Generator(device).manual_seed(3)).to(dtype)
+    if tokens is not None:
+        x = tokens.contiguous()
+    else:
+        x = torch.randn(batch, N, C, device=device, generator=torch.Generator(device).manual_seed(3)).to(dtype)
     out = torch.empty_like(x)
     s = blk.shape_struct(x)
     w = _pack_block(blk, dtype)
@@ -217,12 +221,16 @@ def stage_profile(model, batch, device, iters, pk, ms_per_step):
             ev.record(stream)            # creates the underlying cudaEvent_t
         arr = (ctypes.c_void_p * n_ev)(*[ev.cuda_event for ev in row])
         _lib.check(lib.vtp_dge_block_forward_timed(ctypes.byref(s), ctypes.byref(w), x.data_ptr(), out.data_ptr(),
-                                                   None, counts.data_ptr(), ws.data_ptr(), nbytes, arr, n_ev,
+                                                   forced.data_ptr() if forced is not None else None,
+                                                   counts.data_ptr(), ws.data_ptr(), nbytes, arr, n_ev,
                                                    stream.cuda_stream))
     torch.cuda.synchronize(device)
     L = int(counts.sum().item())
-    grains = region_grains(x, blk._pack.tensors["gate_w"], blk._pack.tensors["gate_b"], G, device)
-    fine = float((grains == 0).float().mean().item())
+    if forced is not None:
+        fine = float((forced.argmax(-1) == 0).float().mean().item())
+    else:
+        grains = region_grains(x, blk._pack.tensors["gate_w"], blk._pack.tensors["gate_b"], G, device)
+        fine = float((grains == 0).float().mean().item())
     ms = [sum(evs[i][j].elapsed_time(evs[i][j + 1]) for i in range(iters)) / iters for j in range(len(STAGES))]
     BN, H, HW = batch * N, 4 * C, G * G
     work = {   # (kind, algorithmic bytes or flops)
@@ -316,16 +324,18 @@ def kv_launch_roofline(model, batch, device, pk, iters=20):
                       f"{(M * C + M * 2 * C) * 2 / 1e6:.0f} MB per launch (> L2)"}
 
 
-def fine_fraction(model, img_dev):
-    """Fraction of regions at the finest grain in each block of a forward (from the grain trace)."""
+def traced_forward(model, img_dev):
+    """One launch-by-launch forward with the traces on: the fraction of regions at the finest grain in each
+    block, and the tokens the middle block received (the input of the per-kernel profile)."""
     keep = model.trace
-    model.trace = "grains"
+    model.trace = True
     model(img_dev)
     torch.cuda.synchronize(img_dev.device)
     f = (model.last_grains == 0).float().mean(dim=(1, 2)).cpu().tolist()
+    mid = model.last_tokens[len(model.blocks) // 2].clone()
     model.trace = keep
-    model.last_grains = None
-    return f
+    model.last_grains = model.last_tokens = None
+    return f, mid
 
 
 def model_roofline(model, batch, counts, ms_per_step, pk, image_bytes, fine):
@@ -563,6 +573,17 @@ def pvt_sweep(args):
     e1.record()
     torch.cuda.synchronize()
     model_ms = e0.elapsed_time(e1) / 10
+    # the same forward replayed as one CUDA graph (no host work between its ~60 launches)
+    for _ in range(3):
+        m.forward_graph(img)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(20):
+        m.forward_graph(img)
+    e1.record()
+    torch.cuda.synchronize()
+    graph_ms = e0.elapsed_time(e1) / 20
+    diff = float((m.forward_graph(img) - m(img)).abs().max())
     xc = O.make_images(4, 256, seed=5)
     t0 = time.perf_counter()
     O.pvt_dge_forward(xc, sd, cfg)
@@ -570,6 +591,9 @@ def pvt_sweep(args):
     assert _lib.device_status() == 0
     print(json.dumps({"pvt_sweep": rows, "batch": B, "dtype": "bf16",
                       "pvt_tiny_model": {"ms_per_forward": round(model_ms, 3), "images_per_s": round(B / model_ms * 1e3),
+                                         "ms_per_forward_graph": round(graph_ms, 3),
+                                         "images_per_s_graph": round(B / graph_ms * 1e3),
+                                         "graph_vs_launch_by_launch_max_abs_diff": diff,
                                          "cpu_oracle_images_per_s": round(cpu_rate, 1)}}), flush=True)
 
 
@@ -863,16 +887,24 @@ def main():
         }
         if e2e_other:
             line["e2e_other_host_dtype"] = e2e_other
+        mid_tokens = None
         if dtype == torch.bfloat16 and not args.cuda_cores:
+            fine, mid_tokens = traced_forward(model, img_dev)
             line["roofline"] = kv_launch_roofline(model, B, device, pk)
             line["model_roofline"] = model_roofline(model, B, counts_cpu, ms_total / args.steps, pk,
-                                                    img_dev.element_size(), fine_fraction(model, img_dev))
+                                                    img_dev.element_size(), fine)
         if not args.no_stage_profile and dtype == torch.bfloat16 and not args.cuda_cores:
-            rows, all_linear, extra = stage_profile(model, B, device, 10, pk, ms_total / args.steps)
+            forced = None
+            if model.gate_image_bias is not None:     # the block entry point takes forced logits, not a per-image bias
+                R = (S // 16) // 4
+                forced = model.gate_image_bias[:, None, None, :].expand(B, R, R, 3).contiguous()
+            rows, all_linear, extra = stage_profile(model, B, device, 10, pk, ms_total / args.steps, mid_tokens, forced)
             line["roofline"]["all_linear_launches_of_a_block"] = all_linear
             line["roofline"]["frac_all_launches"] = all_linear["frac_in_step_est"]
             line["kernels"] = rows
-            line["kernels_note"] = ("ms_event_bracketed: every stage sits between two event records, which keeps the "
+            line["kernels_note"] = ("one block (the middle one's weights and the tokens it received in this forward), "
+                                    "q and kv projections as separate launches (the forward pairs them in one); "
+                                    "ms_event_bracketed: every stage sits between two event records, which keeps the "
                                     "next launch from queueing behind the running one: an upper bound. ms_in_step_est "
                                     "= that share scaled so that depth x block + front/back equals ms_per_step")
             line["block"] = extra

@@ -7,13 +7,19 @@
 // backward products, which the reference also spells as forward calls with other transpose flags
 // (vtpack/layers/sparse_ops.py:30-55).
 //
-// Shapes per (image, head) are small (about 113 x 257 x 64 in DeiT-S+DGE), so this is a
-// shared-memory tiled CUDA-core kernel: 64 x 64 output tile, 16-deep slices, 256 threads with a
+// bf16 operands go to the tcgen05 kernel of ragged_gemm_tc.cu; fp32 operands (full-precision products)
+// take the kernel in this file.  Shapes per (image, head) are small (about 113 x 257 x 64 in
+// DeiT-S+DGE): a shared-memory tiled CUDA-core kernel: 64 x 64 output tile, 16-deep slices, 256 threads with a
 // 4 x 4 accumulator block each, fp32 accumulation in slice order.  The loads walk whichever axis is
 // contiguous in memory for the given transpose flag; row lengths need no alignment.
 #include "common.cuh"
 
 namespace vtp {
+
+// bf16: the tensor-core kernel (ragged_gemm_tc.cu)
+int ragged_gemm_tcgen05(const void* a, const void* b, void* out, int heads, int n_images, long long a_rows,
+                        int a_cols, long long b_rows, int b_cols, const int32_t* a_off, const int32_t* b_off,
+                        int max_m, int max_n, int ta, int tb, long long out_rows, int out_cols, cudaStream_t st);
 
 constexpr int RG_TM = 64, RG_TN = 64, RG_TK = 16, RG_THREADS = 256;
 
@@ -136,6 +142,10 @@ extern "C" int vtp_batched_sparse_gemm(const void* a, const void* b, void* out, 
     VTP_REQUIRE(max_n <= out_cols, VTP_ERR_SHAPE, "batched_sparse_gemm: %d output columns, buffer has %d", max_n,
                 out_cols);
     if (max_m == 0 || max_n == 0 || out_rows == 0) return VTP_OK;
+    if (dtype == VTP_BF16)       // tensor cores; fp32 keeps full-precision products on CUDA cores
+        return ragged_gemm_tcgen05(a, b, out, heads, n_images, a_rows, a_cols, b_rows, b_cols, a_offsets, b_offsets,
+                                   max_m, max_n, a_transposed ? 1 : 0, b_transposed ? 1 : 0, out_rows, out_cols,
+                                   static_cast<cudaStream_t>(stream));
     RaggedGemmArgs g;
     g.a = a; g.b = b; g.out = out;
     g.a_rows = a_rows; g.b_rows = b_rows; g.out_rows = out_rows;

@@ -18,7 +18,7 @@ import torch.nn as nn
 
 from ... import _lib
 from ...layers import DynamicGrainedEncoder, batched_sparse_attention, batched_sparse_gemm
-from ...runtime import dtype_code, ptr, require_cuda, scratch, stream_ptr
+from ...runtime import dtype_code, ptr, require_cuda, scratch, scratch_generation, stream_ptr
 from .deit_dge import DropPath, Mlp, _WeightPack, _pack_block, _shape_struct
 
 __all__ = ["Mlp", "Attention", "Block", "PatchEmbed", "PyramidVisionTransformer",
@@ -236,6 +236,36 @@ class PyramidVisionTransformer(nn.Module):
             elif isinstance(m, DynamicGrainedEncoder):
                 m.router.init_parameters()
         self.last_counts = None
+
+    def forward_graph(self, x):
+        """Eval forward through a CUDA graph captured for this input buffer (its contents may change between
+        calls, its address and shape may not); returns the graph's own output tensor, overwritten by the next
+        call.  The stages are sequenced from Python through some sixty small launches per forward; replaying
+        them as one graph removes the host work between them.  The graph is captured again when a parameter
+        has changed, when the per-device scratch buffer has been replaced, or for another input buffer."""
+        if self.training:
+            raise RuntimeError("forward_graph is an eval-mode path")
+        key = (x.data_ptr(), tuple(x.shape), x.dtype,
+               tuple((p.data_ptr(), p._version) for p in self.parameters()))
+        g = getattr(self, "_graph", None)
+        if g is None or g["key"] != key or g["scratch_gen"] != scratch_generation(x.device):
+            cur = torch.cuda.current_stream(x.device)
+            side = torch.cuda.Stream(x.device)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):          # warm-up outside capture: scratch, attributes, weight packs
+                for _ in range(2):
+                    self.forward(x)
+            cur.wait_stream(side)
+            torch.cuda.synchronize(x.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.forward(x)
+            g = {"key": key, "graph": graph, "out": out, "counts": self.last_counts, "x": x,
+                 "scratch": scratch(x.device, 1), "scratch_gen": scratch_generation(x.device)}
+            self._graph = g
+        g["graph"].replay()
+        self.last_counts = g["counts"]
+        return g["out"]
 
     def _stage_pos_embed(self, pos_embed, patch_embed, H, W):
         """The stage's position embedding, bilinearly resized when the token grid is not the one it
