@@ -369,3 +369,36 @@ def test_attention_offsets_beyond_the_buffers_are_clamped(vl):
         ref = O.batched_sparse_attention_forward(qh, k, v, torch.tensor([30, 10]), d ** -0.5)
         got = out[:l_max].reshape(l_max, h, d).permute(1, 0, 2).float().cpu()
         assert rel_err(got, ref) < 2e-2
+
+
+def test_gelu_epilogue_error_on_a_dense_sweep(vl):
+    """The tensor-core Linear evaluates erf-GELU as a tanh fit in packed fp16.  Through an identity weight the
+    epilogue sees the inputs themselves: a dense sweep of [-12, 12], the far range up to the fp16 limit, and
+    the non-finite values.  Bound: 4e-3 absolute up to |x| = 1 and 4e-3 relative beyond (the fit's 2.7e-4, the
+    fp16 arithmetic's 5e-4 rms and one bf16 rounding of the result, 2^-9 relative).  Beyond the fp16 range the
+    input saturates at 65504 (the reference would return x itself); -inf gives 0, NaN stays NaN."""
+    _lib, _ = vl
+    lib = _lib.lib()
+    K = 64
+    sweep = torch.cat([torch.linspace(-12, 12, 64 * 254), torch.tensor([20., -20., 100., -100., 1000., -1000.,
+                       6.0e4, -6.0e4, 0., -0.] + [0.] * 54)]).bfloat16()
+    special = torch.tensor([float("inf"), float("-inf"), float("nan"), 1e5, -1e5] + [0.] * 59).bfloat16()
+    x = torch.cat([sweep, special]).reshape(-1, K)                       # [256, 64]
+    M = x.shape[0]
+    w = torch.eye(K).bfloat16()
+    xd, wd = x.to(DEV), w.to(DEV)
+    y = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    _lib.check(lib.vtp_linear(xd.data_ptr(), K, wd.data_ptr(), None, None, 0, y.data_ptr(), K, 1, M, None, K, K,
+                              _lib.FLAG_GELU, None))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    got = y.float().cpu().reshape(-1)
+    xin = x.float().reshape(-1)
+    n_fin = sweep.numel()
+    ref = F.gelu(xin[:n_fin].double()).float()
+    err = (got[:n_fin] - ref).abs()
+    bound = 4e-3 * xin[:n_fin].abs().clamp_min(1.0)
+    assert bool((err <= bound).all()), float((err / bound).max())
+    assert float(err[xin[:n_fin].abs() <= 12].max()) < 8e-3
+    sp = got[n_fin:n_fin + 5]
+    assert sp[0] >= 65000 and sp[1] == 0 and torch.isnan(sp[2]) and sp[3] >= 65000 and sp[4] == 0

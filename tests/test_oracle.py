@@ -346,3 +346,31 @@ def test_forced_indices_and_image_bias_hooks():
     tr2 = []
     O.deit_dge_forward(img, sd, 2, 3, (4, 2, 1), trace=tr2, gate_image_bias=bias)
     assert all(t["batches"].tolist() == [17, 257] for t in tr2)
+
+
+@pytest.mark.parametrize("B,Hr,Wr,extra,seed", [(2, 4, 4, 1, 0), (3, 2, 3, 0, 1), (1, 8, 8, 2, 2)])
+def test_two_restatements_agree_row_for_row(B, Hr, Wr, extra, seed):
+    """The vectorised restatement against the scalar one (one kernel work item at a time, in the kernels'
+    statement order): patch rows in the same ORDER, pooled rows and unpooled tokens bit for bit.  A permuted
+    row order or a transposed sub-patch walk in either would show here, which look-ups by coordinate miss."""
+    from oracle import scalar_check as S
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.randint(0, 3, (B, Hr, Wr), generator=g)
+    sp = torch.tensor([4, 2, 1])
+    p_vec, l_vec = O.grained_sample_index_to_patch(idx, sp, 4, extra)
+    p_sca, l_sca = S.index_to_patch(idx.numpy(), [4, 2, 1], 4, extra)
+    assert l_vec.tolist() == l_sca.tolist()
+    written = p_sca[:, 2] != -7                       # column 2 of extra-token rows is never written by the reference
+    assert (written == (p_sca[:, 1] >= 0)).all()
+    assert np.array_equal(p_vec.numpy()[:, [0, 1, 3]], p_sca[:, [0, 1, 3]])
+    assert np.array_equal(p_vec.numpy()[written, 2], p_sca[written, 2])
+    H, W, C = Hr * 4, Wr * 4, 5
+    x = torch.randn(B, extra + H * W, C, generator=g)
+    comp_vec = O.grained_sample_compress(x, p_vec, H, W, extra)
+    comp_sca = S.compress(x.numpy(), p_vec.numpy(), W, extra)
+    assert np.array_equal(comp_vec.numpy(), comp_sca)
+    q = torch.randn(p_vec.shape[0], C, generator=g)
+    out_vec = O.grained_sample_decompress(q, p_vec, x, H, W, extra, True)
+    out_sca = S.decompress_add_ref(q.numpy(), p_vec.numpy(), x.numpy(), W, extra)
+    assert not np.isnan(out_sca).any()                # every token belongs to exactly one patch
+    assert np.array_equal(out_vec.numpy(), out_sca)

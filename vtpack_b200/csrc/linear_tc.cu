@@ -256,9 +256,15 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
                     const uint32_t ph = (it / STAGES) & 1;
                     ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, status, STATUS_GEMM_PRODUCER);
                     if (!ok) break;
+#if defined(VTP_LINEAR_EXPERIMENT) && (VTP_LINEAR_EXPERIMENT & 1)
+                    // measurement build: no operand traffic, the MMAs run on whatever the ring holds
+                    (void)bytes; (void)wm;
+                    mbar_arrive(&full[s]);
+#else
                     mbar_arrive_expect_tx(&full[s], bytes);
                     tma_load_2d(smem_a + s * S::A_BYTES, &P.ta, &full[s], kb * TBK, wi.m0);
                     tma_load_2d(smem_b + s * S::B_BYTES, wm, &full[s], kb * TBK, wi.ct0);
+#endif
                 }
             }
         }
@@ -330,7 +336,9 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
                 const int b = slab_no & 1;
                 ok = mbar_wait(&slab_full[b], (slab_no >> 1) & 1, abort_flag, status, STATUS_GEMM_EPILOGUE);
                 if (!ok) break;
+#if !(defined(VTP_LINEAR_EXPERIMENT) && (VTP_LINEAR_EXPERIMENT & 2))     // measurement build: no output traffic
                 tma_store_2d(&L.p[cur.it.p].ty, smem_out + b * (TBM * 128), cur.it.ct0 + cur.sl * 64, cur.it.m0);
+#endif
                 bulk_commit_group();
                 bulk_wait_group_read0();              // the slab has been read: it can be written again
                 if (res) {
