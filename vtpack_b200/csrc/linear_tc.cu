@@ -43,7 +43,24 @@ namespace vtp {
 
 using namespace sm100;
 
-constexpr int TBM = 128;   // tile rows = TMEM lanes
+constexpr int TBM = 128;   // tile rows of one CTA = TMEM lanes
+// CTAs per MMA tile.  2: the CTAs of a cluster of two share 256-row tiles (tcgen05 cta_group::2): each stages
+// its own 128 rows of A and half of the tile's W rows, the rank-0 CTA issues the MMAs, each CTA runs the
+// epilogue of its own 128 rows.  A CTA then stages and the tensor core reads 8 KB per 128 x 256 x 16 MMA step
+// instead of 12 KB; with one CTA per tile the shared-memory operand reads, not the tensor core, set the pace.
+#ifndef VTP_LINEAR_CTA_GROUP
+#define VTP_LINEAR_CTA_GROUP 1
+#endif
+constexpr int CG = VTP_LINEAR_CTA_GROUP;
+static_assert(CG == 1 || CG == 2, "one CTA or a pair per tile");
+constexpr int TM = TBM * CG;   // tile rows of the CTA group
+// Staging slabs of the epilogue (128 rows x 64 columns each) and how many TMA stores may be reading them at
+// a time.  A store's shared-memory read takes longer than the epilogue needs to fill the next slab, so with
+// two slabs the epilogue waits on the store; the pair kernel's smaller operand stages leave room for four.
+constexpr int NSTG = CG == 2 ? 4 : 2;
+constexpr int STORES_IN_FLIGHT = NSTG / 2;
+// depth of the operand ring for a tile width: what fits beside the staging slabs
+constexpr int ring_stages(int bn) { return CG == 2 ? (bn == 128 ? 6 : 5) : (bn == 128 ? 5 : 4); }
 constexpr int TBK = 64;    // 64 bf16 = one 128-byte swizzle row
 constexpr int EPI_THREADS = 512;  // 16 epilogue warps, four per TMEM lane quarter
 constexpr int TC_THREADS = 64 + EPI_THREADS + 32;   // + the store warp
@@ -51,11 +68,11 @@ constexpr int TC_THREADS = 64 + EPI_THREADS + 32;   // + the store warp
 template <int BN, int STAGES>
 struct TcSmem {
     static constexpr int A_BYTES = TBM * TBK * 2;
-    static constexpr int B_BYTES = BN * TBK * 2;
+    static constexpr int B_BYTES = (BN / CG) * TBK * 2;   // this CTA's share of the W rows
     static constexpr int RING = STAGES * (A_BYTES + B_BYTES);
-    static constexpr int STAGE_OUT = 2 * TBM * 128;   // two 128-row x 64-column bf16 slabs
+    static constexpr int STAGE_OUT = NSTG * TBM * 128;   // 128-row x 64-column bf16 slabs
     static constexpr int BIAS = 2 * BN * 4;           // the bias and LayerNorm-fold slices of the tile in the epilogue
-    static constexpr int USED = RING + STAGE_OUT + BIAS + 256 /* barriers */;
+    static constexpr int USED = RING + STAGE_OUT + BIAS + 512 /* barriers */;
     // Dynamic shared memory is only promised 16-byte alignment; the ring wants 1024.  In
     // practice the base is already aligned; the kernel checks that what is left fits.
     static constexpr int TOTAL = (USED + 1024 <= 232448) ? USED + 1024 : 232448;
@@ -143,21 +160,26 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;       // [2]
     uint64_t* acc_empty = acc_full + 2;        // [2]
-    uint64_t* res_full = acc_empty + 2;        // [2] residual slab landed in the staging buffer
-    uint64_t* slab_full = res_full + 2;        // [2] every epilogue warp has written its part of the staging slab
-    uint64_t* slab_free = slab_full + 2;       // [2] the TMA store has read the staging slab
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(slab_free + 2);
+    uint64_t* res_full = acc_empty + 2;        // [NSTG] residual slab landed in the staging buffer
+    uint64_t* slab_full = res_full + NSTG;     // [NSTG] every epilogue warp has written its part of the staging slab
+    uint64_t* slab_free = slab_full + NSTG;    // [NSTG] the TMA store has read the staging slab
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(slab_free + NSTG);
+    static_assert((2 * STAGES + 4 + 3 * NSTG) * 8 + 8 <= 512, "barrier area");
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_kb = K / TBK;
+    const int rank = CG == 2 ? (int)cluster_ctarank() : 0;             // this CTA within its group
+    const int n_groups = (int)gridDim.x / CG, group = (int)blockIdx.x / CG;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], EPI_THREADS / 32);
+            mbar_init(&acc_empty[b], CG * (EPI_THREADS / 32));   // rank 0's: the epilogue warps of the whole group
+        }
+        for (int b = 0; b < NSTG; ++b) {
             mbar_init(&res_full[b], 1);
             mbar_init(&slab_full[b], EPI_THREADS / 32);
             mbar_init(&slab_free[b], 1);
@@ -166,11 +188,12 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, S::TMEM_COLS);
-        tmem_relinquish();
+        if (CG == 2) { tmem_alloc_pair(tmem_slot, S::TMEM_COLS); tmem_relinquish_pair(); }
+        else { tmem_alloc(tmem_slot, S::TMEM_COLS); tmem_relinquish(); }
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (CG == 2) cluster_sync_all();     // the partner's barriers exist before anything arrives on them
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -187,32 +210,32 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
             Mp[i] = L.p[i].m_max;
             if (L.p[i].m_dev) Mp[i] = min(*reinterpret_cast<const volatile int32_t*>(L.p[i].m_dev), L.p[i].m_max);
             ntp[i] = (L.p[i].N + BN - 1) / BN;
-            totp[i] = ((Mp[i] + TBM - 1) / TBM) * ntp[i];
+            totp[i] = ((Mp[i] + TM - 1) / TM) * ntp[i];
         }
     }
     // no tiles for this CTA, or an earlier CTA gave up on a wait (the launch is void): skip the work
     const bool void_launch = status && (*reinterpret_cast<volatile int*>(status) & STATUS_WAIT_MASK) != 0;
     const int total = void_launch ? 0 : totp[0] + totp[1];
-    // Tail splitting.  A CTA takes tiles blockIdx.x, + gridDim.x, ...; the R tiles left for the last,
-    // partial round are cut into `parts` column strips of BN / parts columns, one strip per CTA, so that
+    // Tail splitting.  A CTA group takes tiles group, + n_groups, ...; the R tiles left for the last,
+    // partial round are cut into `parts` column strips of BN / parts columns, one strip per group, so that
     // the round costs a fraction of a tile instead of a whole one with most SMs idle.  Strips use their
     // own W boxes (tw2 / tw3) and a narrower MMA; kernels that keep per-tile row statistics
     // (EPI_EMIT) do not split.
-    const int full_items = (total / (int)gridDim.x) * (int)gridDim.x;
+    const int full_items = (total / n_groups) * n_groups;
     int parts = 1;
     {
-        const int R = total - full_items, G = (int)gridDim.x;
+        const int R = total - full_items, G = n_groups;
         if (!(EPI & EPI_EMIT) && R > 0) {
             if (BN == 256) parts = (R * 4 <= G) ? 4 : (R * 2 <= G ? 2 : 1);
             else if (BN == 192) parts = (R * 3 <= G) ? 3 : 1;
             else parts = (R * 2 <= G) ? 2 : 1;
         }
     }
-    // j-th work item of this CTA: problem p, rows m0.., columns ct0 .. ct0 + width of its output.  The last
+    // j-th work item of this CTA: problem p, this CTA's rows m0.., columns ct0 .. ct0 + width of its output.  The last
     // column tile of a problem whose N is not a multiple of BN is as wide as the columns left, in 64s.
     struct Item { int p, m0, nt, ct0, width; };
     auto item_at = [&](int j, Item& it) -> bool {
-        const int idx = (int)blockIdx.x + j * (int)gridDim.x;
+        const int idx = group + j * n_groups;
         int tile, sub = 0, pr = 1;
         if (idx < full_items) {
             tile = idx;
@@ -226,7 +249,7 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
         it.p = (NPROB == 2 && tile >= totp[0]) ? 1 : 0;       // one-problem launches index their problem statically
         const int lt = tile - (it.p ? totp[0] : 0);
         const int n_tiles = ntp[it.p];
-        it.m0 = (lt / n_tiles) * TBM;
+        it.m0 = (lt / n_tiles) * TM + rank * TBM;
         it.nt = lt % n_tiles;
         int tile_w = BN;
         if (NPROB == 2) {
@@ -247,10 +270,11 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
             bool ok = true;
             Item wi;
             for (int j = 0; ok && item_at(j, wi); ++j) {
-                // the W box that is as tall as the item is wide
+                // the W box that holds this CTA's share of the item's columns
                 const TcProblem& P = L.p[wi.p];
                 const CUtensorMap* wm = wi.width == BN ? &P.tw : ((BN == 256 && wi.width == 64) ? &P.tw3 : &P.tw2);
-                const uint32_t bytes = S::A_BYTES + (uint32_t)wi.width * TBK * 2;
+                const int wshare = wi.width / CG;
+                const uint32_t bytes = CG * (S::A_BYTES + (uint32_t)wshare * TBK * 2);     // of the whole group
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -261,22 +285,39 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
                     (void)bytes; (void)wm;
                     mbar_arrive(&full[s]);
 #else
-                    mbar_arrive_expect_tx(&full[s], bytes);
-                    tma_load_2d(smem_a + s * S::A_BYTES, &P.ta, &full[s], kb * TBK, wi.m0);
-                    tma_load_2d(smem_b + s * S::B_BYTES, wm, &full[s], kb * TBK, wi.ct0);
+                    if (CG == 1) {
+                        mbar_arrive_expect_tx(&full[s], bytes);
+                        tma_load_2d(smem_a + s * S::A_BYTES, &P.ta, &full[s], kb * TBK, wi.m0);
+                        tma_load_2d(smem_b + s * S::B_BYTES, wm, &full[s], kb * TBK, wi.ct0);
+                    } else {
+                        // both CTAs' bytes are counted on rank 0's barrier, which its MMA thread waits on
+                        if (rank == 0) mbar_arrive_expect_tx(&full[s], bytes);
+                        const uint32_t fb = mapa_u32(smem_u32(&full[s]), 0);
+                        tma_load_2d_pair(smem_a + s * S::A_BYTES, &P.ta, fb, kb * TBK, wi.m0);
+                        tma_load_2d_pair(smem_b + s * S::B_BYTES, wm, fb, kb * TBK, wi.ct0 + rank * wshare);
+                    }
 #endif
+                }
+            }
+            if (CG == 2 && ok) {
+                // The MMA thread's last commits arrive on this CTA's `empty` barriers, from the partner for
+                // rank 1: wait for them, so that nothing is signalled into a CTA that has retired.
+                for (int s = 0; s < STAGES && ok; ++s) {
+                    if (it <= s) break;
+                    const int uses = (it - s + STAGES - 1) / STAGES;
+                    ok = mbar_wait(&empty[s], (uses - 1) & 1, abort_flag, status, STATUS_GEMM_PRODUCER);
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
-            // -------------------------------------------------------------- MMA issuer
+        if (lane == 0 && rank == 0) {
+            // -------------------------------------------------------------- MMA issuer (of the group)
             int it = 0, lt = 0;
             bool ok = true;
             Item wi;
             for (int j = 0; ok && item_at(j, wi); ++j, ++lt) {
-                const uint32_t idesc = idesc_bf16_f32(TBM, wi.width, 0, 0);
+                const uint32_t idesc = idesc_bf16_f32(TM, wi.width, 0, 0);
                 const int buf = lt & 1;
                 const uint32_t aph = (lt >> 1) & 1;
                 ok = mbar_wait(&acc_empty[buf], aph ^ 1, abort_flag, status, STATUS_GEMM_MMA);
@@ -294,11 +335,12 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
 #pragma unroll
                     for (int k = 0; k < TBK / 16; ++k) {
                         // 16 bf16 of K = 32 bytes = 2 descriptor address units inside the swizzle row
-                        umma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (CG == 2) umma_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        else umma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
-                    umma_commit(&empty[s]);
+                    if (CG == 2) umma_commit_pair(&empty[s]); else umma_commit(&empty[s]);
                 }
-                if (ok) umma_commit(&acc_full[buf]);
+                if (ok) { if (CG == 2) umma_commit_pair(&acc_full[buf]); else umma_commit(&acc_full[buf]); }
             }
         }
         __syncwarp();
@@ -326,25 +368,30 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
                 mbar_arrive_expect_tx(&res_full[b], TBM * 128);
                 tma_load_2d(smem_out + b * (TBM * 128), &L.p[c.it.p].tr, &res_full[b], c.it.ct0 + c.sl * 64, c.it.m0);
             };
-            Cursor cur = first(), ahead = cur;        // `ahead` runs two slabs in front (residual prefetch)
+            Cursor cur = first(), ahead = cur;        // `ahead` runs NSTG slabs in front (residual prefetch)
             const bool res = L.p[0].res != nullptr;
             if (res) {
-                for (int b = 0; b < 2 && ahead.ok; ++b) { load_residual(ahead, b); advance(ahead); }
+                for (int b = 0; b < NSTG && ahead.ok; ++b) { load_residual(ahead, b); advance(ahead); }
             }
             bool ok = true;
             for (int slab_no = 0; cur.ok && ok; ++slab_no, advance(cur)) {
-                const int b = slab_no & 1;
-                ok = mbar_wait(&slab_full[b], (slab_no >> 1) & 1, abort_flag, status, STATUS_GEMM_EPILOGUE);
+                const int b = slab_no % NSTG;
+                ok = mbar_wait(&slab_full[b], (slab_no / NSTG) & 1, abort_flag, status, STATUS_GEMM_EPILOGUE);
                 if (!ok) break;
 #if !(defined(VTP_LINEAR_EXPERIMENT) && (VTP_LINEAR_EXPERIMENT & 2))     // measurement build: no output traffic
                 tma_store_2d(&L.p[cur.it.p].ty, smem_out + b * (TBM * 128), cur.it.ct0 + cur.sl * 64, cur.it.m0);
 #endif
                 bulk_commit_group();
-                bulk_wait_group_read0();              // the slab has been read: it can be written again
-                if (res) {
-                    if (ahead.ok) { load_residual(ahead, b); advance(ahead); }
-                } else {
-                    mbar_arrive(&slab_free[b]);
+                // every store but the newest STORES_IN_FLIGHT - 1 has read its slab: the slab of the last of those
+                // can be written again (with a residual: it receives the residual of the slab NSTG further on)
+                bulk_wait_group_read<STORES_IN_FLIGHT - 1>();
+                if (slab_no >= STORES_IN_FLIGHT - 1) {
+                    const int fb = (slab_no - (STORES_IN_FLIGHT - 1)) % NSTG;
+                    if (res) {
+                        if (ahead.ok) { load_residual(ahead, fb); advance(ahead); }
+                    } else {
+                        mbar_arrive(&slab_free[fb]);
+                    }
                 }
             }
             bulk_wait_group0();                       // every TMA store has landed before the CTA retires
@@ -352,6 +399,11 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
         __syncwarp();
     } else {
         // ------------------------------------------------------------------- epilogue
+        // the accumulator goes back to the MMA thread, which runs in the group's rank-0 CTA
+        auto release_acc = [&](int b) {
+            if (CG == 2) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[b]), 0));
+            else mbar_arrive(&acc_empty[b]);
+        };
         const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
         const int qsub = (warp - 2) >> 2;             // which of the four warps of that quarter
         const int row = quarter * 32 + lane;          // tile row = TMEM lane
@@ -458,16 +510,17 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
                     } else {
                         tc_fence_before_sync();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&acc_empty[buf]);            // accumulator is free
+                        if (lane == 0) release_acc(buf);                        // accumulator is free
                     }
-                    uint8_t* srow = smem_out + (slab_no & 1) * (TBM * 128) + row * 128;
+                    const int sb = slab_no % NSTG;                                // staging slab of this one
+                    uint8_t* srow = smem_out + sb * (TBM * 128) + row * 128;
                     if (res) {
                         // the residual of this slab is in the staging slab (so the slab is free, too)
-                        ok = mbar_wait(&res_full[slab_no & 1], (slab_no >> 1) & 1, abort_flag, status,
+                        ok = mbar_wait(&res_full[sb], (slab_no / NSTG) & 1, abort_flag, status,
                                        STATUS_GEMM_EPILOGUE);
-                    } else if (slab_no >= 2) {
+                    } else if (slab_no >= NSTG) {
                         // the store of the slab that used this staging slab last has read it
-                        ok = mbar_wait(&slab_free[slab_no & 1], ((slab_no >> 1) - 1) & 1, abort_flag, status,
+                        ok = mbar_wait(&slab_free[sb], ((slab_no / NSTG) - 1) & 1, abort_flag, status,
                                        STATUS_GEMM_EPILOGUE);
                     }
                     if (!ok) break;
@@ -502,7 +555,7 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&slab_full[slab_no & 1]);       // this warp's part of the slab is in place
+                    if (lane == 0) mbar_arrive(&slab_full[sb]);                // this warp's part of the slab is in place
                 }
                 if (EPI & EPI_EMIT) ln.emit[(size_t)(m0 + row) * STAT_SLOTS + wi.nt * 4 + qsub] = make_float2(e1, e2);
                 continue;
@@ -527,7 +580,7 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
                     // every column of this warp's slice is in registers: release the accumulator
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    if (lane == 0) release_acc(buf);
                 }
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
@@ -580,7 +633,11 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, S::TMEM_COLS);
+    if (CG == 2) cluster_sync_all();     // the partner no longer reads this CTA's operands or signals its barriers
+    if (warp == 1) {
+        if (CG == 2) tmem_dealloc_pair(tmem_base, S::TMEM_COLS);
+        else tmem_dealloc(tmem_base, S::TMEM_COLS);
+    }
 }
 
 // ------------------------------------------------------------------------------ host
@@ -633,11 +690,12 @@ static int fill_problem(TcProblem& q, const LinearArgs& p) {
         // third for BN = 192, and a quarter)
         const unsigned long long dims[2] = {(unsigned long long)p.K, (unsigned long long)p.N};
         const unsigned long long strides[1] = {(unsigned long long)p.K * 2ull};
-        const unsigned box[2] = {TBK, BN};
+        // (each CTA of a group loads its share of the rows: box heights divide by CG)
+        const unsigned box[2] = {TBK, BN / CG};
         if (int rc = make_tmap_bf16(&q.tw, p.w, 2, dims, strides, box)) return rc;
-        const unsigned box2[2] = {TBK, BN == 256 ? 128u : 64u};
+        const unsigned box2[2] = {TBK, (BN == 256 ? 128u : 64u) / CG};
         if (int rc = make_tmap_bf16(&q.tw2, p.w, 2, dims, strides, box2)) return rc;
-        const unsigned box3[2] = {TBK, 64u};
+        const unsigned box3[2] = {TBK, 64u / CG};
         if (int rc = make_tmap_bf16(&q.tw3, p.w, 2, dims, strides, box3)) return rc;
     }
     // Output map for the TMA-store epilogue (bf16 output, rows not remapped).
@@ -692,10 +750,11 @@ static int launch_tc(const LinearArgs& p, const LinearArgs* p1, cudaStream_t st)
         }
         if (dev >= 0 && dev < 64) attr_set[dev][np] = true;
     }
-    long long tiles = (long long)ceil_div(p.N, BN) * ceil_div(p.m_max, TBM);
-    if (p1) tiles += (long long)ceil_div(p1->N, BN) * ceil_div(p1->m_max, TBM);
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    const cudaError_t le = launch_pdl(kern, dim3(grid), dim3(TC_THREADS), (size_t)S::TOTAL, st, L, p.K, device_status_ptr());
+    long long tiles = (long long)ceil_div(p.N, BN) * ceil_div(p.m_max, TM);
+    if (p1) tiles += (long long)ceil_div(p1->N, BN) * ceil_div(p1->m_max, TM);
+    const int groups = sm_count() / CG;
+    const int grid = CG * (int)(tiles < groups ? tiles : groups);
+    const cudaError_t le = launch_pdl_cluster(kern, CG, dim3(grid), dim3(TC_THREADS), (size_t)S::TOTAL, st, L, p.K, device_status_ptr());
     if (le != cudaSuccess) {
         cudaGetLastError();
         set_error("linear (tcgen05): %s", cudaGetErrorString(le));
@@ -746,7 +805,7 @@ int linear_tcgen05_pair(const LinearArgs& a, const LinearArgs& b, cudaStream_t s
     if (int rc = check_tc_args(a)) return rc;
     if (int rc = check_tc_args(b)) return rc;
     VTP_REQUIRE(linear_pair_supported(a, b), VTP_ERR_UNSUPPORTED, "linear (tcgen05): these two problems cannot share a launch");
-    return launch_tc<256, 4, bf16, EPI_LN>(a, &b, st);
+    return launch_tc<256, ring_stages(256), bf16, EPI_LN>(a, &b, st);
 }
 
 int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
@@ -764,15 +823,15 @@ int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
     const int epi = ((p.flags & VTP_FLAG_GELU) ? EPI_GELU : 0) | (p.ln_mode ? EPI_LN : 0) | (p.emit_stats ? EPI_EMIT : 0);
     if (f32) {
         VTP_REQUIRE(epi == 0, VTP_ERR_UNSUPPORTED, "linear (tcgen05): fp32 output supports bias and residual only");
-        if (bn == 256) return launch_tc<256, 4, float, 0>(p, nullptr, st);
-        if (bn == 192) return launch_tc<192, 4, float, 0>(p, nullptr, st);
-        return launch_tc<128, 5, float, 0>(p, nullptr, st);
+        if (bn == 256) return launch_tc<256, ring_stages(256), float, 0>(p, nullptr, st);
+        if (bn == 192) return launch_tc<192, ring_stages(192), float, 0>(p, nullptr, st);
+        return launch_tc<128, ring_stages(128), float, 0>(p, nullptr, st);
     }
 #define VTP_TC_CASE(E)                                                  \
     if (epi == (E)) {                                                   \
-        if (bn == 256) return launch_tc<256, 4, bf16, (E)>(p, nullptr, st);      \
-        if (bn == 192) return launch_tc<192, 4, bf16, (E)>(p, nullptr, st);      \
-        return launch_tc<128, 5, bf16, (E)>(p, nullptr, st);                     \
+        if (bn == 256) return launch_tc<256, ring_stages(256), bf16, (E)>(p, nullptr, st);      \
+        if (bn == 192) return launch_tc<192, ring_stages(192), bf16, (E)>(p, nullptr, st);      \
+        return launch_tc<128, ring_stages(128), bf16, (E)>(p, nullptr, st);                     \
     }
     VTP_TC_CASE(0)
     VTP_TC_CASE(EPI_GELU)
