@@ -9,6 +9,7 @@ Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of 
 reference's eval path on the host cores instead.
 """
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -640,6 +641,15 @@ def train_ops_sweep(args):
         nbytes = (B * N + L) * C * 2
         rows.append({"op": name, "shape": f"B={B} N={N} C={C} L={L}", "us": round(us, 1),
                      "GB/s": round(nbytes / us / 1e3), "frac_of_hbm_peak": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)})
+    # the region-parallel form of unpool_grad (what the autograd function calls for a list made from grain indices)
+    idx32, first, splits_l, region_size, Hr, Wr, _ = patches._vtp_regions
+    arr = (ctypes.c_int * len(splits_l))(*splits_l)
+    us = _time_us(lambda: _lib.check(lib.vtp_unpool_grad_regions(
+        ptr(x), dtype_code(x.dtype), B, Hr, Wr, region_size, C, 1, ptr(idx32), arr, len(splits_l), ptr(first),
+        ptr(patches._vtp_offsets), L, ptr(gq), st)))
+    nbytes = (B * N + L) * C * 2
+    rows.append({"op": "unpool_grad (regions)", "shape": f"B={B} N={N} C={C} L={L}", "us": round(us, 1),
+                 "GB/s": round(nbytes / us / 1e3), "frac_of_hbm_peak": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)})
     # ---- ragged products of the training-mode attention: S = Q K^T and O = P V
     qh = torch.randn(heads, L, d, device=dev, generator=gen).bfloat16()
     kh = torch.randn(heads, B * N, d, device=dev, generator=gen).bfloat16()

@@ -159,6 +159,24 @@ int vtp_unpool_grad(const void* grad_out, int dtype, int B, int N, int C, int W,
                     void* grad_q, void* stream);
 
 /*
+ * vtp_unpool_grad for a patch list that was made from grain indices (vtp_index_to_patch), region-parallel:
+ * one thread block per region reads the region's region_size^2 rows of grad_out at once and writes the sums
+ * of its patches; nothing walks the list.  indices int32 [B, Hr*Wr] (values clamped to the split table),
+ * region_first int32 [B*Hr*Wr] = packed row of each region's first patch, offsets int32 [B+1] = packed row
+ * of each image's first extra token; grad_out [B, num_extra + Hr*Wr*region_size^2, C], grad_q [n_patches, C]
+ * (a region or extra token whose rows would fall outside grad_q is skipped and STATUS_BAD_INDEX set).
+ * The sums are taken in fp32 per grid row and then over the rows (the list-walking form adds in (dy, dx)
+ * order; the two agree to fp32 rounding).  Region size 4 and a C whose row is 8..192 16-byte chunks in one of
+ * the kernel's lane layouts: vtp_region_layout_supported(dtype, C) says whether; otherwise VTP_ERR_SHAPE,
+ * and vtp_unpool_grad is the general form.
+ */
+int vtp_region_layout_supported(int dtype, int C);
+int vtp_unpool_grad_regions(const void* grad_out, int dtype, int B, int Hr, int Wr, int region_size, int C,
+                            int num_extra, const int32_t* indices, const int* splits, int n_splits,
+                            const int32_t* region_first, const int32_t* offsets, int n_patches, void* grad_q,
+                            void* stream);
+
+/*
  * Ragged batched matrix product of the training path.  For image i and head h
  *   out_i = op(a_i) * op(b_i),  a_i = a[h, a_offsets[i] : a_offsets[i+1], :],  b_i likewise,
  * op = transpose when the matching flag is non-zero; the out_i are stacked along the row axis: image i

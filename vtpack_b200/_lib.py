@@ -11,6 +11,9 @@ LIB_PATH = os.path.join(HERE, "libvtpack_b200.so")
 
 VTP_F32, VTP_BF16 = 0, 1
 FLAG_GELU, FLAG_OUT_F32, FLAG_CUDA_CORES = 1, 2, 4
+# return codes (include/vtpack_b200.h) and the index-guard bit of the device status word
+ERR_NULL, ERR_SHAPE, ERR_DTYPE, ERR_ALIGN, ERR_UNSUPPORTED, ERR_DRIVER = -1, -2, -3, -4, -5, -6
+STATUS_BAD_INDEX = 64
 
 c_void_p, c_int, c_ll, c_float, c_uint = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_uint
 
@@ -61,6 +64,9 @@ PROTOTYPES = {
                               c_void_p, c_void_p]),
     "vtp_unpool_grad": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                 c_void_p, c_void_p]),
+    "vtp_region_layout_supported": (c_int, [c_int, c_int]),
+    "vtp_unpool_grad_regions": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                        C.POINTER(c_int), c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "vtp_batched_sparse_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_int, c_ll,
                                         c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_int,
                                         c_void_p]),

@@ -7,6 +7,7 @@
 // (vtpack/layers/csrc/grained_sample/grained_sample.cu:31-69, 71-144) and the nn.LayerNorm
 // calls of Block.forward (vtpack/models/dge/deit_dge.py:127-128).
 #include "common.cuh"
+#include "region_ops.h"
 #include "runtime.h"
 
 namespace vtp {
@@ -553,6 +554,38 @@ extern "C" int vtp_unpool_grad(const void* grad_out, int dtype, int B, int N, in
                                   nullptr, nullptr, 0.f, nullptr, nullptr, 0, st);
     return launch_pool<bf16>(grad_out, B, N, C, W, num_extra, patches, n_patches_dev, n_patches_max, grad_q,
                              nullptr, nullptr, 0.f, nullptr, nullptr, 0, st);
+}
+
+// The same gradient for a patch list that was made from grain indices: one CTA per region, every token
+// row of the region requested before any arithmetic, no walk over the list (region_ops.cu).
+extern "C" int vtp_region_layout_supported(int dtype, int C) {
+    RegionGeom g{};
+    g.B = g.Hr = g.Wr = 1; g.C = C; g.region = 4;
+    return (dtype == VTP_F32 || dtype == VTP_BF16) && C > 0 && region_ops_supported(g, dtype) ? 1 : 0;
+}
+
+extern "C" int vtp_unpool_grad_regions(const void* grad_out, int dtype, int B, int Hr, int Wr, int region_size,
+                                       int C, int num_extra, const int32_t* indices, const int* splits,
+                                       int n_splits, const int32_t* region_first, const int32_t* offsets,
+                                       int n_patches, void* grad_q, void* stream) {
+    VTP_REQUIRE(grad_out && indices && splits && region_first && offsets && grad_q, VTP_ERR_NULL,
+                "unpool_grad (regions): null pointer");
+    VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "unpool_grad (regions): dtype %d", dtype);
+    VTP_REQUIRE(B > 0 && Hr > 0 && Wr > 0 && C > 0 && num_extra >= 0 && n_patches >= 0, VTP_ERR_SHAPE,
+                "unpool_grad (regions): bad shape");
+    if (n_patches == 0) return VTP_OK;
+    RegionPoolArgs a;
+    if (int rc = make_splits(&a.sp, splits, n_splits, region_size)) return rc;
+    a.g.B = B; a.g.Hr = Hr; a.g.Wr = Wr; a.g.W = Wr * region_size; a.g.C = C; a.g.num_extra = num_extra;
+    a.g.region = region_size;
+    a.g.N = num_extra + Hr * Wr * region_size * region_size;
+    VTP_REQUIRE(region_ops_supported(a.g, dtype), VTP_ERR_SHAPE,
+                "unpool_grad (regions): region size %d / C=%d have no region kernel (use vtp_unpool_grad)", region_size, C);
+    VTP_REQUIRE(aligned16(grad_out) && aligned16(grad_q), VTP_ERR_ALIGN, "unpool_grad (regions): unaligned rows");
+    a.x = grad_out; a.idx = indices; a.region_first = region_first; a.offsets = offsets; a.comp = grad_q;
+    a.sum_only = true;
+    a.g.l_max = n_patches;       // regions whose rows would not fit grad_q are skipped and flagged
+    return region_pool(a, dtype, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int vtp_layernorm(const void* x, int dtype, int rows_max, const int32_t* rows_dev, int C,

@@ -15,6 +15,7 @@
 // 107-144) and the nn.LayerNorm norm1 calls of Block.forward
 // (vtpack/models/dge/deit_dge.py:127) on the fused path.
 #include "region_ops.h"
+#include "runtime.h"
 
 namespace vtp {
 
@@ -189,14 +190,17 @@ __device__ __forceinline__ void publish_partials(float* part, float (&acc)[CPL][
 }
 
 // ------------------------------------------------------------------------------- pool
-// STATS = true : comp rows + (mean, rstd) of every comp row (and of every token row unless
-//                they are already known), for the GEMMs that apply LayerNorm in their
-//                epilogue; zeroes the stats_acc rows.
-// STATS = false: comp rows + explicit LN(x) rows and LN(comp) rows.
+// POOL_STATS: comp rows + (mean, rstd) of every comp row (and of every token row unless
+//             they are already known), for the GEMMs that apply LayerNorm in their
+//             epilogue; zeroes the stats_acc rows.
+// POOL_LN:    comp rows + explicit LN(x) rows and LN(comp) rows.
+// POOL_PLAIN: comp rows only, as means or (sum_only) as sums: the latter is the gradient of the
+//             replicate-unpool with respect to its packed rows (vtpack/layers/grained_sample.py:61-72).
 // Seven CTAs per SM (at most 73 registers, a few spilled words): the kernel is bound by how many
 // regions are in flight, and measured faster over the whole forward than at the 88 registers / five
 // CTAs the compiler picks on its own (six: +0.5 %, seven: +0.9 %, eight: +0.8 %).
-template <typename T, int G, int CPL, bool STATS>
+constexpr int POOL_LN = 0, POOL_STATS = 1, POOL_PLAIN = 2;
+template <typename T, int G, int CPL, int MODE>
 __global__ void __launch_bounds__(128, 7)
 pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restrict__ idx,
                    const int32_t* __restrict__ region_first, const int32_t* __restrict__ offsets,
@@ -204,7 +208,9 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
                    int32_t* __restrict__ region_first_out, int32_t* __restrict__ counts_next, Splits sp,
                    T* __restrict__ comp, float2* __restrict__ stats_x, float2* __restrict__ stats_q,
                    float2* __restrict__ stats_acc, int write_stats_x, const float* __restrict__ lnw,
-                   const float* __restrict__ lnb, float eps, T* __restrict__ xn, T* __restrict__ qn) {
+                   const float* __restrict__ lnb, float eps, T* __restrict__ xn, T* __restrict__ qn, int sum_only,
+                   int* status) {
+    constexpr bool STATS = MODE == POOL_STATS, EXPLICIT_LN = MODE == POOL_LN;
     using L = Lay<T, G, CPL>;
     constexpr int VN = L::VN, GROUPS = L::GROUPS, TPG = L::TPG;
     extern __shared__ float part[];          // [4 grid rows][2 halves][C] partial sums
@@ -222,6 +228,10 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
         int dst_row;
         if (region_first) {
             dst_row = offsets[b] + t;
+            if (VTP_INDEX_GUARDS && g.l_max > 0 && (dst_row < 0 || dst_row >= g.l_max)) {   // caller's offsets
+                if (sub == 0 && status) atomicOr(status, STATUS_BAD_INDEX);
+                return;
+            }
         } else {
             int base = 0;
             for (int j = sub; j < b; j += G) base += counts[j];
@@ -245,7 +255,7 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
                 st = stats_x[src_row];
             }
             if (sub == 0) { stats_q[dst_row] = st; if (stats_acc) stats_acc[dst_row] = make_float2(0.f, 0.f); }
-        } else {
+        } else if (EXPLICIT_LN) {
             ln_store<T, G, CPL>(f, sub, g.C, lnw, lnb, eps, xn + src_row * g.C);
             ln_store<T, G, CPL>(f, sub, g.C, lnw, lnb, eps, qn + (size_t)dst_row * g.C);
         }
@@ -267,6 +277,11 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
     int first;
     if (region_first) {
         first = region_first[rid];
+        // a caller-supplied first row whose patches would not fit the packed array: skip the region
+        if (VTP_INDEX_GUARDS && g.l_max > 0 && (first < 0 || first + s * s > g.l_max)) {
+            if (threadIdx.x == 0 && status) atomicOr(status, STATUS_BAD_INDEX);
+            return;
+        }
     } else {
         int img_base;
         first = derive_first(counts, idx, b, rr, R, sp, g.num_extra, lane, &img_base);
@@ -297,7 +312,7 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
                 st = stats_x[tok0 + j];
             }
             if (step == 1 && sub == 0) { stats_q[prow] = st; if (stats_acc) stats_acc[prow] = make_float2(0.f, 0.f); }
-        } else {
+        } else if (EXPLICIT_LN) {
             ln_store<T, G, CPL>(f, sub, g.C, lnw, lnb, eps, xn + (tok0 + j) * g.C);
             if (step == 1) ln_store<T, G, CPL>(f, sub, g.C, lnw, lnb, eps, qn + (size_t)prow * g.C);
         }
@@ -341,7 +356,7 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
         }
     }
     // step * step is 4 or 16: multiplying by its reciprocal is the division, bit for bit
-    const float inv_denom = 1.0f / (float)(step * step);
+    const float inv_denom = sum_only ? 1.0f : 1.0f / (float)(step * step);
 #pragma unroll
     for (int ch = 0; ch < CPL; ++ch)
 #pragma unroll
@@ -352,7 +367,7 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
         const float2 st = mean_rstd(row_sums<T, G, CPL>(acc), g.C, eps);
         if (sub == 0) { stats_q[row] = st; if (stats_acc) stats_acc[row] = make_float2(0.f, 0.f); }
     } else {
-        ln_store<T, G, CPL>(acc, sub, g.C, lnw, lnb, eps, qn + (size_t)row * g.C);
+        if (EXPLICIT_LN) ln_store<T, G, CPL>(acc, sub, g.C, lnw, lnb, eps, qn + (size_t)row * g.C);
         round_store<T, CPL>(acc, comp + (size_t)row * g.C, sub, G);
     }
 }
@@ -595,14 +610,19 @@ static void launch_pool_t(const RegionPoolArgs& a, cudaStream_t st) {
     const int grid = a.g.B * R + ceil_div(a.g.B * a.g.num_extra, RG * (32 / G));
     const size_t smem = (size_t)8 * a.g.C * sizeof(float);
     if (a.stats_q)
-        pool_region_kernel<T, G, CPL, true><<<grid, 128, smem, st>>>(
+        pool_region_kernel<T, G, CPL, POOL_STATS><<<grid, 128, smem, st>>>(
             (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.counts, a.offsets_out, a.region_first_out,
             a.counts_next, a.sp, (T*)a.comp, a.stats_x, a.stats_q, a.stats_acc, a.stats_x_ready ? 0 : 1, nullptr,
-            nullptr, a.eps, nullptr, nullptr);
-    else
-        pool_region_kernel<T, G, CPL, false><<<grid, 128, smem, st>>>(
+            nullptr, a.eps, nullptr, nullptr, 0, nullptr);
+    else if (a.xn && a.qn)
+        pool_region_kernel<T, G, CPL, POOL_LN><<<grid, 128, smem, st>>>(
             (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.counts, a.offsets_out, a.region_first_out,
-            a.counts_next, a.sp, (T*)a.comp, nullptr, nullptr, nullptr, 0, a.lnw, a.lnb, a.eps, (T*)a.xn, (T*)a.qn);
+            a.counts_next, a.sp, (T*)a.comp, nullptr, nullptr, nullptr, 0, a.lnw, a.lnb, a.eps, (T*)a.xn, (T*)a.qn, 0, nullptr);
+    else
+        pool_region_kernel<T, G, CPL, POOL_PLAIN><<<grid, 128, smem, st>>>(
+            (const T*)a.x, a.g, a.idx, a.region_first, a.offsets, a.counts, a.offsets_out, a.region_first_out,
+            a.counts_next, a.sp, (T*)a.comp, nullptr, nullptr, nullptr, 0, nullptr, nullptr, a.eps, nullptr, nullptr,
+            a.sum_only ? 1 : 0, device_status_ptr());
 }
 
 template <typename T, int G, int CPL>

@@ -12,6 +12,8 @@ struct RegionGeom {
     int W, N, C;        // token grid width, tokens per image (extra + H*W), channels
     int num_extra;      // cls tokens in front of the grid
     int region;         // tokens per region side
+    int l_max = 0;      // rows of the packed array where the caller supplies each region's first row
+                        // (0: the rows come from this library's own compaction and are not checked)
 };
 
 struct RegionPoolArgs {
@@ -32,6 +34,9 @@ struct RegionPoolArgs {
     bool stats_x_ready = false;              // stats_x was already written (by the previous block's unpool)
     const float* lnw = nullptr; const float* lnb = nullptr; float eps = 1e-6f;
     void* xn = nullptr; void* qn = nullptr;
+    // With neither statistics nor LayerNorm rows asked for: plain pooled rows, as means or (sum_only) as the
+    // sums of each patch's tokens, which is the gradient of the replicate-unpool for its packed rows.
+    bool sum_only = false;
 };
 
 // What the unpool kernel can prepare for the block that follows, from the rows it has just

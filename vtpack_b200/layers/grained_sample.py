@@ -50,6 +50,14 @@ def grained_sample_index_to_patch(indices, split_sizes, region_size, num_extra_t
     patches = p64[:L]
     patches._vtp_i32 = p32[:L]
     patches._vtp_offsets = offsets
+    # what the region-parallel gradient kernel needs instead of the list: the grain index of every region and
+    # the packed row of its first patch (the image's first row + its extra tokens + the patches of the regions
+    # in front of it)
+    per_side = torch.tensor(splits, dtype=torch.int32, device=dev)[indices.reshape(B, -1).clamp(0, len(splits) - 1)]
+    per_region = per_side * per_side
+    first = offsets[:B, None] + int(num_extra_tokens) + torch.cumsum(per_region, 1, dtype=torch.int32) - per_region
+    patches._vtp_regions = (indices.reshape(B, -1).to(torch.int32).contiguous(), first.to(torch.int32).contiguous(),
+                            splits, int(region_size), Hr, Wr, int(num_extra_tokens))
     return patches, batch_lengths
 
 
@@ -101,6 +109,7 @@ class _GrainedSampleDecompress(Function):
         p32 = _patches_i32(patches)
         ctx.save_for_backward(p32)
         ctx.geom = (tuple(ref_input.shape), int(width), int(num_extra_tokens), bool(is_add_ref))
+        ctx.regions = (getattr(patches, "_vtp_regions", None), getattr(patches, "_vtp_offsets", None))
         out = torch.empty(ref_input.shape, dtype=input.dtype, device=input.device)
         B, N, C = ref_input.shape
         _lib.check(_lib.lib().vtp_unpool_add(
@@ -115,9 +124,23 @@ class _GrainedSampleDecompress(Function):
         shape, width, num_extra_tokens, is_add_ref = ctx.geom
         grad_output = grad_output.contiguous()
         grad_input = torch.empty(p32.shape[0], shape[2], dtype=grad_output.dtype, device=grad_output.device)
-        _lib.check(_lib.lib().vtp_unpool_grad(
-            ptr(grad_output), dtype_code(grad_output.dtype), *_mover_args(shape, p32, width, num_extra_tokens),
-            ptr(grad_input), stream_ptr(grad_output.device)))
+        lib = _lib.lib()
+        regions, offsets = ctx.regions
+        B, N, C = shape
+        if (regions is not None and offsets is not None and regions[3] == 4 and regions[6] == num_extra_tokens
+                and regions[0].shape[0] == B and N == num_extra_tokens + regions[4] * regions[5] * 16
+                and width == regions[5] * 4 and lib.vtp_region_layout_supported(dtype_code(grad_output.dtype), C)):
+            # the list came from grain indices: one thread block per region instead of a walk over the list
+            idx32, first, splits, region_size, Hr, Wr, _ = regions
+            arr = (ctypes.c_int * len(splits))(*splits)
+            _lib.check(lib.vtp_unpool_grad_regions(
+                ptr(grad_output), dtype_code(grad_output.dtype), B, Hr, Wr, region_size, C, num_extra_tokens,
+                ptr(idx32), arr, len(splits), ptr(first), ptr(offsets), p32.shape[0], ptr(grad_input),
+                stream_ptr(grad_output.device)))
+        else:
+            _lib.check(lib.vtp_unpool_grad(
+                ptr(grad_output), dtype_code(grad_output.dtype), *_mover_args(shape, p32, width, num_extra_tokens),
+                ptr(grad_input), stream_ptr(grad_output.device)))
         grad_ref = grad_output if is_add_ref else torch.zeros_like(grad_output)
         return grad_input, None, grad_ref, None, None, None, None
 
