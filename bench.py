@@ -666,12 +666,25 @@ def train_ops_sweep(args):
             outs.append(torch.bmm(a[:, off[i]:off[i + 1]], bi.transpose(-1, -2) if tb else bi))
         return torch.cat(outs, dim=1)
 
+    a_off = torch.tensor(off, dtype=torch.int32, device=dev)
+    b_off = (torch.arange(B + 1, dtype=torch.int32) * N).to(dev)
+    a_max = int(lengths.max())
     for name, a, tb in (("ragged Q K^T", qh, True), ("ragged P V", prob, False)):
-        us = _time_us(lambda: layers.batched_sparse_gemm(a, kh, lengths, kv_len, False, tb), iters=10)
+        out_cols = N if tb else d
+        out = torch.empty(heads, L, out_cols, dtype=torch.bfloat16, device=dev)
+        # the launch itself (offsets already on the device), then the call a training step makes (the autograd
+        # function: two host-side prefix sums and their copies, the output allocation, then the same launch)
+        us = _time_us(lambda: _lib.check(lib.vtp_batched_sparse_gemm(
+            ptr(a), ptr(kh), ptr(out), dtype_code(a.dtype), heads, B, a.shape[1], a.shape[2], kh.shape[1], d,
+            ptr(a_off), ptr(b_off), a_max, N, 0, int(tb), L, out_cols, st)))
+        us_call = _time_us(lambda: layers.batched_sparse_gemm(a, kh, lengths, kv_len, False, tb), iters=10)
         us_loop = _time_us(lambda: per_image(a, kh, tb), iters=3, warm=1)
         flops = 2.0 * heads * L * N * d
+        nbytes = (a.numel() + kh.numel() + out.numel()) * 2
         rows.append({"op": name, "shape": f"heads={heads} L={L} keys={N} d={d}", "us": round(us, 1),
-                     "tflops": round(flops / us / 1e6, 2), "per_image_bmm_loop_us": round(us_loop, 1)})
+                     "tflops": round(flops / us / 1e6, 2), "GB/s": round(nbytes / us / 1e3),
+                     "frac_of_hbm_peak": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3),
+                     "us_through_autograd_function": round(us_call, 1), "per_image_bmm_loop_us": round(us_loop, 1)})
     # ---- bilinear-sampling attention at a deformable-PVT stage: 64 x 64 map, 64 channels per head
     Bb, H, P = max(1, B // 8), 64, 9
     for mode in ("point", "channel"):

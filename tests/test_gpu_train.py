@@ -235,6 +235,34 @@ def test_ragged_products_all_flag_combinations(layers, dtype, ta, tb):
     assert rel_err(out.float(), ref) < (1e-5 if dtype == torch.float32 else 8e-3)
 
 
+@pytest.mark.parametrize("keys,d,las", [(257, 64, [113, 41, 257, 0, 130]), (264, 64, [70, 129]), (65, 64, [33, 7]),
+                                        (1025, 32, [300, 5])])
+def test_ragged_products_model_shapes_bf16(layers, keys, d, las):
+    """The six products of the training-mode attention (forward S = Q K^T and O = P V; backward dP = dO V^T,
+    dQ = dS K, dK = dS^T Q, dV = P^T dO) at the model's shapes: 257 keys (rows of 514 bytes: unaligned rows, a
+    one-column tail beside the 256-column tile, a reduction of 4 x 64 + 1), query counts below, at and above
+    one 128-row tile, an image without queries; also 264 keys (an 8-column tail), 65 and 1025.  bf16 on tensor
+    cores against float64 on the bf16-rounded operands."""
+    h = 3
+    B = len(las)
+    la, lb = torch.tensor(las), torch.full([B], keys, dtype=torch.long)
+    L = int(la.sum())
+    gen = torch.Generator().manual_seed(keys + d + L)
+    q = torch.randn(h, L, d, generator=gen).bfloat16()
+    k = torch.randn(h, B * keys, d, generator=gen).bfloat16()
+    p = torch.randn(h, L, keys, generator=gen).bfloat16()
+    cases = [("S = Q K^T", q, k, la, lb, False, True), ("O = P V", p, k, la, lb, False, False),
+             ("dK = dS^T Q", p, q, la, la, True, False)]
+    for name, a, b, xa, xb, ta, tb in cases:
+        ref = O.batched_sparse_gemm_forward(a.double(), b.double(), xa, xb, ta, tb)
+        out = layers.batched_sparse_gemm(a.to(DEV), b.to(DEV), xa, xb, ta, tb)
+        torch.cuda.synchronize()
+        assert out.shape == ref.shape and out.dtype == torch.bfloat16, name
+        assert rel_err(out.float(), ref) < 8e-3, name
+    from vtpack_b200 import _lib
+    assert _lib.device_status() == 0
+
+
 def _train_block(mode):
     from vtpack_b200.models.dge import deit_dge
     cfg = O.TRAIN_BLOCK

@@ -142,7 +142,9 @@ extern "C" int vtp_batched_sparse_gemm(const void* a, const void* b, void* out, 
     VTP_REQUIRE(max_n <= out_cols, VTP_ERR_SHAPE, "batched_sparse_gemm: %d output columns, buffer has %d", max_n,
                 out_cols);
     if (max_m == 0 || max_n == 0 || out_rows == 0) return VTP_OK;
-    if (dtype == VTP_BF16)       // tensor cores; fp32 keeps full-precision products on CUDA cores
+    // bf16 on tensor cores (operand arrays that start on a 16-byte boundary: the kernel fetches with aligned
+    // 16-byte loads); fp32 keeps full-precision products on CUDA cores
+    if (dtype == VTP_BF16 && aligned16(a) && aligned16(b))
         return ragged_gemm_tcgen05(a, b, out, heads, n_images, a_rows, a_cols, b_rows, b_cols, a_offsets, b_offsets,
                                    max_m, max_n, a_transposed ? 1 : 0, b_transposed ? 1 : 0, out_rows, out_cols,
                                    static_cast<cudaStream_t>(stream));

@@ -34,7 +34,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // One try: the thread may be SUSPENDED by the hardware for up to `kSuspendHintNs` while the phase is
 // incomplete and is woken when it completes.  Without the hint a waiting thread comes back at once and
 // a polling loop fills the issue slots of its SM sub-partition, at the expense of the warps that work.
-constexpr uint32_t kSuspendHintNs = 20000;
+#ifndef VTP_SUSPEND_HINT_NS
+#define VTP_SUSPEND_HINT_NS 20000
+#endif
+constexpr uint32_t kSuspendHintNs = VTP_SUSPEND_HINT_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
