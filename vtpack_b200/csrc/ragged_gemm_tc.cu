@@ -35,7 +35,20 @@ constexpr int RT_K = 64;           // reduction slice: one 128-byte swizzle row 
 constexpr int RT_THREADS = 256;
 constexpr int RT_A_BYTES = RT_M * RT_K * 2;                    // 16 KB
 constexpr int RT_B_BYTES = (RT_N + RT_TAIL + 8) * RT_K * 2;    // 34 KB (a multiple of 1024)
-constexpr int RT_SMEM = 2 * (RT_A_BYTES + RT_B_BYTES) + 1024 + 256;
+// Resident a: where the tile's rows of a (rows of 257 elements, say) fit into shared memory as they lie in
+// memory, they are fetched ONCE, as one contiguous range with 16-byte asynchronous copies, and every slice is
+// cut out of that image; reading 128-byte pieces of 514-byte rows slice by slice costs a memory round trip per
+// slice and uses DRAM badly.  The image lies behind the two a slices and ONE b slice of 64 rows (with two, and
+// the shared memory that leaves two CTAs per SM used to the last KB, the products measured 12 % slower).
+constexpr int RT_RAW_OFF = 2 * RT_A_BYTES + 64 * 128;
+constexpr int RT_RAW_BYTES = RT_M * 257 * 2 + 32;              // 128 rows of 257 elements, shifted by up to 7
+constexpr int RT_BAR_OFF = (2 * (RT_A_BYTES + RT_B_BYTES) > RT_RAW_OFF + RT_RAW_BYTES) ? 2 * (RT_A_BYTES + RT_B_BYTES)
+                                                                                        : RT_RAW_OFF + RT_RAW_BYTES;
+constexpr int RT_USED = RT_BAR_OFF + 256;
+// Dynamic shared memory is only promised 16-byte alignment and the buffers want 1024; in practice the base is
+// aligned already.  What two CTAs per SM leave is requested, and the kernel checks that its layout fits.
+constexpr int RT_SMEM = (RT_USED + 1024 <= 233472 / 2 - 1024) ? RT_USED + 1024 : 233472 / 2 - 1024;
+static_assert(RT_RAW_BYTES % 16 == 0 && RT_USED <= RT_SMEM, "two CTAs per SM");
 constexpr int RT_ATOM_BYTES = RT_K * 128;                      // one MN-major atom column: 64 k rows of 128 bytes
 constexpr int RT_BSUB_MAX = (RT_N + RT_TAIL + 63) / 64;        // 64-row sub-tiles of a b slice, at most
 static_assert(RT_B_BYTES % 1024 == 0, "slice buffers stay 1024-byte aligned");
@@ -179,7 +192,11 @@ ragged_gemm_tc_kernel(RaggedTcArgs g, int* status) {
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sa = base;                                   // two A slices
     uint8_t* sb = base + 2 * RT_A_BYTES;                  // two B slices
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + 2 * (RT_A_BYTES + RT_B_BYTES));
+    if (static_cast<int>(base - smem_raw) + RT_USED > RT_SMEM) {
+        if (threadIdx.x == 0 && status) atomicOr(status, STATUS_GEMM_PRODUCER);
+        return;
+    }
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + RT_BAR_OFF);
     uint64_t* slice_done = bars;                          // [2] the MMAs that read a slice buffer have completed
     uint64_t* acc_full = bars + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
@@ -242,15 +259,51 @@ ragged_gemm_tc_kernel(RaggedTcArgs g, int* status) {
     float tail_acc[RT_TAIL];
 #pragma unroll
     for (int j = 0; j < RT_TAIL; ++j) tail_acc[j] = 0.f;
+    // ---- resident a (see RT_RAW_OFF): the tile's rows of a as one contiguous range, copied asynchronously
+    const bool resident = A_HI && RT_BSUB == 1 && !g.ta && (long long)rows * g.a_cols * 2 + 32 <= RT_RAW_BYTES;
+    uint8_t* raw = base + RT_RAW_OFF;
+    int rshift = 0;                                        // elements between the image's start and the tile's first
+    if (resident) {
+        const long long e_first = a_base + (long long)m0 * g.a_cols;
+        const long long e0 = e_first & ~7LL;
+        rshift = (int)(e_first - e0);
+        const int nvec = (rshift + rows * g.a_cols + 7) >> 3;
+        for (int v = threadIdx.x; v < nvec; v += RT_THREADS) {
+            const long long e = e0 + 8LL * v;
+            if (e + 8 <= a_total) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(raw + 16 * v)), "l"(g.a + e) : "memory");
+            } else {                                       // the end of the array: nothing read beyond it
+                unsigned short h[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    h[j] = (e + j < a_total) ? *reinterpret_cast<const unsigned short*>(g.a + e + j) : (unsigned short)0;
+                *reinterpret_cast<uint4*>(raw + 16 * v) =
+                    make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    // resident a: the (single, 64-row) b sub-tile of slice c + 1 is requested while slice c is being put together,
+    // so that no slice waits for global memory
+    auto b_sub0 = [&](int k0) {
+        return g.tb ? SubTile{b_base, n0, N, k0, K, 64} : SubTile{b_base, k0, K, n0, N, 64};
+    };
+    uint4 bnext[2], bnext_hi[2];
+    if (resident && b_all_aligned) issue_subtile<false>(bnext, bnext_hi, g.b, b_total, g.b_cols, b_sub0(0), true);
     bool ok = true;
     for (int c = 0; c < n_slices && ok; ++c) {
         const int buf = c & 1, k0 = c * RT_K;
-        // the MMAs of slice c - 2 have finished reading this buffer
-        ok = mbar_wait(&slice_done[buf], ((c >> 1) & 1) ^ 1, abort_flag, status, STATUS_GEMM_PRODUCER);
+        // the MMAs of slice c - 2 have finished reading this buffer (resident a: those of slice c - 1, whose b
+        // slice lies in the one b buffer there is)
+        if (resident) {
+            if (c > 0) ok = mbar_wait(&slice_done[(c - 1) & 1], ((c - 1) >> 1) & 1, abort_flag, status, STATUS_GEMM_PRODUCER);
+        } else {
+            ok = mbar_wait(&slice_done[buf], ((c >> 1) & 1) ^ 1, abort_flag, status, STATUS_GEMM_PRODUCER);
+        }
         ok = __syncthreads_and(ok) != 0;                   // one verdict for the CTA: nobody is left at a barrier
         if (!ok) break;
         uint8_t* sa_c = sa + buf * RT_A_BYTES;
-        uint8_t* sb_c = sb + buf * RT_B_BYTES;
+        uint8_t* sb_c = resident ? sb : sb + buf * RT_B_BYTES;
         // the slice as sub-tiles of 64 rows x 64 elements (8 KB each): two of a, up to RT_BSUB of b
         SubTile at[2], bt[RT_BSUB];
 #pragma unroll
@@ -267,15 +320,41 @@ ragged_gemm_tc_kernel(RaggedTcArgs g, int* status) {
         {
             uint4 alo[2][2], ahi[A_HI ? 2 : 1][2], blo[RT_BSUB][2], bhi[1][2];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) issue_subtile<A_HI>(alo[j], ahi[A_HI ? j : 0], g.a, a_total, g.a_cols, at[j], true);
-            if (b_all_aligned) {
+            for (int j = 0; j < 2; ++j) issue_subtile<A_HI>(alo[j], ahi[A_HI ? j : 0], g.a, a_total, g.a_cols, at[j], !resident);
+            const bool b_ahead = resident && b_all_aligned;       // this slice's b is in registers already
+            if (b_ahead) {
+                commit_subtile<false>(bnext, bnext_hi, sb_c, g.b, b_total, g.b_cols, bt[0], true);
+                issue_subtile<false>(bnext, bnext_hi, g.b, b_total, g.b_cols, b_sub0(k0 + RT_K), c + 1 < n_slices);
+            } else if (b_all_aligned) {
 #pragma unroll
                 for (int j = 0; j < RT_BSUB; ++j) issue_subtile<false>(blo[j], bhi[0], g.b, b_total, g.b_cols, bt[j], j < nb);
             }
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-                commit_subtile<A_HI>(alo[j], ahi[A_HI ? j : 0], sa_c + j * RT_SUB_BYTES, g.a, a_total, g.a_cols, at[j], true);
-            if (b_all_aligned) {
+                commit_subtile<A_HI>(alo[j], ahi[A_HI ? j : 0], sa_c + j * RT_SUB_BYTES, g.a, a_total, g.a_cols, at[j], !resident);
+            if (resident) {
+                if (c == 0) {                              // the image has landed, for every thread
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    __syncthreads();
+                }
+                // the slice of a out of the image: the two aligned vectors around each unit, shifted into place
+#pragma unroll
+                for (int i = 0; i < RT_M * 8 / RT_THREADS; ++i) {
+                    const int u = threadIdx.x + i * RT_THREADS;
+                    const int r = u >> 3, gk = k0 + (u & 7) * 8;
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (r < rows && gk < K) {
+                        const int eoff = rshift + r * g.a_cols + gk;
+                        const uint4* rv = reinterpret_cast<const uint4*>(raw) + (eoff >> 3);
+                        v = shift_elems(rv[0], rv[1], eoff & 7);
+                        if (gk + 8 > K) v = keep_first(v, K - gk);
+                    }
+                    *reinterpret_cast<uint4*>(sa_c + sw128_chunk(r, u & 7)) = v;
+                }
+            }
+            if (b_ahead) {
+                // committed above
+            } else if (b_all_aligned) {
 #pragma unroll
                 for (int j = 0; j < RT_BSUB; ++j)
                     commit_subtile<false>(blo[j], bhi[0], sb_c + j * RT_SUB_BYTES, g.b, b_total, g.b_cols, bt[j], j < nb);
