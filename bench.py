@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Throughput benchmark of the DeiT+DGE eval forward (BASELINE metric: images/sec).
+"""Throughput benchmark of the DeiT+DGE eval forward (metric: images/sec).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
@@ -88,7 +88,7 @@ class ClockSampler:
 
 
 def alternate_gate_bias(batch, n_splits=3, big=1e4):
-    """BASELINE config 5's gate skew: even images forced all-coarse (the last split, 1x1), odd images
+    """The 512-pixel measurement configuration's gate skew: even images forced all-coarse (the last split, 1x1), odd images
     all-fine (the first split, 4x4), as a per-image offset of the router logits."""
     bias = torch.zeros(batch, n_splits)
     bias[0::2, n_splits - 1] = big
@@ -464,7 +464,7 @@ def _torch_dense_block(x, blk):
 
 
 def layer_sweep(args):
-    """BASELINE config 4: one DeiT-S DGE layer at batch 256, gate logits N(0,1) plus a bias on
+    """The layer-level configuration: one DeiT-S DGE layer at batch 256, gate logits N(0,1) plus a bias on
     the finest grain chosen by bisection so that the realised fraction of fine regions is
     0 / 0.25 / 0.5 / 1; against the dense block (this library's kernels, and PyTorch ops)."""
     from vtpack_b200 import _lib, synthetic

@@ -22,7 +22,7 @@ def _block(C, h, sd, dtype):
 
 
 def test_layer_fp32_golden(golden_dir):
-    """BASELINE config 1: one DeiT-Ti DGE layer, fp32, B=2, injected gate logits; fp32
+    """Benchmark configuration 1: one DeiT-Ti DGE layer, fp32, B=2, injected gate logits; fp32
     tolerance 1e-4 relative."""
     g = np.load(os.path.join(golden_dir, "layer_tiny_fp32.npz"))
     sd = O.make_state_dict(192, 1, 3, seed=0)
@@ -139,7 +139,7 @@ def test_model_fp32_golden(golden_dir):
 
 @pytest.mark.parametrize("cuda_cores", [True, False])
 def test_model_bf16_logits(cuda_cores):
-    """BASELINE config 2 at reduced batch: DeiT-Ti+DGE bf16 vs the fp32 oracle on
+    """Benchmark configuration 2 at reduced batch: DeiT-Ti+DGE bf16 vs the fp32 oracle on
     bf16-rounded weights; logits max-abs <= 2e-2, top-1 agreement reported."""
     from vtpack_b200 import _lib
     B = 16
@@ -185,7 +185,7 @@ def test_model_bf16_top1_agreement_1024_images():
 
 @pytest.mark.parametrize("dtype,depth,tol", [(torch.float32, 4, 1e-4), (torch.bfloat16, 12, 2e-2)])
 def test_model_512px(dtype, depth, tol):
-    """BASELINE config 5 shape through the whole-model entry point at reduced batch and width:
+    """Benchmark configuration 5 shape through the whole-model entry point at reduced batch and width:
     512 x 512 images (32 x 32 grid + cls = 1025 tokens, 64 regions per image, 1025 keys = four
     256-key chunks + one tail key), free-running router.  fp32: logits within 1e-4 relative of
     the oracle wherever the per-layer query counts agree (they must, unless a gate is a near-tie);
@@ -210,7 +210,7 @@ def test_model_512px(dtype, depth, tol):
 
 
 def test_layer_512px_bf16_skewed():
-    """BASELINE config 5 shape at reduced batch: 32x32 grid (1025 keys = 4 chunks of 256 + 1 tail
+    """Benchmark configuration 5 shape at reduced batch: 32x32 grid (1025 keys = 4 chunks of 256 + 1 tail
     key), even images all-coarse (65 queries), odd images all-fine (1025 queries), bf16."""
     from vtpack_b200 import _lib
     sd = O.round_bf16(O.make_state_dict(384, 1, 6, img_size=512, seed=20))
@@ -228,7 +228,7 @@ def test_layer_512px_bf16_skewed():
 
 @pytest.mark.parametrize("fine_bias", [-1e4, -0.5, 0.7, 1e4])
 def test_layer_gate_skew_bf16(fine_bias):
-    """BASELINE config 4 at reduced batch: gate skew from all-coarse to all-fine."""
+    """Benchmark configuration 4 at reduced batch: gate skew from all-coarse to all-fine."""
     sd = O.round_bf16(O.make_state_dict(384, 1, 6, seed=22))
     x = O.make_tokens(6, 257, 384, seed=23).bfloat16().float()
     gate = O.make_gate_logits(6, 4, 4, 3, seed=24, fine_bias=fine_bias)
@@ -241,7 +241,7 @@ def test_layer_gate_skew_bf16(fine_bias):
 
 
 def test_full_size_properties():
-    """BASELINE config 3 size (DeiT-S, batch 256, bf16): properties that need no oracle run.
+    """Benchmark configuration 3 size (DeiT-S, batch 256, bf16): properties that need no oracle run.
     Images are independent, so permuting the batch permutes the logits; every per-image query
     count is 1 + sum of 16 values from {1, 4, 16}, hence within [17, 257] and = 2 (mod 3); with
     every region forced to the finest grain the DGE block is the dense block."""

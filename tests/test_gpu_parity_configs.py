@@ -66,7 +66,7 @@ def _gate_agreement(model, sd, depth, G):
 
 
 def test_bench_input_deit_s_b256_logits_and_gates():
-    """BASELINE config 3 as the bench runs it: DeiT-S+DGE, bf16, batch 256, the bench's seeded images and
+    """Benchmark configuration 3 as the bench runs it: DeiT-S+DGE, bf16, batch 256, the bench's seeded images and
     weights, against the fp32 oracle on the bf16-rounded weights.
     (a) Same activations -> same gates: gates are fp32 arithmetic on the activations the device holds; with
         the oracle's router fed those very bf16 tokens, every grain index whose top-2 margin exceeds 1e-5 is
@@ -153,7 +153,7 @@ def test_top1_agreement_separable_head_1024_images():
 
 
 def test_config2_deit_ti_b64_bf16():
-    """BASELINE config 2 at its own batch: DeiT-Ti+DGE, bf16, batch 64."""
+    """Benchmark configuration 2 at its own batch: DeiT-Ti+DGE, bf16, batch 64."""
     from vtpack_b200 import _lib
     B = 64
     sd = O.round_bf16(O.make_state_dict(192, 12, 3, seed=0))
@@ -174,7 +174,7 @@ def test_config2_deit_ti_b64_bf16():
 
 @pytest.mark.parametrize("fine_frac", [0.0, 0.25, 0.5, 1.0])
 def test_config4_layer_b256_gate_skew(fine_frac):
-    """BASELINE config 4 at its own batch: one DeiT-S DGE layer, bf16, batch 256, gate logits N(0,1) plus
+    """Benchmark configuration 4 at its own batch: one DeiT-S DGE layer, bf16, batch 256, gate logits N(0,1) plus
     a bias on the finest grain so that about `fine_frac` of the regions take it."""
     from vtpack_b200 import _lib
     from vtpack_b200.models.dge.deit_dge import Block
@@ -207,7 +207,7 @@ def test_config4_layer_b256_gate_skew(fine_frac):
 
 
 def test_config5_512px_alternating_skew_c384():
-    """BASELINE config 5 at full width and depth, reduced batch: DeiT-S+DGE, 512 px (1025 tokens, 64 regions),
+    """Benchmark configuration 5 at full width and depth, reduced batch: DeiT-S+DGE, 512 px (1025 tokens, 64 regions),
     bf16, even images forced all-coarse (65 queries), odd images all-fine (1025 queries) through the per-image
     gate bias the bench uses; logits within 2e-2 max-abs of the fp32 oracle on bf16-rounded weights."""
     from vtpack_b200 import _lib
