@@ -474,46 +474,45 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
             float e1 = 0.f, e2 = 0.f;     // sum and sum of squares of this thread's outputs
             if (tma_path) {
                 // ---- full tile: registers -> swizzled staging slab -> TMA store
+                // The slab loop is unrolled (two register sets take the tensor-memory loads in turn, so nothing is
+                // copied) and every shared-memory access goes through a 32-bit shared-space address worked out once
+                // per tile: the tensor core pays for each instruction these sixteen warps issue.
                 named_barrier(1, EPI_THREADS);                       // bias slice complete
-                uint32_t r[16];
+                const uint32_t cell0 = (uint32_t)row * 128u + ((uint32_t)((qsub * 2) ^ (row & 7)) << 4);
+                const uint32_t cell1 = (uint32_t)row * 128u + ((uint32_t)((qsub * 2 + 1) ^ (row & 7)) << 4);
+                const uint32_t stage_a = smem_u32(smem_out);
+                const uint32_t vec_a = smem_u32(bias_s) + (uint32_t)qsub * 64u;     // this thread's 16 columns of slab 0
+                uint32_t rbuf[2][16];
                 __syncwarp();
-                tmem_ld_32x16(tacc + qsub * 16, r);
-#pragma unroll 1
-                for (int sl = 0; sl < NSLAB; ++sl, ++slab_no) {
+                tmem_ld_32x16(tacc + qsub * 16, rbuf[0]);
+#pragma unroll
+                for (int sl = 0; sl < BN / 64; ++sl) {
+                    if (sl >= NSLAB || !ok) continue;
+                    uint32_t (&r)[16] = rbuf[sl & 1];
                     // the additive part of this slab's 16 columns (bias, or bias + ln_b * s for a folded
                     // LayerNorm), fetched from shared memory while the accumulator columns are on their way
                     float cadd[16];
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const float4* bs = reinterpret_cast<const float4*>(bias_s + sl * 64 + (qsub * 2 + j) * 8);
-                        const float4 b0 = bs[0];
-                        const float4 b1 = bs[1];
-                        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const float4 b = lds_f4(vec_a + (uint32_t)sl * 256u + q4 * 16u);
+                        cadd[4 * q4] = b.x; cadd[4 * q4 + 1] = b.y; cadd[4 * q4 + 2] = b.z; cadd[4 * q4 + 3] = b.w;
                         if (EPI & EPI_LN) {
-                            const float4 s0 = bs[BN / 4];
-                            const float4 s1 = bs[BN / 4 + 1];
-                            const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) cadd[8 * j + i] = fmaf(ln_b, ss[i], bb[i]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) cadd[8 * j + i] = bb[i];
+                            const float4 sv = lds_f4(vec_a + (uint32_t)BN * 4u + (uint32_t)sl * 256u + q4 * 16u);
+                            cadd[4 * q4] = fmaf(ln_b, sv.x, b.x); cadd[4 * q4 + 1] = fmaf(ln_b, sv.y, b.y);
+                            cadd[4 * q4 + 2] = fmaf(ln_b, sv.z, b.z); cadd[4 * q4 + 3] = fmaf(ln_b, sv.w, b.w);
                         }
                     }
                     tmem_ld_wait();
-                    float v[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
                     if (sl + 1 < NSLAB) {
                         __syncwarp();
-                        tmem_ld_32x16(tacc + (sl + 1) * 64 + qsub * 16, r);     // next slab in flight
+                        tmem_ld_32x16(tacc + (sl + 1) * 64 + qsub * 16, rbuf[(sl + 1) & 1]);     // next slab in flight
                     } else {
                         tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) release_acc(buf);                        // accumulator is free
                     }
                     const int sb = slab_no % NSTG;                                // staging slab of this one
-                    uint8_t* srow = smem_out + sb * (TBM * 128) + row * 128;
+                    const uint32_t srow_a = stage_a + (uint32_t)sb * (TBM * 128);
                     if (res) {
                         // the residual of this slab is in the staging slab (so the slab is free, too)
                         ok = mbar_wait(&res_full[sb], (slab_no / NSTG) & 1, abort_flag, status,
@@ -523,40 +522,41 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
                         ok = mbar_wait(&slab_free[sb], ((slab_no / NSTG) - 1) & 1, abort_flag, status,
                                        STATUS_GEMM_EPILOGUE);
                     }
-                    if (!ok) break;
+                    if (!ok) continue;
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
-                        float* vj = v + 8 * j;
-                        const int chunk = qsub * 2 + j;                          // 16-byte chunk within the 128-byte row
-                        uint4* cell = reinterpret_cast<uint4*>(srow + ((chunk ^ (row & 7)) << 4));
+                        const uint32_t cell = srow_a + (j ? cell1 : cell0);
+                        float vj[8];
                         if (EPI & EPI_LN) {
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) vj[i] = fmaf(ln_a, vj[i], cadd[8 * j + i]);
+                            for (int i = 0; i < 8; ++i) vj[i] = fmaf(ln_a, __uint_as_float(r[8 * j + i]), cadd[8 * j + i]);
                         } else {
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) vj[i] += cadd[8 * j + i];
+                            for (int i = 0; i < 8; ++i) vj[i] = __uint_as_float(r[8 * j + i]) + cadd[8 * j + i];
                         }
                         if (EPI & EPI_GELU) gelu8(vj);
                         if (res) {
                             Vec<bf16> rv;
                             float rf[8];
-                            rv.raw = *cell;                                      // residual slab, same layout
+                            rv.raw = lds_u4(cell);                               // residual slab, same layout
                             rv.to_float(rf);
 #pragma unroll
                             for (int i = 0; i < 8; ++i) vj[i] += rf[i];
                         }
-                        if ((EPI & EPI_EMIT) && nt0 + sl * 64 + chunk * 8 < N) {
+                        if ((EPI & EPI_EMIT) && nt0 + sl * 64 + (qsub * 2 + j) * 8 < N) {
 #pragma unroll
                             for (int i = 0; i < 8; ++i) { e1 += vj[i]; e2 = fmaf(vj[i], vj[i], e2); }
                         }
                         Vec<bf16> ov;
                         ov.from_float(vj);
-                        *cell = ov.raw;
+                        sts_u4(cell, ov.raw);
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&slab_full[sb]);                // this warp's part of the slab is in place
+                    ++slab_no;
                 }
+                if (!ok) break;
                 if (EPI & EPI_EMIT) ln.emit[(size_t)(m0 + row) * STAT_SLOTS + wi.nt * 4 + qsub] = make_float2(e1, e2);
                 continue;
             }
