@@ -28,7 +28,7 @@ STAGES = ["router_gate", "patch_list", "pool_ln1", "q_proj", "kv_proj", "attenti
 # DRAM bytes (read + written) of one launch of the dominant kernel on the roofline's workload (the kv
 # projection at batch 256: M=65792, N=768, K=384), from the ncu capture summarised in
 # profiles/linear_tc_kv_projection_m65792_n768_k384.md; scaled by the row count for other batch sizes
-NCU_TRAFFIC_BYTES_PER_ROW = (51183872 + 43640832) / 65792
+NCU_TRAFFIC_BYTES_PER_ROW = (51173888 + 43880448) / 65792
 
 
 def peaks():
