@@ -370,8 +370,8 @@ def launches_per_forward(model):
     depth = len(model.blocks)
     if model.compute_dtype() == torch.bfloat16 and not model.flags:
         C = model.embed_dim
-        # the q and kv projections share one launch when both widths tile by 256 with 0, 64 or 128 columns left
-        paired = C >= 256 and C % 256 in (0, 64, 128) and (2 * C) % 256 in (0, 64, 128)
+        # the q and kv projections share one launch when both widths are whole 64-column slabs
+        paired = C >= 64 and C % 64 == 0
         return 9 + (7 if paired else 8) * depth
     return 5 + 12 * depth
 

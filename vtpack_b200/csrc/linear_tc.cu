@@ -789,12 +789,13 @@ static int check_tc_args(const LinearArgs& p) {
 // Two independent Linears that follow the same kind of LayerNorm fold (the q and kv projections of a block)
 // in ONE launch of 128 x 256 tiles: the tiles of the second problem fill the last, partial round of the first,
 // and one launch's ramp and tail is saved.  Both: bf16 output, bias + folded LayerNorm (ln_mode 1), no
-// residual, no row remap; an N that is not a multiple of 256 must leave 64 or 128 columns.
+// residual, no row remap; N a multiple of 64.
 bool linear_pair_supported(const LinearArgs& a, const LinearArgs& b) {
     auto ok = [](const LinearArgs& p) {
-        const int rem = p.N % 256;
+        // whole 64-column slabs: a last tile of 64 or 128 columns is a narrow tile, one of 192 a full tile whose
+        // W rows beyond N the TMA load fills with zeros and whose last slab the TMA store drops
         return p.dtype == VTP_BF16 && p.ln_mode == 1 && !p.res && !p.emit_stats && p.out_grp == 0 && p.flags == 0 &&
-               p.m_max > 0 && p.N >= 256 && (rem == 0 || rem == 64 || rem == 128);
+               p.m_max > 0 && p.N >= 64 && p.N % 64 == 0;
     };
     return ok(a) && ok(b) && a.K == b.K;
 }
