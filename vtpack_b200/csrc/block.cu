@@ -11,7 +11,8 @@
 
 namespace vtp {
 
-int token_im2col(const void* x, int dtype, int B, int H, int W, int C, int sr, void* cols, cudaStream_t st);  // patch_embed.cu
+int token_im2col(const void* x, int dtype, int B, int H, int W, int C, int sr, void* cols, cudaStream_t st,
+                 const float2* stats = nullptr, const float* lnw = nullptr, const float* lnb = nullptr);  // patch_embed.cu
 
 struct Carver {
     char* base;
@@ -157,6 +158,10 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
                 "block: spatial reduction needs the sr and sr_norm parameters");
     const int n_keys = keys_per_image(s);
     const bool fold = by_region && s.dtype == VTP_BF16 && !kflag && has_folded_weights(w) && !reduce;
+    // A PVT block folds norm1 into q and norm2 into fc1 all the same; only its keys need LayerNorm rows, and the
+    // im2col in front of the reducing convolution normalises them on the way from the token statistics.
+    const bool fold_q = fold || (by_region && s.dtype == VTP_BF16 && !kflag && reduce && w.q_wf && w.q_s && w.q_c &&
+                                 w.fc1_wf && w.fc1_s && w.fc1_c);
     const int par = chain.parity & 1;
     int32_t* idx = b.idx[par];
     int32_t* counts = b.counts[par];
@@ -177,7 +182,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
         RegionGateArgs ga;
         ga.g = g; ga.x = x_in; ga.gw = w.gate_w; ga.gb = w.gate_b; ga.S = s.n_splits; ga.logits_out = b.logits[par];
         ga.idx_out = idx; ga.eps = s.eps; ga.image_bias = chain.image_bias;
-        if (fold) { ga.stats_x = stats_x; stats_x_ready = true; }
+        if (fold_q) { ga.stats_x = stats_x; stats_x_ready = true; }
         rc = region_gate(ga, s.dtype, st);
     } else {
         rc = vtp_router_gate(x_in, s.dtype, s.B, s.H, s.W, C, s.num_extra, s.region, w.gate_w, w.gate_b,
@@ -199,7 +204,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
         pa.offsets = b.offsets; pa.counts = counts; pa.offsets_out = b.offsets; pa.region_first_out = b.region_first;
         const bool will_chain = fold && chain.next && has_folded_weights(*chain.next);
         pa.counts_next = (chained && will_chain) ? b.counts[par ^ 1] : nullptr;
-        if (fold) {
+        if (fold_q) {
             pa.stats_x = stats_x; pa.stats_q = b.stats_q;
             pa.stats_x_ready = stats_x_ready;
         }
@@ -212,16 +217,18 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     if (rc || (rc = marks.mark(3))) return rc;
 
     LinearArgs lq;   // q = LN(comp) Wq^T + b
-    lq.a = fold ? b.comp : b.qn; lq.lda = C; lq.w = fold ? w.q_wf : w.q_w; lq.bias = fold ? w.q_c : w.q_b;
+    lq.a = fold_q ? b.comp : b.qn; lq.lda = C; lq.w = fold_q ? w.q_wf : w.q_w; lq.bias = fold_q ? w.q_c : w.q_b;
     lq.y = b.qp; lq.ldy = C; lq.dtype = s.dtype; lq.m_max = rows; lq.m_dev = L_dev; lq.N = C; lq.K = C; lq.flags = kflag;
-    if (fold) { lq.ln_mode = 1; lq.ln_stats = b.stats_q; lq.ln_s = w.q_s; }
+    if (fold_q) { lq.ln_mode = 1; lq.ln_stats = b.stats_q; lq.ln_s = w.q_s; }
 
     const void* keys_in = fold ? x_in : b.xn;
     if (reduce) {
         if ((rc = linear(lq, st)) || (rc = marks.mark(4))) return rc;
         // x_ = norm(sr(LN1(x) as [B,C,H,W])): the stride-sr convolution as im2col rows times a matrix
         const int krows = s.B * n_keys, KS = s.sr_ratio * s.sr_ratio * C;
-        if ((rc = token_im2col(b.xn, s.dtype, s.B, s.H, s.W, C, s.sr_ratio, b.sr_cols, st))) return rc;
+        if (fold_q) rc = token_im2col(x_in, s.dtype, s.B, s.H, s.W, C, s.sr_ratio, b.sr_cols, st, stats_x, w.norm1_w, w.norm1_b);
+        else rc = token_im2col(b.xn, s.dtype, s.B, s.H, s.W, C, s.sr_ratio, b.sr_cols, st);
+        if (rc) return rc;
         LinearArgs lsr;
         lsr.a = b.sr_cols; lsr.lda = KS; lsr.w = w.sr_w; lsr.bias = w.sr_b; lsr.y = b.sr_out; lsr.ldy = C;
         lsr.dtype = s.dtype; lsr.m_max = krows; lsr.N = C; lsr.K = KS; lsr.flags = kflag;
@@ -255,20 +262,20 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     LinearArgs lp;   // q1 = comp + attn_out Wp^T + b   (and, when folding, the row sums LN2 needs)
     lp.a = b.ao; lp.lda = C; lp.w = w.proj_w; lp.bias = w.proj_b; lp.res = b.comp; lp.ldr = C; lp.y = b.q1;
     lp.ldy = C; lp.dtype = s.dtype; lp.m_max = rows; lp.m_dev = L_dev; lp.N = C; lp.K = C; lp.flags = kflag;
-    if (fold) lp.emit_stats = b.stats_acc;
+    if (fold_q) lp.emit_stats = b.stats_acc;
     if ((rc = linear(lp, st)) || (rc = marks.mark(7))) return rc;
 
-    if (!fold) {
+    if (!fold_q) {
         rc = vtp_layernorm(b.q1, s.dtype, rows, L_dev, C, C, w.norm2_w, w.norm2_b, s.eps, b.qn, st);
         if (rc) return rc;
     }
     if ((rc = marks.mark(8))) return rc;
 
     LinearArgs l1;   // hid = GELU(LN2(q1) W1^T + b)
-    l1.a = fold ? b.q1 : b.qn; l1.lda = C; l1.w = fold ? w.fc1_wf : w.fc1_w; l1.bias = fold ? w.fc1_c : w.fc1_b;
+    l1.a = fold_q ? b.q1 : b.qn; l1.lda = C; l1.w = fold_q ? w.fc1_wf : w.fc1_w; l1.bias = fold_q ? w.fc1_c : w.fc1_b;
     l1.y = b.hid; l1.ldy = s.hidden; l1.dtype = s.dtype; l1.m_max = rows; l1.m_dev = L_dev; l1.N = s.hidden; l1.K = C;
     l1.flags = kflag | VTP_FLAG_GELU;
-    if (fold) { l1.ln_mode = 2; l1.ln_stats = b.stats_acc; l1.ln_s = w.fc1_s; l1.ln_dim = C; l1.ln_eps = s.eps;
+    if (fold_q) { l1.ln_mode = 2; l1.ln_stats = b.stats_acc; l1.ln_s = w.fc1_s; l1.ln_dim = C; l1.ln_eps = s.eps;
                 l1.ln_slots = linear_stat_slots(C); }
     if ((rc = linear(l1, st)) || (rc = marks.mark(9))) return rc;
 

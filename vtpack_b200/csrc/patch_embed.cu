@@ -86,7 +86,9 @@ __global__ void cls_row_kernel(const T* __restrict__ cls, const T* __restrict__ 
 // Replaces the permute / reshape in front of attn.sr (vtpack/models/dge/pvt_dge.py:82-83).
 template <typename T>
 __global__ void __launch_bounds__(256)
-token_im2col_kernel(const T* __restrict__ x, long long total_vec, int H, int W, int C, int sr, T* __restrict__ cols) {
+token_im2col_kernel(const T* __restrict__ x, long long total_vec, int H, int W, int C, int sr, T* __restrict__ cols,
+                    const float2* __restrict__ stats, const float* __restrict__ lnw, const float* __restrict__ lnb) {
+    // stats != null: the rows gathered are LayerNorm(x), normalised on the way from each token's (mean, rstd)
     constexpr int VN = Vec<T>::N;
     const int run = sr * C / VN;                  // 16-byte vectors per window row
     const int Wo = W / sr, Ho = H / sr;
@@ -101,20 +103,31 @@ token_im2col_kernel(const T* __restrict__ x, long long total_vec, int H, int W, 
         const long long tok = (b * H + (long long)oy * sr + dy) * W + (long long)ox * sr;
         Vec<T> t;
         t.load(x + tok * C + (long long)i * VN);
+        if (stats) {
+            const int e0 = i * VN;                        // element of the window row: token e0 / C, channel e0 % C
+            const float2 ms = stats[tok + e0 / C];
+            const int ch = e0 % C;
+            float f[VN];
+            t.to_float(f);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) f[k] = (f[k] - ms.x) * ms.y * __ldg(lnw + ch + k) + __ldg(lnb + ch + k);
+            t.from_float(f);
+        }
         t.store(cols + ((((b * Ho + oy) * Wo + ox) * sr + dy) * (long long)run + i) * VN);
     }
 }
 
-int token_im2col(const void* x, int dtype, int B, int H, int W, int C, int sr, void* cols, cudaStream_t st) {
+int token_im2col(const void* x, int dtype, int B, int H, int W, int C, int sr, void* cols, cudaStream_t st,
+                 const float2* stats, const float* lnw, const float* lnb) {
     const int vn = dtype == VTP_BF16 ? 8 : 4;
     VTP_REQUIRE(C % vn == 0, VTP_ERR_SHAPE, "spatial reduction: C=%d must be a multiple of %d", C, vn);
     const long long total = (long long)B * H * W * C / vn;
     if (total == 0) return VTP_OK;
     const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (dtype == VTP_BF16)
-        token_im2col_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, total, H, W, C, sr, (bf16*)cols);
+        token_im2col_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, total, H, W, C, sr, (bf16*)cols, stats, lnw, lnb);
     else
-        token_im2col_kernel<float><<<grid, 256, 0, st>>>((const float*)x, total, H, W, C, sr, (float*)cols);
+        token_im2col_kernel<float><<<grid, 256, 0, st>>>((const float*)x, total, H, W, C, sr, (float*)cols, stats, lnw, lnb);
     return check_launch("spatial reduction im2col");
 }
 
@@ -154,7 +167,7 @@ extern "C" int vtp_token_im2col(const void* x, int dtype, int B, int H, int W, i
     VTP_REQUIRE(B > 0 && H > 0 && W > 0 && C > 0 && ratio > 0 && H % ratio == 0 && W % ratio == 0, VTP_ERR_SHAPE,
                 "token im2col: grid %dx%d / ratio %d", H, W, ratio);
     VTP_REQUIRE(aligned16(x) && aligned16(cols), VTP_ERR_ALIGN, "token im2col: unaligned pointer");
-    return token_im2col(x, dtype, B, H, W, C, ratio, cols, static_cast<cudaStream_t>(stream));
+    return token_im2col(x, dtype, B, H, W, C, ratio, cols, static_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr);
 }
 
 extern "C" int vtp_add_rows(const void* x, int x_mod, const void* addend, int a_mod, int a_off, void* out, int out_grp,

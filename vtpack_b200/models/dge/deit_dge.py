@@ -167,7 +167,7 @@ class _WeightPack:
 
 
 def _param_key(mod: nn.Module, dtype):
-    return (dtype, getattr(mod, "fold_layernorm", None)) + tuple((p.data_ptr(), p._version, p.dtype) for p in mod.parameters())
+    return (dtype, getattr(mod, "fold_layernorm", None), getattr(mod, "fold_q_fc1", None)) + tuple((p.data_ptr(), p._version, p.dtype) for p in mod.parameters())
 
 
 def _pack_block(blk, dtype) -> _lib.BlockWeights:
@@ -195,11 +195,15 @@ def _pack_block(blk, dtype) -> _lib.BlockWeights:
             t["sr_w"] = mat(sr.weight.permute(0, 2, 3, 1).reshape(sr.weight.shape[0], -1))
             t["sr_b"] = vec(sr.bias) if sr.bias is not None else zeros(a.dim, sr.weight)
             t["sr_norm_w"], t["sr_norm_b"] = vec(a.norm.weight), vec(a.norm.bias)
-        if dtype == torch.bfloat16 and blk.fold_layernorm and sr is None:
-            # LayerNorm folded into the Linear that follows it (weight preparation, once)
-            for name, lin_w, lin_b, gw, gb in (("q", t["q_w"], t["q_b"], t["norm1_w"], t["norm1_b"]),
-                                               ("kv", t["kv_w"], t["kv_b"], t["norm1_w"], t["norm1_b"]),
-                                               ("fc1", t["fc1_w"], t["fc1_b"], t["norm2_w"], t["norm2_b"])):
+        if dtype == torch.bfloat16 and (blk.fold_layernorm or (sr is not None and getattr(blk, "fold_q_fc1", False))):
+            # LayerNorm folded into the Linear that follows it (weight preparation, once).  A block with a spatial
+            # reduction folds q and fc1 only: its kv projection reads the reduced, separately normalised keys.
+            folds = [("q", t["q_w"], t["q_b"], t["norm1_w"], t["norm1_b"]),
+                     ("kv", t["kv_w"], t["kv_b"], t["norm1_w"], t["norm1_b"]),
+                     ("fc1", t["fc1_w"], t["fc1_b"], t["norm2_w"], t["norm2_b"])]
+            if sr is not None:
+                del folds[1]
+            for name, lin_w, lin_b, gw, gb in folds:
                 wf = torch.empty_like(lin_w)
                 sv = torch.empty(lin_w.shape[0], dtype=torch.float32, device=lin_w.device)
                 cv = torch.empty_like(sv)

@@ -101,7 +101,9 @@ class Block(nn.Module):
         self.dge = DynamicGrainedEncoder(in_channels=dim, split_sizes=split_sizes, complexity_handler=self.complexity)
         self.split_sizes = list(split_sizes)
         self.flags = 0
-        self.fold_layernorm = sr_ratio <= 1      # the reduced keys need explicit LayerNorm rows
+        self.fold_layernorm = sr_ratio <= 1      # bf16: norm1 into q and kv, norm2 into fc1 (GEMM epilogues)
+        self.fold_q_fc1 = sr_ratio > 1           # with a spatial reduction: q and fc1 only, the keys are normalised
+                                                 # on the way into the reducing convolution
         self._pack = _WeightPack()
 
     def complexity(self, num_inputs, num_queries):
