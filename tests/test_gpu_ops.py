@@ -151,7 +151,10 @@ def test_linear_fp32(vl, M, N, K, gelu, res):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 64, 64), (130, 192, 192), (257, 768, 192), (64, 1000, 384), (300, 384, 1536),
-                                   (1024, 1536, 384)])
+                                   (1024, 1536, 384),
+                                   # narrow, short-K Linears (PVT stages 1 and 2): several tiles per CTA, so the
+                                   # staging slabs and the held bias slice go round more than once
+                                   (148 * 128 * 5 + 77, 64, 64), (148 * 128 * 3, 128, 64), (148 * 128 * 3 + 5, 128, 128)])
 @pytest.mark.parametrize("gelu,res", [(False, False), (True, False), (False, True)])
 def test_linear_bf16_tensor_cores(vl, M, N, K, gelu, res):
     _lib, _ = vl

@@ -54,11 +54,15 @@ constexpr int TBM = 128;   // tile rows of one CTA = TMEM lanes
 constexpr int CG = VTP_LINEAR_CTA_GROUP;
 static_assert(CG == 1 || CG == 2, "one CTA or a pair per tile");
 constexpr int TM = TBM * CG;   // tile rows of the CTA group
-// Staging slabs of the epilogue (128 rows x 64 columns each) and how many TMA stores may be reading them at
+// Staging slabs of the epilogue (128 rows x 64 columns each); half as many TMA stores may be reading them at
 // a time.  A store's shared-memory read takes longer than the epilogue needs to fill the next slab, so with
 // two slabs the epilogue waits on the store; the pair kernel's smaller operand stages leave room for four.
-constexpr int NSTG = CG == 2 ? 4 : 2;
-constexpr int STORES_IN_FLIGHT = NSTG / 2;
+// A narrow Linear (N <= 128) with one k-block per tile, or two and a residual to fetch, spends its time in the
+// epilogue's hand-offs: it runs with a ring of SHALLOW_RING stages, gives the shared memory to four staging
+// slabs and keeps its bias slice across tiles (measured at 1 M rows, K = N = 64: 80 -> 71 us, with a residual
+// 117 -> 85 us; wide tiles with GELU and K = 128 without a residual were faster on the deep ring).
+constexpr int SHALLOW_RING = 3;
+constexpr int staging_slabs(int stages) { return CG == 2 ? 4 : (stages <= SHALLOW_RING ? 4 : 2); }
 // depth of the operand ring for a tile width: what fits beside the staging slabs
 constexpr int ring_stages(int bn) { return CG == 2 ? (bn == 128 ? 6 : 5) : (bn == 128 ? 5 : 4); }
 constexpr int TBK = 64;    // 64 bf16 = one 128-byte swizzle row
@@ -70,6 +74,8 @@ struct TcSmem {
     static constexpr int A_BYTES = TBM * TBK * 2;
     static constexpr int B_BYTES = (BN / CG) * TBK * 2;   // this CTA's share of the W rows
     static constexpr int RING = STAGES * (A_BYTES + B_BYTES);
+    static constexpr int NSTG = staging_slabs(STAGES);
+    static constexpr int STORES_IN_FLIGHT = NSTG / 2;
     static constexpr int STAGE_OUT = NSTG * TBM * 128;   // 128-row x 64-column bf16 slabs
     static constexpr int BIAS = 2 * BN * 4;           // the bias and LayerNorm-fold slices of the tile in the epilogue
     static constexpr int USED = RING + STAGE_OUT + BIAS + 512 /* barriers */;
@@ -146,6 +152,7 @@ template <int BN, int STAGES, typename OutT, int EPI, int NPROB>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
     using S = TcSmem<BN, STAGES>;
+    constexpr int NSTG = S::NSTG, STORES_IN_FLIGHT = S::STORES_IN_FLIGHT;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = base;
@@ -408,6 +415,7 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
         const int qsub = (warp - 2) >> 2;             // which of the four warps of that quarter
         const int row = quarter * 32 + lane;          // tile row = TMEM lane
         int lt = 0, slab_no = 0;
+        int held_p = -1, held_ct0 = -1, held_width = -1;   // the bias slice that is in shared memory
         bool ok = true;
         Item wi;
         for (int j = 0; ok && item_at(j, wi); ++j, ++lt) {
@@ -422,10 +430,16 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
             const int buf = lt & 1;
             const uint32_t aph = (lt >> 1) & 1;
             const bool tma_path = P.use_tma_store && m0 + TBM <= M;
-            if (tma_path) {
+            // A CTA whose tiles keep to one column range (a Linear no wider than a tile, or a column-tile count
+            // that divides the grid) loads the slice once: a short-K tile is too brief to hide a global load and
+            // two barriers of the sixteen warps in.
+            const bool new_slice = tma_path && !(STAGES <= SHALLOW_RING && wi.p == held_p && nt0 == held_ct0 &&
+                                                 wi.width == held_width);
+            if (new_slice) {
                 // this tile's bias slice -> shared memory (one value per thread), so the column
                 // loop reads it as a broadcast instead of through the global-load path
                 named_barrier(1, EPI_THREADS);                       // nobody reads the previous slice any more
+                held_p = wi.p; held_ct0 = nt0; held_width = wi.width;
                 const int te = threadIdx.x - 64;
                 if (te < wi.width) {
                     bias_s[te] = (bias && nt0 + te < N) ? __ldg(bias + nt0 + te) : 0.f;
@@ -477,7 +491,7 @@ linear_tc_kernel(const __grid_constant__ TcLaunch L, int K, int* status) {
                 // The slab loop is unrolled (two register sets take the tensor-memory loads in turn, so nothing is
                 // copied) and every shared-memory access goes through a 32-bit shared-space address worked out once
                 // per tile: the tensor core pays for each instruction these sixteen warps issue.
-                named_barrier(1, EPI_THREADS);                       // bias slice complete
+                if (new_slice) named_barrier(1, EPI_THREADS);        // bias slice complete
                 const uint32_t cell0 = (uint32_t)row * 128u + ((uint32_t)((qsub * 2) ^ (row & 7)) << 4);
                 const uint32_t cell1 = (uint32_t)row * 128u + ((uint32_t)((qsub * 2 + 1) ^ (row & 7)) << 4);
                 const uint32_t stage_a = smem_u32(smem_out);
@@ -828,8 +842,10 @@ int linear_tcgen05(const LinearArgs& p, cudaStream_t st) {
         if (bn == 192) return launch_tc<192, ring_stages(192), float, 0>(p, nullptr, st);
         return launch_tc<128, ring_stages(128), float, 0>(p, nullptr, st);
     }
+    const bool shallow = CG == 1 && bn == 128 && (p.K <= TBK || (p.K <= 2 * TBK && p.res));
 #define VTP_TC_CASE(E)                                                  \
     if (epi == (E)) {                                                   \
+        if (shallow) return launch_tc<128, SHALLOW_RING, bf16, (E)>(p, nullptr, st);            \
         if (bn == 256) return launch_tc<256, ring_stages(256), bf16, (E)>(p, nullptr, st);      \
         if (bn == 192) return launch_tc<192, ring_stages(192), bf16, (E)>(p, nullptr, st);      \
         return launch_tc<128, ring_stages(128), bf16, (E)>(p, nullptr, st);                     \
