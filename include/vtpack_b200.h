@@ -367,6 +367,20 @@ int vtp_dge_block_forward(const vtp_dge_shape* s, const vtp_block_weights* w, co
                           void* workspace, long long workspace_bytes, void* stream);
 
 /*
+ * Eval forward of n_blocks consecutive DGE blocks of ONE shape, w[0 .. n_blocks-1]: a stage of the pyramid
+ * model (the `for blk in block: x = blk(x, H, W)` loop, vtpack/models/dge/pvt_dge.py:318-319) or any run
+ * of DeiT+DGE blocks (vtpack/models/dge/deit_dge.py:291-292).  x_in [B,N,C] -> x_out [B,N,C] (may alias);
+ * blocks after the first work on x_out in place.  Same results as n_blocks calls of
+ * vtp_dge_block_forward; where two neighbours both run with folded LayerNorms, the first one's unpool
+ * also leaves the second one's token statistics, router decisions and per-image counts, so the second
+ * starts at its pooling.  counts_out (int32 [n_blocks, B], optional) receives the per-image query
+ * counts of every block.  The workspace is one block's (vtp_block_workspace_bytes).
+ */
+int vtp_dge_blocks_forward(const vtp_dge_shape* s, const vtp_block_weights* w, int n_blocks,
+                           const void* x_in, void* x_out, int32_t* counts_out, void* workspace,
+                           long long workspace_bytes, void* stream);
+
+/*
  * Same as vtp_dge_block_forward, and records events[i] (cudaEvent_t created by the caller,
  * null entries skipped) on the stream after stage i:
  *   0 start, 1 router gate, 2 patch list, 3 pool+LN1, 4 q proj, 5 kv proj, 6 attention,

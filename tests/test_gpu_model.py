@@ -327,6 +327,34 @@ def test_pvt_block_stages(C, heads, H, sr, mr, extra, dtype):
     assert err < (1e-4 if dtype == torch.float32 else 2e-2), err
 
 
+@pytest.mark.parametrize("C,heads,H,sr,mr,extra", [(64, 1, 64, 8, 8, 0), (128, 2, 32, 4, 8, 0), (320, 5, 16, 2, 4, 0),
+                                                   (512, 8, 8, 1, 4, 1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pvt_stage_in_one_call_equals_block_by_block(C, heads, H, sr, mr, extra, dtype):
+    """Three blocks of a stage through ``stage_forward`` (one C-ABI call; in bf16 a block's unpool leaves the
+    next block's router decisions, counts and token statistics) against the same blocks called one by one
+    (every block runs its own gate and patch-list kernels): identical per-image query counts for every
+    block, outputs equal to within the last bit of a few sums whose order differs."""
+    from vtpack_b200 import _lib
+    from vtpack_b200.models.dge.pvt_dge import stage_forward
+    B = 6
+    blocks = [_pvt_block(C, heads, mr, sr, O.make_pvt_block_weights(C, mr, sr, seed=20 + i), dtype) for i in range(3)]
+    x = O.make_tokens(B, H * H + extra, C, seed=8).to(DEV).to(dtype)
+    one = x
+    counts_one = []
+    for blk in blocks:
+        one = blk(one, H, H)
+        counts_one.append(blk.dge.states["batches_device"].tolist())
+    x_before = x.clone()
+    got = stage_forward(blocks, x, H, H)
+    assert _lib.device_status() == 0
+    assert torch.equal(x, x_before)                       # the caller's tokens are not written
+    assert [blk.dge.states["batches_device"].tolist() for blk in blocks] == counts_one
+    assert len({tuple(c) for c in counts_one}) > 1        # the blocks did pick different grains
+    assert rel_err(got.float(), one.float()) < (1e-6 if dtype == torch.float32 else 4e-3)
+    assert blocks[1].dge.get_complexity()["dynamic"] is not None
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_pvt_model(golden_dir, dtype):
     """PVT+DGE tiny (4 stages, 8 blocks, patch 4: 4096 -> 64 tokens) through the mirror model: fp32

@@ -94,6 +94,8 @@ PROTOTYPES = {
     "vtp_block_workspace_bytes": (c_ll, [C.POINTER(DgeShape)]),
     "vtp_dge_block_forward": (c_int, [C.POINTER(DgeShape), C.POINTER(BlockWeights), c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_ll, c_void_p]),
+    "vtp_dge_blocks_forward": (c_int, [C.POINTER(DgeShape), C.POINTER(BlockWeights), c_int, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_ll, c_void_p]),
     "vtp_dge_block_forward_timed": (c_int, [C.POINTER(DgeShape), C.POINTER(BlockWeights), c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_ll, C.POINTER(c_void_p), c_int,
                                             c_void_p]),

@@ -118,6 +118,26 @@ static bool has_folded_weights(const vtp_block_weights& w) {
     return w.q_wf && w.q_s && w.q_c && w.kv_wf && w.kv_s && w.kv_c && w.fc1_wf && w.fc1_s && w.fc1_c;
 }
 
+static bool has_folded_q_fc1(const vtp_block_weights& w) {
+    return w.q_wf && w.q_s && w.q_c && w.fc1_wf && w.fc1_s && w.fc1_c;
+}
+
+static RegionGeom region_geom(const vtp_dge_shape& s) {
+    RegionGeom g;
+    g.B = s.B; g.Hr = s.H / s.region; g.Wr = s.W / s.region; g.W = s.W; g.N = s.num_extra + s.H * s.W; g.C = s.C;
+    g.num_extra = s.num_extra; g.region = s.region;
+    return g;
+}
+
+// Whether a block of this shape runs with norm1 folded into q and norm2 into fc1 (bf16 tensor-core path,
+// region-parallel token movers, prepared weights).  A block without a spatial reduction folds kv too.  Only
+// such blocks hand the next block its gate decisions and token statistics from their unpool.
+static bool block_folds(const vtp_dge_shape& s, const vtp_block_weights& w) {
+    if (!region_ops_supported(region_geom(s), s.dtype) || s.dtype != VTP_BF16 || (s.flags & VTP_FLAG_CUDA_CORES))
+        return false;
+    return s.sr_ratio > 1 ? has_folded_q_fc1(w) : has_folded_weights(w);
+}
+
 // Position of a block inside a model forward: whether the previous block's unpool already
 // produced this block's gate decisions and token statistics (in scratch slot `parity`), and
 // the block that follows, whose gate and statistics this block's unpool can produce.
@@ -148,20 +168,18 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
 
     Splits sp;
     if ((rc = make_splits(&sp, s.splits, s.n_splits, s.region))) return rc;
-    RegionGeom g;
-    g.B = s.B; g.Hr = Hr; g.Wr = Wr; g.W = s.W; g.N = N; g.C = C; g.num_extra = s.num_extra; g.region = s.region;
+    const RegionGeom g = region_geom(s);
     // Region-parallel gate / pool / unpool when the region is 4x4 tokens, else one warp per patch.
     const bool by_region = region_ops_supported(g, s.dtype);
-    // LayerNorm folded into the q / kv / fc1 GEMM epilogues (bf16 tensor-core path with prepared weights).
     const bool reduce = s.sr_ratio > 1;        // PVT block: keys from spatially reduced tokens (explicit LayerNorm rows)
     VTP_REQUIRE(!reduce || (w.sr_w && w.sr_norm_w && w.sr_norm_b), VTP_ERR_NULL,
                 "block: spatial reduction needs the sr and sr_norm parameters");
     const int n_keys = keys_per_image(s);
-    const bool fold = by_region && s.dtype == VTP_BF16 && !kflag && has_folded_weights(w) && !reduce;
-    // A PVT block folds norm1 into q and norm2 into fc1 all the same; only its keys need LayerNorm rows, and the
-    // im2col in front of the reducing convolution normalises them on the way from the token statistics.
-    const bool fold_q = fold || (by_region && s.dtype == VTP_BF16 && !kflag && reduce && w.q_wf && w.q_s && w.q_c &&
-                                 w.fc1_wf && w.fc1_s && w.fc1_c);
+    // LayerNorm folded into the GEMM epilogues (bf16 tensor-core path with prepared weights): norm1 into q and
+    // norm2 into fc1.  A PVT block's keys need LayerNorm rows all the same; the im2col in front of the reducing
+    // convolution normalises them on the way from the token statistics.  Without a reduction kv folds norm1 too.
+    const bool fold_q = block_folds(s, w);
+    const bool fold = fold_q && !reduce;
     const int par = chain.parity & 1;
     int32_t* idx = b.idx[par];
     int32_t* counts = b.counts[par];
@@ -169,7 +187,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     bool stats_x_ready = false;
     // chained: gate decisions, per-image counts and token statistics came from the previous
     // block's unpool; the pool kernel then also derives the row offsets itself
-    const bool chained = chain.have_gate && fold && !forced_logits;
+    const bool chained = chain.have_gate && fold_q && !forced_logits;
     VTP_REQUIRE(!chain.image_bias || by_region, VTP_ERR_UNSUPPORTED,
                 "block: a per-image gate bias needs the region-parallel gate (4x4-token regions)");
 
@@ -202,7 +220,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
         pa.g = g; pa.sp = sp; pa.x = x_in; pa.idx = idx; pa.comp = b.comp; pa.eps = s.eps;
         pa.region_first = chained ? nullptr : b.region_first;
         pa.offsets = b.offsets; pa.counts = counts; pa.offsets_out = b.offsets; pa.region_first_out = b.region_first;
-        const bool will_chain = fold && chain.next && has_folded_weights(*chain.next);
+        const bool will_chain = fold_q && chain.next && block_folds(s, *chain.next);
         pa.counts_next = (chained && will_chain) ? b.counts[par ^ 1] : nullptr;
         if (fold_q) {
             pa.stats_x = stats_x; pa.stats_q = b.stats_q;
@@ -288,7 +306,7 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
         RegionUnpoolArgs ua;
         ua.g = g; ua.sp = sp; ua.q = b.qp; ua.comp = b.comp; ua.ref = x_in; ua.out = x_out; ua.idx = idx;
         ua.region_first = b.region_first; ua.offsets = b.offsets;
-        if (fold && chain.next && has_folded_weights(*chain.next)) {
+        if (fold_q && chain.next && block_folds(s, *chain.next)) {
             // the rows being written are the next block's input: leave its LayerNorm statistics and
             // its router gate's decisions in the other scratch slot
             ua.next.stats_x = b.stats_x[par ^ 1]; ua.next.eps = s.eps;
@@ -402,6 +420,32 @@ extern "C" int vtp_dge_block_forward(const vtp_dge_shape* s, const vtp_block_wei
                          static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int vtp_dge_blocks_forward(const vtp_dge_shape* s, const vtp_block_weights* w, int n_blocks,
+                                      const void* x_in, void* x_out, int32_t* counts_out, void* workspace,
+                                      long long workspace_bytes, void* stream) {
+    if (int rc = check_shape(s)) return rc;
+    VTP_REQUIRE(w && x_in && x_out && workspace, VTP_ERR_NULL, "blocks: null pointer");
+    VTP_REQUIRE(n_blocks > 0, VTP_ERR_SHAPE, "blocks: n_blocks=%d", n_blocks);
+    VTP_REQUIRE(aligned16(workspace), VTP_ERR_ALIGN, "blocks: workspace must be 16-byte aligned");
+    VTP_REQUIRE(workspace_bytes >= carve_block(*s, nullptr).bytes, VTP_ERR_SHAPE,
+                "blocks: workspace of %lld bytes is smaller than the %lld needed", workspace_bytes,
+                carve_block(*s, nullptr).bytes);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    bool chained = false;      // block i-1's unpool prepared block i's gate
+    for (int i = 0; i < n_blocks; ++i) {
+        BlockChain chain;
+        chain.have_gate = chained;
+        chain.parity = i & 1;
+        chain.next = (i + 1 < n_blocks) ? &w[i + 1] : nullptr;
+        if (int rc = block_forward(*s, w[i], i == 0 ? x_in : x_out, x_out, nullptr,
+                                   counts_out ? counts_out + (size_t)i * s->B : nullptr, workspace, st, StageMarks(),
+                                   chain))
+            return rc;
+        chained = chain.next && block_folds(*s, w[i]) && block_folds(*s, *chain.next);
+    }
+    return VTP_OK;
+}
+
 extern "C" int vtp_dge_block_forward_timed(const vtp_dge_shape* s, const vtp_block_weights* w, const void* x_in,
                                            void* x_out, const float* forced_logits, int32_t* counts_out,
                                            void* workspace, long long workspace_bytes, void* const* events,
@@ -489,11 +533,7 @@ extern "C" int vtp_deit_dge_forward_ex(const vtp_dge_shape* s, const vtp_model_w
                                                    cudaMemcpyDeviceToDevice, st);
             if (ce != cudaSuccess) return fail((int)ce, "model: grain trace copy: %s", cudaGetErrorString(ce));
         }
-        RegionGeom g;
-        g.B = s->B; g.Hr = s->H / s->region; g.Wr = s->W / s->region; g.W = s->W; g.N = N; g.C = C;
-        g.num_extra = s->num_extra; g.region = s->region;
-        chained = chain.next && region_ops_supported(g, s->dtype) && s->dtype == VTP_BF16 &&
-                  !(s->flags & VTP_FLAG_CUDA_CORES) && has_folded_weights(blocks[i]) && has_folded_weights(*chain.next);
+        chained = chain.next && block_folds(*s, blocks[i]) && block_folds(*s, *chain.next);
     }
     rc = vtp_layernorm(ms.x, s->dtype, s->B, nullptr, C, (long long)N * C, m->norm_w, m->norm_b, s->eps, ms.cls_n, st);
     if (rc) return rc;

@@ -290,6 +290,8 @@ pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restr
             if (rr == 0) {
                 offsets_out[b] = img_base;
                 if (b == g.B - 1) offsets_out[g.B] = img_base + counts[b];
+                // a grid without extra tokens has no extra-token CTA to start the next block's count
+                if (counts_next && g.num_extra == 0) counts_next[b] = 0;
             }
         }
     }
@@ -597,10 +599,10 @@ gate_region_kernel(const T* __restrict__ x, RegionGeom g, const float* __restric
 
 // (G, CPL) with G * CPL == number of 16-byte chunks in a row; false if the row does not factor
 static bool pick_layout(int nchunks, int* G, int* CPL) {
-    static const int cpls[] = {3, 2, 1, 6, 4};
+    static const int cpls[] = {3, 2, 1, 6, 4, 5};      // 5: C = 320 (PVT stage 3) is 8 lanes x 5 chunks in bf16
     for (int c : cpls)
         for (int g = 32; g >= 8; g >>= 1)
-            if (g * c == nchunks && (g == 32 || c <= 3)) { *G = g; *CPL = c; return true; }
+            if (g * c == nchunks && (g == 32 || c <= 3 || c == 5)) { *G = g; *CPL = c; return true; }
     return false;
 }
 
@@ -657,6 +659,9 @@ static void launch_gate_t(const RegionGateArgs& a, cudaStream_t st) {
         else if (G == 8 && CPL == 1) FN<T, 8, 1>(ARGS, ST);                     \
         else if (G == 32 && CPL == 6) FN<T, 32, 6>(ARGS, ST);                   \
         else if (G == 32 && CPL == 4) FN<T, 32, 4>(ARGS, ST);                   \
+        else if (G == 32 && CPL == 5) FN<T, 32, 5>(ARGS, ST);                   \
+        else if (G == 16 && CPL == 5) FN<T, 16, 5>(ARGS, ST);                   \
+        else if (G == 8 && CPL == 5) FN<T, 8, 5>(ARGS, ST);                     \
         else return fail(VTP_ERR_SHAPE, "C=%d has no lane layout", (ARGS).g.C); \
     } while (0)
 

@@ -145,6 +145,44 @@ class Block(nn.Module):
         return out
 
 
+def stage_forward(blocks, x, H, W):
+    """Eval forward of a stage's blocks (``pvt_dge.py:318-319``: ``for blk in block: x = blk(x, H, W)``) as ONE
+    C-ABI call, ``vtp_dge_blocks_forward``: same results as calling the blocks one by one, but a block whose
+    predecessor ran with folded LayerNorms finds its router decisions, per-image counts and token statistics
+    already written by the predecessor's unpool.  Every block's ``dge.states`` is filled as by its own call."""
+    blocks = list(blocks)
+    require_cuda(x)
+    x = x.contiguous()
+    B, N, C = x.shape
+    b0 = blocks[0]
+    s = _shape_struct(x.dtype, B, H, W, N - H * W, C, b0.attn.num_heads, b0.mlp.fc1.out_features,
+                      b0.split_sizes, b0.norm1.eps, b0.flags, b0.attn.scale)
+    if b0.attn.sr_ratio > 1:
+        s.sr_ratio = b0.attn.sr_ratio
+        s.sr_eps = float(b0.attn.norm.eps)
+    for blk in blocks[1:]:
+        same = (blk.attn.num_heads == b0.attn.num_heads and blk.mlp.fc1.out_features == b0.mlp.fc1.out_features
+                and blk.split_sizes == b0.split_sizes and blk.norm1.eps == b0.norm1.eps and blk.flags == b0.flags
+                and blk.attn.scale == b0.attn.scale and blk.attn.sr_ratio == b0.attn.sr_ratio)
+        if not same:
+            raise ValueError("stage_forward: the blocks of a stage must share one shape")
+    packs = (_lib.BlockWeights * len(blocks))(*[_pack_block(blk, x.dtype) for blk in blocks])
+    lib = _lib.lib()
+    nbytes = lib.vtp_block_workspace_bytes(ctypes.byref(s))
+    _lib.check(0 if nbytes >= 0 else int(nbytes))
+    ws = scratch(x.device, nbytes)
+    out = torch.empty_like(x)
+    counts = torch.empty(len(blocks), B, dtype=torch.int32, device=x.device)
+    _lib.check(lib.vtp_dge_blocks_forward(ctypes.byref(s), packs, len(blocks), ptr(x), ptr(out), ptr(counts), ptr(ws),
+                                          nbytes, stream_ptr(x.device)))
+    for i, blk in enumerate(blocks):
+        # (the input of a block after the first is overwritten in place; the complexity accounting only takes
+        # its shape, which the stage's output buffer has too)
+        blk.dge.states.update({"batches_device": counts[i], "input": x if i == 0 else out, "gate": None,
+                               "size": (H, W), "num_extra_tokens": N - H * W})
+    return out
+
+
 class PatchEmbed(nn.Module):
     """Image (or previous stage's map) to patch embedding: convolution with kernel = stride =
     patch_size, then LayerNorm (``pvt_dge.py:149-179``)."""
@@ -359,9 +397,9 @@ class PyramidVisionTransformer(nn.Module):
                 cls = self.cls_token.detach().reshape(1, C).contiguous()
                 _lib.check(lib.vtp_add_rows(ptr(cls), 1, ptr(pos), 1, 0, ptr(tokens), 1, HW + 1, 0, dtype_code(dtype),
                                             B, C, st))
-            for blk in getattr(self, f"block{i + 1}"):
-                tokens = blk(tokens, H, W)
-                counts.append(blk.dge.states["batches_device"])
+            stage = getattr(self, f"block{i + 1}")
+            tokens = stage_forward(stage, tokens, H, W)
+            counts.extend(blk.dge.states["batches_device"] for blk in stage)
             if self.num_classes == 0:
                 grid_rows = tokens[:, 1:] if last else tokens
                 outputs[f"res{i + 2}"] = grid_rows.reshape(B, H, W, C).permute(0, 3, 1, 2).contiguous()
