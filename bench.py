@@ -409,6 +409,17 @@ def profile_case(which):
         x = torch.randn(256, 257, 384, device=dev).bfloat16()
         for _ in range(3):
             model.blocks[0](x)
+    elif which == "pvt_stage1":         # one stage-1 PVT+DGE block (C=64, 64x64 grid, reduction 8, hidden 512) at batch 32
+        from functools import partial
+        from vtpack_b200.models.dge.pvt_dge import Block
+        torch.manual_seed(7)                # the modules' own random initialisation
+        blk = Block(64, 1, mlp_ratio=8, qkv_bias=True, norm_layer=partial(torch.nn.LayerNorm, eps=1e-6), sr_ratio=8,
+                    split_sizes=[4, 2, 1])
+        blk = blk.eval().to(device=dev, dtype=torch.bfloat16)
+        x = torch.randn(32, 64 * 64, 64, device=dev, generator=torch.Generator(dev).manual_seed(3)).bfloat16()
+        for _ in range(2):
+            blk(x, 64, 64)
+        print("queries per image:", float(blk.dge.states["batches_device"].float().mean()))
     elif which == "train_ops":          # one launch of each training-path / bilinear kernel at model shapes
         from vtpack_b200 import layers
         B, G, C, heads = 256, 16, 384, 6
@@ -750,7 +761,7 @@ def main():
                          "data loader hands over)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-stage-profile", action="store_true")
-    ap.add_argument("--profile", default=None, choices=["linear_kv", "attention", "block", "train_ops"],
+    ap.add_argument("--profile", default=None, choices=["linear_kv", "attention", "block", "train_ops", "pvt_stage1"],
                     help="run a small case of one kernel family (for ncu) and exit")
     ap.add_argument("--layer-sweep", action="store_true",
                     help="time one DGE layer over gate skew against the dense block and exit")
