@@ -59,6 +59,14 @@ def test_null_and_shape_errors(lib):
     assert lib.vtp_index_to_patch(p, 0, splits, 3, 1, 4, 4, 4, 1, p, p, p, None, None) == -2  # 3 does not divide 4
     s = _lib.DgeShape()
     assert lib.vtp_block_workspace_bytes(ctypes.byref(s)) == -1
+    # a stage of blocks in one call: null arrays, no blocks, a workspace that is too small
+    s.dtype, s.B, s.H, s.W, s.num_extra, s.C, s.heads, s.hidden, s.region, s.n_splits = 1, 4, 16, 16, 0, 64, 1, 512, 4, 3
+    s.splits[0], s.splits[1], s.splits[2] = 4, 2, 1
+    w = (_lib.BlockWeights * 2)()
+    assert lib.vtp_dge_blocks_forward(ctypes.byref(s), None, 2, p, p, None, p, 1 << 30, None) == -1
+    assert lib.vtp_dge_blocks_forward(ctypes.byref(s), w, 0, p, p, None, p, 1 << 30, None) == -2
+    assert lib.vtp_dge_blocks_forward(ctypes.byref(s), w, 2, p, p, None, p, 16, None) == -2
+    assert b"workspace" in lib.vtp_last_error_string()
 
 
 def test_workspace_size_formula(lib):
