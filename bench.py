@@ -524,6 +524,49 @@ def layer_sweep(args):
                       "model": "DeiT-S layer, 16x16 grid, 16 regions"}), flush=True)
 
 
+def pvt_model_roofline_ms(B, counts, pk):
+    """Sum over the launches of one PVT+DGE tiny forward (256 px, bf16) of max(FLOPs / sustained tensor peak,
+    algorithmic bytes / copy bandwidth), in ms.  `counts`: per block, the per-image query counts the forward
+    left.  Bytes are each kernel's operands read or written once (the unpool as the reference defines it: token
+    map in and out, packed rows and their pooled copies in); the stage embeddings count their im2col, GEMM,
+    LayerNorm and position-embedding passes."""
+    e = 2.0
+    tf, bw = pk["bf16_tflops_sustained"] * 1e12, pk["hbm_gbs"] * 1e9
+    t = lambda fl, by: max(fl / tf, by / bw)                  # noqa: E731
+    total, blk = 0.0, 0
+    cin, side = 3, 256
+    for C, heads, H, sr, mr, extra, depth, P in ((64, 1, 64, 8, 8, 0, 2, 4), (128, 2, 32, 4, 8, 0, 2, 2),
+                                                  (320, 5, 16, 2, 4, 0, 2, 2), (512, 8, 8, 1, 4, 1, 2, 2)):
+        N = H * H + extra
+        rows, krows = B * N, B * (N if sr == 1 else (H // sr) ** 2)
+        in_bytes = B * cin * side * side * (4.0 if cin == 3 else e)
+        K = cin * P * P
+        total += t(0, in_bytes + B * H * H * K * e)                        # im2col
+        total += t(2.0 * B * H * H * K * C, B * H * H * (K + C) * e)        # embedding GEMM
+        total += 2 * t(0, 2 * rows * C * e)                                # its LayerNorm, position rows
+        for j in range(depth):
+            L = float(counts[blk].float().sum())
+            blk += 1
+            hid = mr * C
+            if j == 0:
+                total += t(0, rows * C * e)                                # gate + token statistics
+            total += t(0, (rows + L) * C * e)                              # pool
+            total += t(2 * L * C * C, 2 * L * C * e)                       # q
+            if sr > 1:
+                total += t(0, 2 * rows * C * e)                            # im2col of the reduction
+                total += t(2.0 * krows * C * sr * sr * C, (rows + krows) * C * e)
+                total += t(0, 2 * krows * C * e)                           # its LayerNorm
+            total += t(2.0 * krows * 2 * C * C, krows * 3 * C * e)          # kv
+            total += t(4.0 * L * (krows / B) * C, (2 * L * C + krows * 2 * C) * e)   # attention
+            total += t(2 * L * C * C, 3 * L * C * e)                       # out projection + residual
+            total += t(2 * L * C * hid, L * (C + hid) * e)                 # fc1
+            total += t(2 * L * hid * C, L * (hid + 2 * C) * e)             # fc2 + residual
+            total += t(0, (2 * rows + 2 * L) * C * e)                      # unpool
+        cin, side = C, H
+    total += t(2.0 * B * 512 * 1000, B * 1000 * 4.0)                       # head
+    return total * 1e3
+
+
 def pvt_sweep(args):
     """The four stage shapes of PVT+DGE (small) at 256 px, one block each, bf16, free-running
     random-init gate: microseconds per block on the GPU, the FLOPs the block does and, beside it,
@@ -601,12 +644,20 @@ def pvt_sweep(args):
     O.pvt_dge_forward(xc, sd, cfg)
     cpu_rate = 4 / (time.perf_counter() - t0)
     assert _lib.device_status() == 0
+    pk, pk_kind = peaks()
+    roof_ms = pvt_model_roofline_ms(B, m.last_counts, pk)
     print(json.dumps({"pvt_sweep": rows, "batch": B, "dtype": "bf16",
                       "pvt_tiny_model": {"ms_per_forward": round(model_ms, 3), "images_per_s": round(B / model_ms * 1e3),
                                          "ms_per_forward_graph": round(graph_ms, 3),
                                          "images_per_s_graph": round(B / graph_ms * 1e3),
                                          "graph_vs_launch_by_launch_max_abs_diff": diff,
-                                         "cpu_oracle_images_per_s": round(cpu_rate, 1)}}), flush=True)
+                                         "cpu_oracle_images_per_s": round(cpu_rate, 1),
+                                         "model_roofline": {"roofline_ms": round(roof_ms, 4), "measured_ms": round(graph_ms, 4),
+                                                            "frac": round(roof_ms / graph_ms, 3), "peaks": pk_kind,
+                                                            "note": "kernel-weighted: sum over the launches of one forward "
+                                                                    "of max(FLOPs / sustained cuBLAS bf16 peak, algorithmic "
+                                                                    "bytes / copy bandwidth) over the graph-replayed forward"}}}),
+          flush=True)
 
 
 def _time_us(fn, iters=20, warm=3):
@@ -747,7 +798,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--model", default="small", choices=["tiny", "small", "base"])
+    ap.add_argument("--model", default="small", choices=["tiny", "small", "base", "pvt_tiny"],
+                    help="DeiT+DGE size; pvt_tiny runs the PVT+DGE sweep and whole-model timing (same as --pvt-sweep)")
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
     ap.add_argument("--img-size", type=int, default=256, help="input side in pixels (512: 32x32 tokens, 64 regions)")
     ap.add_argument("--gate-skew", default="none", choices=["none", "alternate"],
@@ -776,7 +828,7 @@ def main():
     if args.profile:
         profile_case(args.profile)
         return
-    if args.pvt_sweep:
+    if args.pvt_sweep or args.model == "pvt_tiny":
         pvt_sweep(args)
         return
     if args.layer_sweep:
