@@ -291,6 +291,16 @@ int vtp_patch_im2col(const void* images, int image_dtype, int B, int S, int P, i
                      void* stream);
 
 /*
+ * The same im2col for patches that are not multiples of 8 pixels (PVT+DGE's 4 x 4 first stage,
+ * vtpack/models/dge/pvt_dge.py:160-179), with rows `ld_cols` elements apart (a multiple of 8, at least
+ * 3*P*P) and the tail of every row zeroed: 48 columns padded to 64 make the reduction a whole 64-element
+ * block, so the patch-embedding GEMM runs on the tensor-core vtp_linear with K = ld_cols and the conv
+ * weight [C, 3*P*P] padded with zero columns.  No cls row.
+ */
+int vtp_patch_im2col_padded(const void* images, int image_dtype, int B, int S, int P, int dtype, void* cols,
+                            int ld_cols, void* stream);
+
+/*
  * Stride-`ratio` window gather on a token grid: x [B, H*W, C] -> cols [B*(H/ratio)*(W/ratio), ratio*ratio*C],
  * column (dy, dx, c).  With vtp_linear it is a convolution of kernel = stride = ratio whose weight
  * [C_out, C_in, ratio, ratio] was reordered once to [C_out, (dy, dx, c_in)]: the spatial reduction of a

@@ -113,7 +113,9 @@ def test_gate_argmax_ties(vl):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1e-2)])
-@pytest.mark.parametrize("rows,C", [(5, 192), (1000, 384), (33, 768)])
+@pytest.mark.parametrize("rows,C", [(5, 192), (1000, 384), (33, 768),
+                                    # narrow rows (several rows per warp): PVT stages 1 and 2, ragged row counts
+                                    (1, 64), (7, 64), (4099, 64), (1001, 128), (3, 32), (514, 96)])
 def test_layernorm(vl, dtype, tol, rows, C):
     from vtpack_b200.models.dge.deit_dge import _layernorm
     g = torch.Generator().manual_seed(7)
@@ -260,6 +262,33 @@ def test_token_im2col_is_a_strided_convolution(vl, dtype, B, H, W, C, ratio):
     conv = F.conv2d(x.float().cpu().permute(0, 2, 1).reshape(B, C, H, W), w, stride=ratio).flatten(2).transpose(1, 2)
     got = cols.float().cpu() @ w.permute(0, 2, 3, 1).reshape(C, -1).t()
     assert rel_err(got.reshape(conv.shape), conv) < 1e-5
+
+
+@pytest.mark.parametrize("img_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,S,P", [(2, 32, 4), (3, 24, 12)])
+def test_small_patch_im2col_plain_and_padded_rows(vl, dtype, img_dtype, B, S, P):
+    """Patches that are not multiples of 8 pixels (PVT's 4 x 4 first stage): the rows equal F.unfold's columns
+    rounded to the row dtype, bit for bit; with a padded row pitch the first 3*P*P columns are the same and the
+    tail is zero even though the buffer was not."""
+    _lib, _ = vl
+    from vtpack_b200.runtime import dtype_code, ptr, stream_ptr
+    g = torch.Generator().manual_seed(5)
+    img = torch.randn(B, 3, S, S, generator=g).to(img_dtype).to(DEV)
+    KP, G = 3 * P * P, S // P
+    ref = F.unfold(img.float(), kernel_size=P, stride=P).transpose(1, 2).reshape(B * G * G, KP).to(dtype)
+    cols = torch.empty(B * G * G, KP, dtype=dtype, device=DEV)
+    _lib.check(_lib.lib().vtp_patch_im2col(ptr(img), dtype_code(img_dtype), B, S, P, dtype_code(dtype), ptr(cols),
+                                           None, None, 0, None, stream_ptr(img.device)))
+    assert torch.equal(cols, ref)
+    ld = (KP + 63) // 64 * 64 + 8
+    padded = torch.full((B * G * G, ld), 7.0, dtype=dtype, device=DEV)
+    _lib.check(_lib.lib().vtp_patch_im2col_padded(ptr(img), dtype_code(img_dtype), B, S, P, dtype_code(dtype), ptr(padded),
+                                                  ld, stream_ptr(img.device)))
+    assert torch.equal(padded[:, :KP], ref)
+    assert bool((padded[:, KP:] == 0).all())
+    assert _lib.lib().vtp_patch_im2col_padded(ptr(img), dtype_code(img_dtype), B, S, P, dtype_code(dtype), ptr(padded),
+                                              KP - 8, stream_ptr(img.device)) == _lib.ERR_SHAPE
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -22,26 +22,52 @@ __device__ __forceinline__ void load8(const bf16* p, float* f) {
     v.to_float(f);
 }
 
-// Patches narrower than 8 pixels (PVT's first stage: 4 x 4): one thread moves 4 adjacent pixels.
-template <typename I, typename T>
+// Patches narrower than 8 pixels (PVT's first stage: 4 x 4): one thread moves 4 adjacent pixels, one vector
+// load and one vector store.  Rows of `cols` are `ld` elements apart; the thread that moves a patch's first
+// pixels also zeroes the row's tail beyond 3 * P * P (ld > 3 * P * P pads the reduction for the tensor-core GEMM).
+__device__ __forceinline__ void load4(const float* p, float* f) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float* f) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float* f) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    uint2 v;
+    v.x = *reinterpret_cast<const uint32_t*>(&a);
+    v.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+// (IDX: unsigned when every element index fits 32 bits — the index arithmetic is most of this kernel's
+// instructions, and 64-bit divisions cost several times the 32-bit ones — else long long)
+template <typename I, typename T, typename IDX>
 __global__ void __launch_bounds__(256)
-im2col4_kernel(const I* __restrict__ img, long long total4, int S, int P, T* __restrict__ cols) {
+im2col4_kernel(const I* __restrict__ img, long long total4, int S, int P, T* __restrict__ cols, int ld) {
     const int G = S / P;
     const int KP = 3 * P * P;
-    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total4;
-         e += (long long)gridDim.x * blockDim.x) {
-        const long long pix = e * 4;
-        const int ix = (int)(pix % S);
-        const int iy = (int)((pix / S) % S);
-        const int c = (int)((pix / ((long long)S * S)) % 3);
-        const long long b = pix / ((long long)3 * S * S);
+    const IDX uS = (IDX)S, plane = (IDX)S * (IDX)S;
+    for (IDX e = (IDX)blockIdx.x * blockDim.x + threadIdx.x; e < (IDX)total4; e += (IDX)gridDim.x * blockDim.x) {
+        const IDX pix = e * 4;
+        const int ix = (int)(pix % uS);
+        const int iy = (int)((pix / uS) % uS);
+        const int c = (int)((pix / plane) % 3);
+        const long long b = (long long)(pix / (plane * 3));
         float f[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) f[i] = to_f32(img[pix + i]);
+        load4(img + pix, f);
         const int gy = iy / P, py = iy % P, gx = ix / P, px = ix % P;
-        T* dst = cols + ((b * G + gy) * G + gx) * KP + c * P * P + py * P + px;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dst[i] = from_f32<T>(f[i]);
+        T* row = cols + ((b * G + gy) * G + gx) * (long long)ld;
+        store4(row + c * P * P + py * P + px, f);
+        if (c == 0 && py == 0 && px == 0) {
+            const float z[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int t = KP; t < ld; t += 4) store4(row + t, z);
+        }
     }
 }
 
@@ -84,22 +110,22 @@ __global__ void cls_row_kernel(const T* __restrict__ cls, const T* __restrict__ 
 // the sr x sr window of tokens, column (dy, dx, c).  A window row (fixed dy) is sr consecutive
 // tokens = sr*C contiguous elements on both sides; one thread moves 16 bytes.
 // Replaces the permute / reshape in front of attn.sr (vtpack/models/dge/pvt_dge.py:82-83).
-template <typename T>
+template <typename T, typename IDX>
 __global__ void __launch_bounds__(256)
 token_im2col_kernel(const T* __restrict__ x, long long total_vec, int H, int W, int C, int sr, T* __restrict__ cols,
                     const float2* __restrict__ stats, const float* __restrict__ lnw, const float* __restrict__ lnb) {
     // stats != null: the rows gathered are LayerNorm(x), normalised on the way from each token's (mean, rstd)
+    // (IDX: unsigned when the vector count fits 32 bits, see im2col4_kernel)
     constexpr int VN = Vec<T>::N;
     const int run = sr * C / VN;                  // 16-byte vectors per window row
     const int Wo = W / sr, Ho = H / sr;
-    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total_vec;
-         v += (long long)gridDim.x * blockDim.x) {
-        const int i = (int)(v % run);
-        long long r = v / run;                    // (b, oy, ox, dy) with dy fastest
-        const int dy = (int)(r % sr); r /= sr;
-        const int ox = (int)(r % Wo); r /= Wo;
-        const int oy = (int)(r % Ho);
-        const long long b = r / Ho;
+    for (IDX v = (IDX)blockIdx.x * blockDim.x + threadIdx.x; v < (IDX)total_vec; v += (IDX)gridDim.x * blockDim.x) {
+        const int i = (int)(v % (IDX)run);
+        IDX r = v / (IDX)run;                     // (b, oy, ox, dy) with dy fastest
+        const int dy = (int)(r % (IDX)sr); r /= (IDX)sr;
+        const int ox = (int)(r % (IDX)Wo); r /= (IDX)Wo;
+        const int oy = (int)(r % (IDX)Ho);
+        const long long b = (long long)(r / (IDX)Ho);
         const long long tok = (b * H + (long long)oy * sr + dy) * W + (long long)ox * sr;
         Vec<T> t;
         t.load(x + tok * C + (long long)i * VN);
@@ -124,35 +150,39 @@ int token_im2col(const void* x, int dtype, int B, int H, int W, int C, int sr, v
     const long long total = (long long)B * H * W * C / vn;
     if (total == 0) return VTP_OK;
     const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (dtype == VTP_BF16)
-        token_im2col_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, total, H, W, C, sr, (bf16*)cols, stats, lnw, lnb);
-    else
-        token_im2col_kernel<float><<<grid, 256, 0, st>>>((const float*)x, total, H, W, C, sr, (float*)cols, stats, lnw, lnb);
+    const bool small = total < (1ll << 31);
+    if (dtype == VTP_BF16) {
+        if (small) token_im2col_kernel<bf16, unsigned><<<grid, 256, 0, st>>>((const bf16*)x, total, H, W, C, sr, (bf16*)cols, stats, lnw, lnb);
+        else token_im2col_kernel<bf16, long long><<<grid, 256, 0, st>>>((const bf16*)x, total, H, W, C, sr, (bf16*)cols, stats, lnw, lnb);
+    } else {
+        if (small) token_im2col_kernel<float, unsigned><<<grid, 256, 0, st>>>((const float*)x, total, H, W, C, sr, (float*)cols, stats, lnw, lnb);
+        else token_im2col_kernel<float, long long><<<grid, 256, 0, st>>>((const float*)x, total, H, W, C, sr, (float*)cols, stats, lnw, lnb);
+    }
     return check_launch("spatial reduction im2col");
 }
 
 // out[orow(r)] = x[r % x_mod] + addend[r % a_mod + a_off], orow(r) = (r / out_grp) * out_stride + out_off + r % out_grp:
 // the position-embedding add of a token stage, and (x_mod = a_mod = out_grp = 1) the cls rows put in front of it.
-template <typename T>
+template <typename T, typename IDX>
 __global__ void __launch_bounds__(256)
 add_rows_kernel(const T* __restrict__ x, int x_mod, const T* __restrict__ addend, int a_mod, int a_off,
                 T* __restrict__ out, int out_grp, int out_stride, int out_off, long long total_vec, int C) {
+    // (IDX: unsigned when the vector count fits 32 bits, see im2col4_kernel)
     constexpr int VN = Vec<T>::N;
     const int cv = C / VN;
-    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total_vec;
-         v += (long long)gridDim.x * blockDim.x) {
-        const long long r = v / cv;
-        const int i = (int)(v % cv) * VN;
+    for (IDX v = (IDX)blockIdx.x * blockDim.x + threadIdx.x; v < (IDX)total_vec; v += (IDX)gridDim.x * blockDim.x) {
+        const IDX r = v / (IDX)cv;
+        const int i = (int)(v % (IDX)cv) * VN;
         Vec<T> a, p;
         float fa[VN], fp[VN];
-        a.load(x + (r % x_mod) * C + i);
-        p.load(addend + (r % a_mod + a_off) * C + i);
+        a.load(x + (long long)(r % (IDX)x_mod) * C + i);
+        p.load(addend + ((long long)(r % (IDX)a_mod) + a_off) * C + i);
         a.to_float(fa);
         p.to_float(fp);
 #pragma unroll
         for (int k = 0; k < VN; ++k) fa[k] += fp[k];
         a.from_float(fa);
-        a.store(out + ((r / out_grp) * out_stride + out_off + r % out_grp) * C + i);
+        a.store(out + ((long long)(r / (IDX)out_grp) * out_stride + out_off + (long long)(r % (IDX)out_grp)) * C + i);
     }
 }
 
@@ -183,17 +213,36 @@ extern "C" int vtp_add_rows(const void* x, int x_mod, const void* addend, int a_
     if (total == 0) return VTP_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = (int)((total + 255) / 256 < (long long)sm_count() * 16 ? (total + 255) / 256 : (long long)sm_count() * 16);
-    if (dtype == VTP_BF16)
-        add_rows_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, x_mod, (const bf16*)addend, a_mod, a_off, (bf16*)out,
-                                                   out_grp, out_stride, out_off, total, C);
-    else
-        add_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)x, x_mod, (const float*)addend, a_mod, a_off,
-                                                    (float*)out, out_grp, out_stride, out_off, total, C);
+    const bool small = total < (1ll << 31);
+#define VTP_ADD_ROWS(T, IDX)                                                                                  \
+    add_rows_kernel<T, IDX><<<grid, 256, 0, st>>>((const T*)x, x_mod, (const T*)addend, a_mod, a_off, (T*)out, \
+                                                  out_grp, out_stride, out_off, total, C)
+    if (dtype == VTP_BF16) { if (small) VTP_ADD_ROWS(bf16, unsigned); else VTP_ADD_ROWS(bf16, long long); }
+    else { if (small) VTP_ADD_ROWS(float, unsigned); else VTP_ADD_ROWS(float, long long); }
+#undef VTP_ADD_ROWS
     return check_launch("add rows");
 }
 
+static int patch_im2col(const void* images, int image_dtype, int B, int S, int P, int dtype, void* cols, int ld,
+                        const void* cls_token, const void* pos_embed, int C, void* x, void* stream);
+
 extern "C" int vtp_patch_im2col(const void* images, int image_dtype, int B, int S, int P, int dtype, void* cols,
                                 const void* cls_token, const void* pos_embed, int C, void* x, void* stream) {
+    return patch_im2col(images, image_dtype, B, S, P, dtype, cols, 3 * P * P, cls_token, pos_embed, C, x, stream);
+}
+
+extern "C" int vtp_patch_im2col_padded(const void* images, int image_dtype, int B, int S, int P, int dtype, void* cols,
+                                       int ld_cols, void* stream) {
+    VTP_REQUIRE(P > 0 && P % 8 != 0, VTP_ERR_UNSUPPORTED,
+                "im2col (padded rows): for patches that are not multiples of 8 pixels; others need no padding");
+    VTP_REQUIRE(ld_cols >= 3 * P * P && ld_cols % 8 == 0, VTP_ERR_SHAPE,
+                "im2col (padded rows): row pitch %d for %d columns (a multiple of 8, at least the columns)", ld_cols,
+                3 * P * P);
+    return patch_im2col(images, image_dtype, B, S, P, dtype, cols, ld_cols, nullptr, nullptr, 0, nullptr, stream);
+}
+
+static int patch_im2col(const void* images, int image_dtype, int B, int S, int P, int dtype, void* cols, int ld,
+                        const void* cls_token, const void* pos_embed, int C, void* x, void* stream) {
     VTP_REQUIRE(images && cols, VTP_ERR_NULL, "im2col: null pointer");
     VTP_REQUIRE(dtype == VTP_F32 || dtype == VTP_BF16, VTP_ERR_DTYPE, "im2col: dtype %d", dtype);
     VTP_REQUIRE(image_dtype == VTP_F32 || image_dtype == VTP_BF16, VTP_ERR_DTYPE, "im2col: image dtype %d", image_dtype);
@@ -206,14 +255,22 @@ extern "C" int vtp_patch_im2col(const void* images, int image_dtype, int B, int 
         const long long total4 = (long long)B * 3 * S * S / 4;
         const int g4 = (int)((total4 + 255) / 256 < (long long)sm_count() * 16 ? (total4 + 255) / 256
                                                                                 : (long long)sm_count() * 16);
+        // 32-bit indices when the pixel count and the padded output both fit
+        const bool small = (long long)B * 3 * S * S < (1ll << 31) && (long long)B * (S / P) * (S / P) * ld < (1ll << 31);
+#define VTP_IM2COL4(I, T, ARGS)                                                              \
+    do {                                                                                     \
+        if (small) im2col4_kernel<I, T, unsigned><<<g4, 256, 0, st>>> ARGS;                   \
+        else im2col4_kernel<I, T, long long><<<g4, 256, 0, st>>> ARGS;                        \
+    } while (0)
         if (image_dtype == VTP_F32 && dtype == VTP_F32)
-            im2col4_kernel<float, float><<<g4, 256, 0, st>>>((const float*)images, total4, S, P, (float*)cols);
+            VTP_IM2COL4(float, float, ((const float*)images, total4, S, P, (float*)cols, ld));
         else if (image_dtype == VTP_F32)
-            im2col4_kernel<float, bf16><<<g4, 256, 0, st>>>((const float*)images, total4, S, P, (bf16*)cols);
+            VTP_IM2COL4(float, bf16, ((const float*)images, total4, S, P, (bf16*)cols, ld));
         else if (dtype == VTP_F32)
-            im2col4_kernel<bf16, float><<<g4, 256, 0, st>>>((const bf16*)images, total4, S, P, (float*)cols);
+            VTP_IM2COL4(bf16, float, ((const bf16*)images, total4, S, P, (float*)cols, ld));
         else
-            im2col4_kernel<bf16, bf16><<<g4, 256, 0, st>>>((const bf16*)images, total4, S, P, (bf16*)cols);
+            VTP_IM2COL4(bf16, bf16, ((const bf16*)images, total4, S, P, (bf16*)cols, ld));
+#undef VTP_IM2COL4
         return check_launch("im2col");
     }
     const long long total8 = (long long)B * 3 * S * S / 8;

@@ -369,6 +369,64 @@ layernorm_kernel(const T* __restrict__ x, int rows_max, const int32_t* __restric
     }
 }
 
+// Rows of at most 16 chunks of 16 bytes (C <= 128 in bf16, 64 in fp32): G = 8 or 16 lanes share a row and a
+// warp normalises 32 / G rows at a time; with a warp per row three quarters of its lanes would have nothing to
+// load.  Same two-pass arithmetic as ln_row_store.
+template <typename T, int G>
+__global__ void __launch_bounds__(256)
+layernorm_narrow_kernel(const T* __restrict__ x, int rows_max, const int32_t* __restrict__ rows_dev, int C,
+                        long long in_stride, const float* __restrict__ lnw, const float* __restrict__ lnb,
+                        float eps, T* __restrict__ y) {
+    constexpr int VN = Vec<T>::N, RPW = 32 / G;
+    const int lane = threadIdx.x & 31, sub = lane % G, grp = lane / G;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int nchunks = C / VN;
+    const bool has = sub < nchunks;
+    int rows = rows_max;
+    if (rows_dev) rows = min(__ldg(rows_dev), rows_max);
+    float w[VN], bb[VN];
+#pragma unroll
+    for (int i = 0; i < VN; ++i) {
+        w[i] = has ? __ldg(lnw + sub * VN + i) : 0.f;
+        bb[i] = has ? __ldg(lnb + sub * VN + i) : 0.f;
+    }
+    // (every lane of a warp goes round the loop the same number of times: the shuffles name the whole warp)
+    for (int r0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * RPW; r0 < rows; r0 += warps * RPW) {
+        const int r = r0 + grp;
+        const bool live = has && r < rows;
+        float f[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) f[i] = 0.f;
+        if (live) {
+            Vec<T> v;
+            v.load(x + (size_t)r * in_stride + sub * VN);
+            v.to_float(f);
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < VN; ++i) s += f[i];
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float mean = s / (float)C;
+        float v2 = 0.f;
+        if (has) {
+#pragma unroll
+            for (int i = 0; i < VN; ++i) { const float d = f[i] - mean; v2 = fmaf(d, d, v2); }
+        }
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) v2 += __shfl_xor_sync(0xffffffffu, v2, o);
+        const float rstd = rsqrtf(v2 / (float)C + eps);
+        if (live) {
+            float o[VN];
+#pragma unroll
+            for (int i = 0; i < VN; ++i) o[i] = (f[i] - mean) * rstd * w[i] + bb[i];
+            Vec<T> ov;
+            ov.from_float(o);
+            ov.store(y + (size_t)r * C + sub * VN);
+        }
+    }
+}
+
 static int row_grid(int rows) {
     const int per_block = 8;   // warps per 256-thread block
     const int want = ceil_div(rows, per_block);
@@ -440,6 +498,16 @@ template <typename T>
 static int launch_ln(const void* x, int rows_max, const int32_t* rows_dev, int C, long long stride,
                      const float* w, const float* b, float eps, void* y, cudaStream_t st) {
     const int maxch = ceil_div(C / Vec<T>::N, 32);
+    const int nchunks = C / Vec<T>::N;
+    if (nchunks <= 16) {
+        const int rpw = nchunks <= 8 ? 4 : 2;
+        const int g = row_grid(ceil_div(rows_max, rpw));
+        if (nchunks <= 8)
+            layernorm_narrow_kernel<T, 8><<<g, 256, 0, st>>>((const T*)x, rows_max, rows_dev, C, stride, w, b, eps, (T*)y);
+        else
+            layernorm_narrow_kernel<T, 16><<<g, 256, 0, st>>>((const T*)x, rows_max, rows_dev, C, stride, w, b, eps, (T*)y);
+        return check_launch("layernorm");
+    }
     const int grid = row_grid(rows_max);
 #define VTP_LN(M)                                                                                 \
     layernorm_kernel<T, M><<<grid, 256, 0, st>>>((const T*)x, rows_max, rows_dev, C, stride, w, b, \

@@ -371,10 +371,21 @@ class PyramidVisionTransformer(nn.Module):
                 if S % P:
                     raise ValueError(f"input size {S} is not a multiple of the patch size {P}")
                 H = W = S // P
-                cols = torch.empty(B * H * W, 3 * P * P, dtype=dtype, device=x.device)
-                _lib.check(lib.vtp_patch_im2col(ptr(x), dtype_code(x.dtype), B, S, P, dtype_code(dtype), ptr(cols),
-                                                None, None, C, None, st))
-                wm = pe.proj.weight.detach().reshape(C, -1).to(dtype).contiguous()
+                KP = 3 * P * P
+                wm = pe.proj.weight.detach().reshape(C, -1).to(dtype)
+                if dtype == torch.bfloat16 and P % 8 and KP % 64:
+                    # 48 columns: pad the reduction to a whole 64-element block (zero columns in the rows and in
+                    # the weight), which takes the GEMM from the CUDA-core kernel to the tensor-core one
+                    ld = (KP + 63) // 64 * 64
+                    cols = torch.empty(B * H * W, ld, dtype=dtype, device=x.device)
+                    _lib.check(lib.vtp_patch_im2col_padded(ptr(x), dtype_code(x.dtype), B, S, P, dtype_code(dtype),
+                                                           ptr(cols), ld, st))
+                    wm = torch.nn.functional.pad(wm, (0, ld - KP))
+                else:
+                    cols = torch.empty(B * H * W, KP, dtype=dtype, device=x.device)
+                    _lib.check(lib.vtp_patch_im2col(ptr(x), dtype_code(x.dtype), B, S, P, dtype_code(dtype), ptr(cols),
+                                                    None, None, C, None, st))
+                wm = wm.contiguous()
             else:
                 cols = torch.empty(B * (H // P) * (W // P), P * P * tokens.shape[-1], dtype=dtype, device=x.device)
                 _lib.check(lib.vtp_token_im2col(ptr(tokens), dtype_code(dtype), B, H, W, tokens.shape[-1], P, ptr(cols), st))
