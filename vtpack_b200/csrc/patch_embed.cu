@@ -71,6 +71,39 @@ im2col4_kernel(const I* __restrict__ img, long long total4, int S, int P, T* __r
     }
 }
 
+// 4 x 4 patches, one CTA per (image, patch row): the twelve image rows (3 channels x 4) of the patch row are
+// read as whole rows, scattered into a shared-memory copy of the S/4 output rows, and those leave as one
+// contiguous range of 16-byte stores (the direct kernel above writes 8-byte pieces 96 or 128 bytes apart).
+template <typename I, typename T>
+__global__ void __launch_bounds__(256)
+im2col_p4_kernel(const I* __restrict__ img, int S, T* __restrict__ cols, int ld) {
+    constexpr int P = 4, KP = 48, VT = 16 / (int)sizeof(T);     // VT: elements of a 16-byte store
+    extern __shared__ __align__(16) unsigned char tile_raw[];
+    T* tile = reinterpret_cast<T*>(tile_raw);
+    const int G = S / P, pitch = ld + VT;                        // one store of padding per row spreads the banks
+    const int b = blockIdx.x / G, gy = blockIdx.x % G;
+    const int per_row = S / 4;
+    // tails beyond the 48 columns
+    for (int i = threadIdx.x; i < G * ((ld - KP) / 4); i += blockDim.x) {
+        const float z[4] = {0.f, 0.f, 0.f, 0.f};
+        store4(tile + (i / ((ld - KP) / 4)) * pitch + KP + (i % ((ld - KP) / 4)) * 4, z);
+    }
+    for (int v = threadIdx.x; v < 12 * per_row; v += blockDim.x) {
+        const int r = v / per_row, gx = v % per_row;             // r = c * 4 + py; four pixels = the patch's row
+        const int c = r >> 2, py = r & 3;
+        float f[4];
+        load4(img + (((size_t)b * 3 + c) * S + (size_t)gy * P + py) * S + (size_t)gx * 4, f);
+        store4(tile + gx * pitch + r * 4, f);
+    }
+    __syncthreads();
+    const int vec_per_row = ld / VT;
+    T* out = cols + ((size_t)b * G + gy) * G * (size_t)ld;
+    for (int v = threadIdx.x; v < G * vec_per_row; v += blockDim.x) {
+        const int row = v / vec_per_row, i = v % vec_per_row;
+        *reinterpret_cast<uint4*>(out + (size_t)row * ld + i * VT) = *reinterpret_cast<const uint4*>(tile + row * pitch + i * VT);
+    }
+}
+
 template <typename I, typename T>
 __global__ void __launch_bounds__(256)
 im2col_kernel(const I* __restrict__ img, long long total8, int S, int P, T* __restrict__ cols) {
@@ -133,10 +166,17 @@ token_im2col_kernel(const T* __restrict__ x, long long total_vec, int H, int W, 
             const int e0 = i * VN;                        // element of the window row: token e0 / C, channel e0 % C
             const float2 ms = stats[tok + e0 / C];
             const int ch = e0 % C;
-            float f[VN];
+            float f[VN], gw[VN], gb[VN];
             t.to_float(f);
 #pragma unroll
-            for (int k = 0; k < VN; ++k) f[k] = (f[k] - ms.x) * ms.y * __ldg(lnw + ch + k) + __ldg(lnb + ch + k);
+            for (int k4 = 0; k4 < VN / 4; ++k4) {          // ch is a multiple of VN: 16-byte loads of the LayerNorm vectors
+                const float4 w4 = __ldg(reinterpret_cast<const float4*>(lnw + ch) + k4);
+                const float4 b4 = __ldg(reinterpret_cast<const float4*>(lnb + ch) + k4);
+                gw[4 * k4] = w4.x; gw[4 * k4 + 1] = w4.y; gw[4 * k4 + 2] = w4.z; gw[4 * k4 + 3] = w4.w;
+                gb[4 * k4] = b4.x; gb[4 * k4 + 1] = b4.y; gb[4 * k4 + 2] = b4.z; gb[4 * k4 + 3] = b4.w;
+            }
+#pragma unroll
+            for (int k = 0; k < VN; ++k) f[k] = (f[k] - ms.x) * ms.y * gw[k] + gb[k];
             t.from_float(f);
         }
         t.store(cols + ((((b * Ho + oy) * Wo + ox) * sr + dy) * (long long)run + i) * VN);
@@ -255,6 +295,19 @@ static int patch_im2col(const void* images, int image_dtype, int B, int S, int P
         const long long total4 = (long long)B * 3 * S * S / 4;
         const int g4 = (int)((total4 + 255) / 256 < (long long)sm_count() * 16 ? (total4 + 255) / 256
                                                                                 : (long long)sm_count() * 16);
+        const size_t p4_smem = (size_t)(S / 4) * (ld + 16 / elem_size(dtype)) * elem_size(dtype);
+        if (P == 4 && ld % (16 / (int)elem_size(dtype)) == 0 && p4_smem <= 48 * 1024) {
+            const int grid = B * (S / 4);
+            if (image_dtype == VTP_F32 && dtype == VTP_F32)
+                im2col_p4_kernel<float, float><<<grid, 256, p4_smem, st>>>((const float*)images, S, (float*)cols, ld);
+            else if (image_dtype == VTP_F32)
+                im2col_p4_kernel<float, bf16><<<grid, 256, p4_smem, st>>>((const float*)images, S, (bf16*)cols, ld);
+            else if (dtype == VTP_F32)
+                im2col_p4_kernel<bf16, float><<<grid, 256, p4_smem, st>>>((const bf16*)images, S, (float*)cols, ld);
+            else
+                im2col_p4_kernel<bf16, bf16><<<grid, 256, p4_smem, st>>>((const bf16*)images, S, (bf16*)cols, ld);
+            return check_launch("im2col");
+        }
         // 32-bit indices when the pixel count and the padded output both fit
         const bool small = (long long)B * 3 * S * S < (1ll << 31) && (long long)B * (S / P) * (S / P) * ld < (1ll << 31);
 #define VTP_IM2COL4(I, T, ARGS)                                                              \
