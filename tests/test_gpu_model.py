@@ -384,6 +384,31 @@ def test_pvt_model(golden_dir, dtype):
         assert float((logits - ref).abs().max()) < 2e-2
 
 
+def test_pvt_model_follows_parameter_updates():
+    """The eval forward keeps tensors derived from parameters (GEMM-layout weights, fp32 vectors, position rows);
+    after parameters change in place — an optimizer step, load_state_dict — the next forward must use the new
+    values: compared with a second model, loaded with the changed parameters, that has never run before."""
+    from vtpack_b200.models.dge.pvt_dge import pvt_dge_s124_tiny_256
+    sd = O.make_pvt_state_dict(O.PVT_CONFIGS["tiny"], seed=0)
+    m = pvt_dge_s124_tiny_256()
+    m.load_state_dict(sd, strict=True)
+    m = m.eval().to(device=DEV, dtype=torch.bfloat16)
+    img = O.make_images(2, 256, seed=8).to(DEV)
+    first = m(img).clone()
+    with torch.no_grad():
+        m.patch_embed1.proj.weight.mul_(1.5)
+        m.patch_embed2.norm.bias.add_(0.25)
+        m.pos_embed3.add_(0.5)
+        m.cls_token.add_(1.0)
+        m.head.bias.add_(2.0)
+    fresh = pvt_dge_s124_tiny_256()
+    fresh.load_state_dict({k: v.float().cpu() for k, v in m.state_dict().items()}, strict=True)
+    fresh = fresh.eval().to(device=DEV, dtype=torch.bfloat16)
+    got, ref = m(img), fresh(img)
+    assert torch.equal(got, ref)
+    assert float((got - first).abs().max()) > 0.5
+
+
 def test_pvt_model_other_input_size_and_pyramid(golden_dir):
     """PVT+DGE tiny in eval mode on 384 px images (position embeddings resized bilinearly) and its
     feature-pyramid variant (num_classes = 0), fp32, against the reference's own outputs."""

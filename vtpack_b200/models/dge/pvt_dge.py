@@ -219,10 +219,10 @@ def _matmul_rows(cols, weight, bias, flags=0, out_dtype=None):
     return y
 
 
-def _norm_rows(x, rows, C, row_stride, ln, eps=None):
+def _norm_rows(x, rows, C, row_stride, ln, eps=None, wb=None):
     y = torch.empty(rows, C, dtype=x.dtype, device=x.device)
     # both fp32 copies must be alive together: a temporary freed between the two would hand its memory to the other
-    w, b = ln.weight.detach().float().contiguous(), ln.bias.detach().float().contiguous()
+    w, b = wb if wb is not None else (ln.weight.detach().float().contiguous(), ln.bias.detach().float().contiguous())
     _lib.check(_lib.lib().vtp_layernorm(ptr(x), dtype_code(x.dtype), rows, None, C, row_stride, ptr(w), ptr(b),
                                         float(ln.eps if eps is None else eps), ptr(y), stream_ptr(x.device)))
     return y
@@ -276,6 +276,19 @@ class PyramidVisionTransformer(nn.Module):
             elif isinstance(m, DynamicGrainedEncoder):
                 m.router.init_parameters()
         self.last_counts = None
+
+    def _const(self, name, sources, make, extra=()):
+        """A tensor derived from parameters only (a weight matrix in GEMM layout and dtype, fp32 copies of bias and
+        LayerNorm vectors, the resized position rows): made once and kept until one of ``sources`` changes, so an
+        eval forward launches no conversion copies of its own."""
+        cache = self.__dict__.setdefault("_consts", {})
+        key = tuple((p.data_ptr(), p._version, p.dtype) for p in sources) + tuple(extra)
+        hit = cache.get(name)
+        if hit is None or hit[0] != key:
+            with torch.no_grad():
+                hit = (key, make())
+            cache[name] = hit
+        return hit[1]
 
     def forward_graph(self, x):
         """Eval forward through a CUDA graph captured for this input buffer (its contents may change between
@@ -372,40 +385,46 @@ class PyramidVisionTransformer(nn.Module):
                     raise ValueError(f"input size {S} is not a multiple of the patch size {P}")
                 H = W = S // P
                 KP = 3 * P * P
-                wm = pe.proj.weight.detach().reshape(C, -1).to(dtype)
-                if dtype == torch.bfloat16 and P % 8 and KP % 64:
+                padded = dtype == torch.bfloat16 and P % 8 != 0 and KP % 64 != 0
+                ld = (KP + 63) // 64 * 64 if padded else KP
+                wm = self._const(f"wm{i}", (pe.proj.weight,), lambda: torch.nn.functional.pad(
+                    pe.proj.weight.detach().reshape(C, -1).to(dtype), (0, ld - KP)).contiguous(), (dtype, ld))
+                if padded:
                     # 48 columns: pad the reduction to a whole 64-element block (zero columns in the rows and in
                     # the weight), which takes the GEMM from the CUDA-core kernel to the tensor-core one
-                    ld = (KP + 63) // 64 * 64
                     cols = torch.empty(B * H * W, ld, dtype=dtype, device=x.device)
                     _lib.check(lib.vtp_patch_im2col_padded(ptr(x), dtype_code(x.dtype), B, S, P, dtype_code(dtype),
                                                            ptr(cols), ld, st))
-                    wm = torch.nn.functional.pad(wm, (0, ld - KP))
                 else:
                     cols = torch.empty(B * H * W, KP, dtype=dtype, device=x.device)
                     _lib.check(lib.vtp_patch_im2col(ptr(x), dtype_code(x.dtype), B, S, P, dtype_code(dtype), ptr(cols),
                                                     None, None, C, None, st))
-                wm = wm.contiguous()
             else:
                 cols = torch.empty(B * (H // P) * (W // P), P * P * tokens.shape[-1], dtype=dtype, device=x.device)
                 _lib.check(lib.vtp_token_im2col(ptr(tokens), dtype_code(dtype), B, H, W, tokens.shape[-1], P, ptr(cols), st))
                 H, W = H // P, W // P
-                wm = pe.proj.weight.detach().permute(0, 2, 3, 1).reshape(C, -1).to(dtype).contiguous()
-            y = _matmul_rows(cols, wm, pe.proj.bias)
-            y = _norm_rows(y, y.shape[0], C, C, pe.norm)
+                wm = self._const(f"wm{i}", (pe.proj.weight,), lambda: pe.proj.weight.detach().permute(0, 2, 3, 1)
+                                 .reshape(C, -1).to(dtype).contiguous(), (dtype,))
+            bias = self._const(f"eb{i}", (pe.proj.bias,), lambda: pe.proj.bias.detach().float().contiguous())
+            wb = self._const(f"en{i}", (pe.norm.weight, pe.norm.bias), lambda: (
+                pe.norm.weight.detach().float().contiguous(), pe.norm.bias.detach().float().contiguous()))
+            y = _matmul_rows(cols, wm, bias)
+            y = _norm_rows(y, y.shape[0], C, C, pe.norm, wb=wb)
             HW = H * W
             last = i == self.num_stages - 1
             # the stage's position rows ([cls row;] grid rows), resized when the grid is not the trained one
-            if last:
-                pos = torch.cat((pos_full[:, 0:1], self._stage_pos_embed(pos_full[:, 1:], pe, H, W)), dim=1)
-            else:
-                pos = self._stage_pos_embed(pos_full, pe, H, W)
-            pos = pos[0].to(dtype).contiguous()
+            def make_pos(pos_full=pos_full, pe=pe, H=H, W=W, last=last):
+                if last:
+                    pos = torch.cat((pos_full[:, 0:1], self._stage_pos_embed(pos_full[:, 1:], pe, H, W)), dim=1)
+                else:
+                    pos = self._stage_pos_embed(pos_full, pe, H, W)
+                return pos[0].to(dtype).contiguous()
+            pos = self._const(f"pos{i}", (getattr(self, f"pos_embed{i + 1}"),), make_pos, (dtype, H, W))
             tokens = torch.empty(B, HW + (1 if last else 0), C, dtype=dtype, device=x.device)
             _lib.check(lib.vtp_add_rows(ptr(y), B * HW, ptr(pos), HW, 1 if last else 0, ptr(tokens), HW,
                                         HW + (1 if last else 0), 1 if last else 0, dtype_code(dtype), B * HW, C, st))
             if last:
-                cls = self.cls_token.detach().reshape(1, C).contiguous()
+                cls = self._const("cls", (self.cls_token,), lambda: self.cls_token.detach().reshape(1, C).contiguous())
                 _lib.check(lib.vtp_add_rows(ptr(cls), 1, ptr(pos), 1, 0, ptr(tokens), 1, HW + 1, 0, dtype_code(dtype),
                                             B, C, st))
             stage = getattr(self, f"block{i + 1}")
@@ -419,9 +438,12 @@ class PyramidVisionTransformer(nn.Module):
             return outputs
         N = tokens.shape[1]
         C = tokens.shape[2]
-        cls_n = _norm_rows(tokens, B, C, N * C, self.norm)
-        logits = _matmul_rows(cls_n, self.head.weight.detach().to(dtype).contiguous(), self.head.bias,
-                              flags=_lib.FLAG_OUT_F32, out_dtype=torch.float32)
+        wb = self._const("norm", (self.norm.weight, self.norm.bias), lambda: (
+            self.norm.weight.detach().float().contiguous(), self.norm.bias.detach().float().contiguous()))
+        cls_n = _norm_rows(tokens, B, C, N * C, self.norm, wb=wb)
+        head_w = self._const("head_w", (self.head.weight,), lambda: self.head.weight.detach().to(dtype).contiguous(), (dtype,))
+        head_b = self._const("head_b", (self.head.bias,), lambda: self.head.bias.detach().float().contiguous())
+        logits = _matmul_rows(cls_n, head_w, head_b, flags=_lib.FLAG_OUT_F32, out_dtype=torch.float32)
         self.last_counts = counts
         return logits
 
