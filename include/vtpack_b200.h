@@ -236,6 +236,17 @@ int vtp_layernorm(const void* x, int dtype, int rows_max, const int32_t* rows_de
                   void* stream);
 
 /*
+ * LayerNorm and a row-wise add in one pass: out[orow(r)] = LN(x[r]) + addend[r % a_mod + a_off] with
+ * orow(r) = (r / out_grp) * out_stride + out_off + r % out_grp, for r < rows (the row maps are those of
+ * vtp_add_rows).  One rounding of the sum instead of two.  Replaces a stage embedding's norm followed by
+ * the position-embedding add, written behind the cls slot in the last stage
+ * (vtpack/models/dge/pvt_dge.py:177, 307-316).
+ */
+int vtp_layernorm_add_rows(const void* x, int dtype, int rows, int C, long long in_row_stride, const float* w,
+                           const float* b, float eps, const void* addend, int a_mod, int a_off, void* out,
+                           int out_grp, int out_stride, int out_off, void* stream);
+
+/*
  * y[m, n] = act(sum_k a[m,k] * w[n,k] + bias[n]) + residual[m,n]
  * a [M,K] (row stride lda elements), w [N,K] dense, bias fp32 [N] or null,
  * residual [M,N] (row stride ldr) or null, y [M,N] (row stride ldy).

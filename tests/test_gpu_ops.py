@@ -291,6 +291,26 @@ def test_small_patch_im2col_plain_and_padded_rows(vl, dtype, img_dtype, B, S, P)
                                               KP - 8, stream_ptr(img.device)) == _lib.ERR_SHAPE
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("C", [64, 128, 320, 512])
+def test_layernorm_and_position_rows_in_one_pass(vl, dtype, tol, C):
+    """vtp_layernorm_add_rows as a stage embedding uses it: LN(y) + position rows, written behind a cls slot;
+    against F.layer_norm + the add in fp32.  The cls slots stay untouched."""
+    _lib, _ = vl
+    from vtpack_b200.runtime import dtype_code, ptr, stream_ptr
+    B, HW = 3, 37
+    g = torch.Generator().manual_seed(3)
+    y = (torch.randn(B * HW, C, generator=g) * 2 + 0.5).to(dtype).to(DEV)
+    pos = torch.randn(HW + 1, C, generator=g).to(dtype).to(DEV)
+    w, b = torch.randn(C, generator=g).to(DEV), torch.randn(C, generator=g).to(DEV)
+    out = torch.full((B, HW + 1, C), 9.0, dtype=dtype, device=DEV)
+    _lib.check(_lib.lib().vtp_layernorm_add_rows(ptr(y), dtype_code(dtype), B * HW, C, C, ptr(w), ptr(b), 1e-6, ptr(pos),
+                                                 HW, 1, ptr(out), HW, HW + 1, 1, stream_ptr(y.device)))
+    ref = F.layer_norm(y.float(), (C,), w, b, 1e-6).reshape(B, HW, C) + pos[1:].float()
+    assert rel_err(out[:, 1:].float(), ref) < tol
+    assert bool((out[:, 0] == 9.0).all())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_add_rows_position_embedding_and_cls_rows(vl, dtype):
     """vtp_add_rows as the model uses it: tokens + position embedding written behind a cls slot, then

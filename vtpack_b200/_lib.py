@@ -91,6 +91,8 @@ PROTOTYPES = {
                                      c_int, c_float, c_uint, c_void_p]),
     "vtp_patch_im2col": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                  c_int, c_void_p, c_void_p]),
+    "vtp_layernorm_add_rows": (c_int, [c_void_p, c_int, c_int, c_int, c_ll, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                                       c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "vtp_patch_im2col_padded": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "vtp_block_workspace_bytes": (c_ll, [C.POINTER(DgeShape)]),
     "vtp_dge_block_forward": (c_int, [C.POINTER(DgeShape), C.POINTER(BlockWeights), c_void_p, c_void_p,

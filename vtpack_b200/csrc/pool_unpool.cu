@@ -39,7 +39,7 @@ template <typename T, int MAXCH>
 __device__ __forceinline__ void ln_row_store(const float (&f)[MAXCH][Vec<T>::N], int lane,
                                              int nchunks, int C, const float (&w)[MAXCH][Vec<T>::N],
                                              const float (&bb)[MAXCH][Vec<T>::N], float eps,
-                                             T* __restrict__ dst) {
+                                             T* __restrict__ dst, const T* __restrict__ add_row = nullptr) {
     constexpr int VN = Vec<T>::N;
     float s = 0.f;
 #pragma unroll
@@ -62,6 +62,14 @@ __device__ __forceinline__ void ln_row_store(const float (&f)[MAXCH][Vec<T>::N],
             float o[VN];
 #pragma unroll
             for (int i = 0; i < VN; ++i) o[i] = (f[ch][i] - mean) * rstd * w[ch][i] + bb[ch][i];
+            if (add_row) {
+                Vec<T> av;
+                float af[VN];
+                av.load(add_row + chunk * VN);
+                av.to_float(af);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) o[i] += af[i];
+            }
             Vec<T> ov;
             ov.from_float(o);
             ov.store(dst + chunk * VN);
@@ -337,11 +345,19 @@ static int elem_grid(long long elems) {
 }
 
 // -------------------------------------------------------------------------- layernorm
+// Optional second half of a LayerNorm launch: y[orow(r)] = LN(x[r]) + addend[r % a_mod + a_off] with
+// orow(r) = (r / out_grp) * out_stride + out_off + r % out_grp (a stage's position-embedding add, written
+// behind a cls slot when there is one).  addend == null: dense output rows, nothing added.
+struct RowAdd {
+    const void* addend = nullptr;
+    int a_mod = 1, a_off = 0, out_grp = 1, out_stride = 1, out_off = 0;
+};
+
 template <typename T, int MAXCH>
 __global__ void __launch_bounds__(256)
 layernorm_kernel(const T* __restrict__ x, int rows_max, const int32_t* __restrict__ rows_dev, int C,
                  long long in_stride, const float* __restrict__ lnw, const float* __restrict__ lnb,
-                 float eps, T* __restrict__ y) {
+                 float eps, T* __restrict__ y, RowAdd add) {
     constexpr int VN = Vec<T>::N;
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -365,7 +381,13 @@ layernorm_kernel(const T* __restrict__ x, int rows_max, const int32_t* __restric
                 for (int i = 0; i < VN; ++i) f[ch][i] = 0.f;
             }
         }
-        ln_row_store<T, MAXCH>(f, lane, nchunks, C, w, bb, eps, y + (size_t)r * C);
+        if (add.addend) {
+            const size_t orow = (size_t)(r / add.out_grp) * add.out_stride + add.out_off + r % add.out_grp;
+            ln_row_store<T, MAXCH>(f, lane, nchunks, C, w, bb, eps, y + orow * C,
+                                   static_cast<const T*>(add.addend) + ((size_t)(r % add.a_mod) + add.a_off) * C);
+        } else {
+            ln_row_store<T, MAXCH>(f, lane, nchunks, C, w, bb, eps, y + (size_t)r * C);
+        }
     }
 }
 
@@ -376,7 +398,7 @@ template <typename T, int G>
 __global__ void __launch_bounds__(256)
 layernorm_narrow_kernel(const T* __restrict__ x, int rows_max, const int32_t* __restrict__ rows_dev, int C,
                         long long in_stride, const float* __restrict__ lnw, const float* __restrict__ lnb,
-                        float eps, T* __restrict__ y) {
+                        float eps, T* __restrict__ y, RowAdd add) {
     constexpr int VN = Vec<T>::N, RPW = 32 / G;
     const int lane = threadIdx.x & 31, sub = lane % G, grp = lane / G;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -420,9 +442,19 @@ layernorm_narrow_kernel(const T* __restrict__ x, int rows_max, const int32_t* __
             float o[VN];
 #pragma unroll
             for (int i = 0; i < VN; ++i) o[i] = (f[i] - mean) * rstd * w[i] + bb[i];
+            size_t orow = (size_t)r;
+            if (add.addend) {
+                Vec<T> av;
+                float af[VN];
+                av.load(static_cast<const T*>(add.addend) + ((size_t)(r % add.a_mod) + add.a_off) * C + sub * VN);
+                av.to_float(af);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) o[i] += af[i];
+                orow = (size_t)(r / add.out_grp) * add.out_stride + add.out_off + r % add.out_grp;
+            }
             Vec<T> ov;
             ov.from_float(o);
-            ov.store(y + (size_t)r * C + sub * VN);
+            ov.store(y + orow * C + sub * VN);
         }
     }
 }
@@ -496,22 +528,22 @@ static int launch_unpool(const void* q, const void* comp, int B, int N, int C, i
 
 template <typename T>
 static int launch_ln(const void* x, int rows_max, const int32_t* rows_dev, int C, long long stride,
-                     const float* w, const float* b, float eps, void* y, cudaStream_t st) {
+                     const float* w, const float* b, float eps, void* y, cudaStream_t st, const RowAdd& add = RowAdd()) {
     const int maxch = ceil_div(C / Vec<T>::N, 32);
     const int nchunks = C / Vec<T>::N;
     if (nchunks <= 16) {
         const int rpw = nchunks <= 8 ? 4 : 2;
         const int g = row_grid(ceil_div(rows_max, rpw));
         if (nchunks <= 8)
-            layernorm_narrow_kernel<T, 8><<<g, 256, 0, st>>>((const T*)x, rows_max, rows_dev, C, stride, w, b, eps, (T*)y);
+            layernorm_narrow_kernel<T, 8><<<g, 256, 0, st>>>((const T*)x, rows_max, rows_dev, C, stride, w, b, eps, (T*)y, add);
         else
-            layernorm_narrow_kernel<T, 16><<<g, 256, 0, st>>>((const T*)x, rows_max, rows_dev, C, stride, w, b, eps, (T*)y);
+            layernorm_narrow_kernel<T, 16><<<g, 256, 0, st>>>((const T*)x, rows_max, rows_dev, C, stride, w, b, eps, (T*)y, add);
         return check_launch("layernorm");
     }
     const int grid = row_grid(rows_max);
 #define VTP_LN(M)                                                                                 \
     layernorm_kernel<T, M><<<grid, 256, 0, st>>>((const T*)x, rows_max, rows_dev, C, stride, w, b, \
-                                                 eps, (T*)y)
+                                                 eps, (T*)y, add)
     if (maxch <= 1) VTP_LN(1);
     else if (maxch == 2) VTP_LN(2);
     else if (maxch == 3) VTP_LN(3);
@@ -654,6 +686,26 @@ extern "C" int vtp_unpool_grad_regions(const void* grad_out, int dtype, int B, i
     a.sum_only = true;
     a.g.l_max = n_patches;       // regions whose rows would not fit grad_q are skipped and flagged
     return region_pool(a, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int vtp_layernorm_add_rows(const void* x, int dtype, int rows, int C, long long in_row_stride, const float* w,
+                                      const float* b, float eps, const void* addend, int a_mod, int a_off, void* out,
+                                      int out_grp, int out_stride, int out_off, void* stream) {
+    VTP_REQUIRE(x && w && b && addend && out, VTP_ERR_NULL, "layernorm + add rows: null pointer");
+    VTP_REQUIRE(rows >= 0 && in_row_stride >= C && a_mod > 0 && a_off >= 0 && out_grp > 0 && out_stride >= out_grp &&
+                    out_off >= 0,
+                VTP_ERR_SHAPE, "layernorm + add rows: bad shape");
+    if (int rc = check_rows("layernorm + add rows", dtype, C, x, out)) return rc;
+    VTP_REQUIRE(aligned16(addend), VTP_ERR_ALIGN, "layernorm + add rows: unaligned pointer");
+    VTP_REQUIRE((in_row_stride * (long long)elem_size(dtype)) % 16 == 0, VTP_ERR_ALIGN,
+                "layernorm + add rows: row stride not 16-byte aligned");
+    if (rows == 0) return VTP_OK;
+    RowAdd add;
+    add.addend = addend; add.a_mod = a_mod; add.a_off = a_off; add.out_grp = out_grp; add.out_stride = out_stride;
+    add.out_off = out_off;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == VTP_F32) return launch_ln<float>(x, rows, nullptr, C, in_row_stride, w, b, eps, out, st, add);
+    return launch_ln<bf16>(x, rows, nullptr, C, in_row_stride, w, b, eps, out, st, add);
 }
 
 extern "C" int vtp_layernorm(const void* x, int dtype, int rows_max, const int32_t* rows_dev, int C,

@@ -409,7 +409,6 @@ class PyramidVisionTransformer(nn.Module):
             wb = self._const(f"en{i}", (pe.norm.weight, pe.norm.bias), lambda: (
                 pe.norm.weight.detach().float().contiguous(), pe.norm.bias.detach().float().contiguous()))
             y = _matmul_rows(cols, wm, bias)
-            y = _norm_rows(y, y.shape[0], C, C, pe.norm, wb=wb)
             HW = H * W
             last = i == self.num_stages - 1
             # the stage's position rows ([cls row;] grid rows), resized when the grid is not the trained one
@@ -421,8 +420,10 @@ class PyramidVisionTransformer(nn.Module):
                 return pos[0].to(dtype).contiguous()
             pos = self._const(f"pos{i}", (getattr(self, f"pos_embed{i + 1}"),), make_pos, (dtype, H, W))
             tokens = torch.empty(B, HW + (1 if last else 0), C, dtype=dtype, device=x.device)
-            _lib.check(lib.vtp_add_rows(ptr(y), B * HW, ptr(pos), HW, 1 if last else 0, ptr(tokens), HW,
-                                        HW + (1 if last else 0), 1 if last else 0, dtype_code(dtype), B * HW, C, st))
+            # tokens = norm(proj(x)) + pos_embed in one pass (written behind the cls slot in the last stage)
+            _lib.check(lib.vtp_layernorm_add_rows(ptr(y), dtype_code(dtype), B * HW, C, C, ptr(wb[0]), ptr(wb[1]),
+                                                  float(pe.norm.eps), ptr(pos), HW, 1 if last else 0, ptr(tokens), HW,
+                                                  HW + (1 if last else 0), 1 if last else 0, st))
             if last:
                 cls = self._const("cls", (self.cls_token,), lambda: self.cls_token.detach().reshape(1, C).contiguous())
                 _lib.check(lib.vtp_add_rows(ptr(cls), 1, ptr(pos), 1, 0, ptr(tokens), 1, HW + 1, 0, dtype_code(dtype),
