@@ -420,6 +420,14 @@ def profile_case(which):
         for _ in range(2):
             blk(x, 64, 64)
         print("queries per image:", float(blk.dge.states["batches_device"].float().mean()))
+    elif which == "pvt_model":          # three launch-by-launch eval forwards of PVT+DGE tiny at batch 256 (bf16)
+        from vtpack_b200.models.dge.pvt_dge import pvt_dge_s124_tiny_256
+        torch.manual_seed(0)                # the modules' own random initialisation
+        m = pvt_dge_s124_tiny_256().eval().to(device=dev, dtype=torch.bfloat16)
+        img = torch.randn(256, 3, 256, 256, device=dev, generator=torch.Generator(dev).manual_seed(4))
+        for _ in range(3):
+            m(img)
+        print("queries per image and block:", [round(float(c.float().mean()), 1) for c in m.last_counts])
     elif which == "train_ops":          # one launch of each training-path / bilinear kernel at model shapes
         from vtpack_b200 import layers
         B, G, C, heads = 256, 16, 384, 6
@@ -813,7 +821,7 @@ def main():
                          "data loader hands over)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-stage-profile", action="store_true")
-    ap.add_argument("--profile", default=None, choices=["linear_kv", "attention", "block", "train_ops", "pvt_stage1"],
+    ap.add_argument("--profile", default=None, choices=["linear_kv", "attention", "block", "train_ops", "pvt_stage1", "pvt_model"],
                     help="run a small case of one kernel family (for ncu) and exit")
     ap.add_argument("--layer-sweep", action="store_true",
                     help="time one DGE layer over gate skew against the dense block and exit")
