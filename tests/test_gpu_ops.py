@@ -266,7 +266,7 @@ def test_token_im2col_is_a_strided_convolution(vl, dtype, B, H, W, C, ratio):
 
 @pytest.mark.parametrize("img_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("B,S,P", [(2, 32, 4), (3, 24, 12)])
+@pytest.mark.parametrize("B,S,P", [(2, 32, 4), (3, 24, 12), (1, 36, 4), (2, 256, 4)])
 def test_small_patch_im2col_plain_and_padded_rows(vl, dtype, img_dtype, B, S, P):
     """Patches that are not multiples of 8 pixels (PVT's 4 x 4 first stage): the rows equal F.unfold's columns
     rounded to the row dtype, bit for bit; with a padded row pitch the first 3*P*P columns are the same and the
