@@ -180,6 +180,9 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     // convolution normalises them on the way from the token statistics.  Without a reduction kv folds norm1 too.
     const bool fold_q = block_folds(s, w);
     const bool fold = fold_q && !reduce;
+    // norm2 into fc1 only where the reduction is long enough to hide it: with K <= 128 the Linear is bound by its
+    // epilogue, the fold adds a quarter to that, and the narrow-row LayerNorm pass costs less than it adds
+    const bool fold_fc1 = fold_q && s.C > 128;
     const int par = chain.parity & 1;
     int32_t* idx = b.idx[par];
     int32_t* counts = b.counts[par];
@@ -280,20 +283,20 @@ static int block_forward(const vtp_dge_shape& s, const vtp_block_weights& w, con
     LinearArgs lp;   // q1 = comp + attn_out Wp^T + b   (and, when folding, the row sums LN2 needs)
     lp.a = b.ao; lp.lda = C; lp.w = w.proj_w; lp.bias = w.proj_b; lp.res = b.comp; lp.ldr = C; lp.y = b.q1;
     lp.ldy = C; lp.dtype = s.dtype; lp.m_max = rows; lp.m_dev = L_dev; lp.N = C; lp.K = C; lp.flags = kflag;
-    if (fold_q) lp.emit_stats = b.stats_acc;
+    if (fold_fc1) lp.emit_stats = b.stats_acc;
     if ((rc = linear(lp, st)) || (rc = marks.mark(7))) return rc;
 
-    if (!fold_q) {
+    if (!fold_fc1) {
         rc = vtp_layernorm(b.q1, s.dtype, rows, L_dev, C, C, w.norm2_w, w.norm2_b, s.eps, b.qn, st);
         if (rc) return rc;
     }
     if ((rc = marks.mark(8))) return rc;
 
     LinearArgs l1;   // hid = GELU(LN2(q1) W1^T + b)
-    l1.a = fold_q ? b.q1 : b.qn; l1.lda = C; l1.w = fold_q ? w.fc1_wf : w.fc1_w; l1.bias = fold_q ? w.fc1_c : w.fc1_b;
+    l1.a = fold_fc1 ? b.q1 : b.qn; l1.lda = C; l1.w = fold_fc1 ? w.fc1_wf : w.fc1_w; l1.bias = fold_fc1 ? w.fc1_c : w.fc1_b;
     l1.y = b.hid; l1.ldy = s.hidden; l1.dtype = s.dtype; l1.m_max = rows; l1.m_dev = L_dev; l1.N = s.hidden; l1.K = C;
     l1.flags = kflag | VTP_FLAG_GELU;
-    if (fold_q) { l1.ln_mode = 2; l1.ln_stats = b.stats_acc; l1.ln_s = w.fc1_s; l1.ln_dim = C; l1.ln_eps = s.eps;
+    if (fold_fc1) { l1.ln_mode = 2; l1.ln_stats = b.stats_acc; l1.ln_s = w.fc1_s; l1.ln_dim = C; l1.ln_eps = s.eps;
                 l1.ln_slots = linear_stat_slots(C); }
     if ((rc = linear(l1, st)) || (rc = marks.mark(9))) return rc;
 
