@@ -103,7 +103,8 @@ class Block(nn.Module):
         self.flags = 0
         self.fold_layernorm = sr_ratio <= 1      # bf16: norm1 into q and kv, norm2 into fc1 (GEMM epilogues)
         self.fold_q_fc1 = sr_ratio > 1           # with a spatial reduction: q and fc1 only, the keys are normalised
-                                                 # on the way into the reducing convolution
+                                                 # on the way into the reducing convolution (the library runs norm2
+                                                 # as its own pass where C <= 128: the fold does not pay there)
         self._pack = _WeightPack()
 
     def complexity(self, num_inputs, num_queries):
