@@ -200,10 +200,10 @@ __device__ __forceinline__ void publish_partials(float* part, float (&acc)[CPL][
 // regions are in flight, and measured faster over the whole forward than at the 88 registers / five
 // CTAs the compiler picks on its own (six: +0.5 %, seven: +0.9 %, eight: +0.8 %).
 constexpr int POOL_LN = 0, POOL_STATS = 1, POOL_PLAIN = 2;
-// (A thread of a narrow-row layout holds one or two 16-byte vectors of a region: such kernels fit 16 (pooling; 12 for the unpool) or 9
-// CTAs per SM, and the kernel is bound by how many regions are in flight.)
+// (A thread of a narrow-row layout holds one or two 16-byte vectors of a region: such kernels run with 16 or 12 CTAs per SM
+// (a few spilled words in the unpool; measured faster all the same), and the kernel is bound by how many regions are in flight.)
 template <typename T, int G, int CPL, int MODE>
-__global__ void __launch_bounds__(128, (Lay<T, G, CPL>::TPG * CPL <= 1) ? 16 : ((Lay<T, G, CPL>::TPG * CPL <= 2) ? 9 : 7))
+__global__ void __launch_bounds__(128, (Lay<T, G, CPL>::TPG * CPL <= 1) ? 16 : ((Lay<T, G, CPL>::TPG * CPL <= 2) ? 12 : 7))
 pool_region_kernel(const T* __restrict__ x, RegionGeom g, const int32_t* __restrict__ idx,
                    const int32_t* __restrict__ region_first, const int32_t* __restrict__ offsets,
                    const int32_t* __restrict__ counts, int32_t* __restrict__ offsets_out,
@@ -430,7 +430,7 @@ __device__ __forceinline__ void gate_from_partials(const float* part, int C, int
 // out[b,tok] = ref[b,tok] + (q[p] - comp[p]) for the patch p that covers the token; optionally
 // also the next block's token statistics, router gate decisions and per-image counts.
 template <typename T, int G, int CPL>
-__global__ void __launch_bounds__(128, (Lay<T, G, CPL>::TPG * CPL <= 1) ? 12 : ((Lay<T, G, CPL>::TPG * CPL <= 2) ? 9 : 4))
+__global__ void __launch_bounds__(128, (Lay<T, G, CPL>::TPG * CPL <= 1) ? 16 : ((Lay<T, G, CPL>::TPG * CPL <= 2) ? 12 : 4))
 unpool_region_kernel(const T* __restrict__ q, const T* __restrict__ comp, const T* ref, T* out, RegionGeom g,
                      const int32_t* __restrict__ idx, const int32_t* __restrict__ region_first,
                      const int32_t* __restrict__ offsets, Splits sp, NextBlock nx) {
